@@ -1,0 +1,133 @@
+/* thrust_b200 — C ABI of the B200 (sm_100a) sort / scan / reduce_by_key path.
+ *
+ * This is the boundary a Thrust custom system (include/thrust_b200/system.h) binds
+ * to. Every entry point replaces one dispatch of the reference's CUDA system
+ * (file:line below are paths inside the reference project, Thrust 2.2.0).
+ *
+ * Conventions
+ *  - All data pointers are DEVICE pointers unless a parameter is named h_*.
+ *  - Scratch follows the two-phase convention the reference uses around its device
+ *    library calls (thrust/system/cuda/detail/sort.h:330-365, scan.h:80-118,
+ *    reduce_by_key.h:999-1047): call with d_temp == NULL to get *temp_bytes, then
+ *    call again with a buffer of at least that size (256-byte aligned).
+ *  - Work is enqueued on `stream` and the call returns without synchronising.
+ *    Kernels never trap or spin forever: a wait that runs out records a status
+ *    word in d_temp, read back with tb200_temp_status() after the stream is idle.
+ *  - Return value: 0 = success, > 0 = a cudaError_t, < 0 = one of tb200_error.
+ *  - Re-entrant: no global mutable state except the optional workspace pool
+ *    (mutex protected). Calls that share d_temp must be stream-ordered.
+ */
+#ifndef THRUST_B200_H_
+#define THRUST_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tb200_stream_t; /* same type as cudaStream_t */
+
+typedef enum tb200_dtype {
+  TB200_I8 = 0, TB200_U8 = 1, TB200_I16 = 2, TB200_U16 = 3, TB200_I32 = 4, TB200_U32 = 5,
+  TB200_I64 = 6, TB200_U64 = 7, TB200_F32 = 8, TB200_F64 = 9, TB200_BOOL = 10
+} tb200_dtype;
+
+typedef enum tb200_error {
+  TB200_OK = 0,
+  TB200_ERR_UNSUPPORTED = -1,      /* type / size combination has no kernel            */
+  TB200_ERR_INVALID_ARGUMENT = -2, /* NULL pointer, bad bit range, misaligned temp ... */
+  TB200_ERR_TEMP_TOO_SMALL = -3,   /* *temp_bytes below what the size query returned   */
+  TB200_ERR_WAIT_TIMEOUT = -4,     /* a bounded look-back wait ran out (device status) */
+  TB200_ERR_OVERFLOW = -5          /* a fixed-capacity buffer would have overflowed    */
+} tb200_error;
+
+/* Library version (major*10000 + minor*100 + patch) and a static description string. */
+int tb200_version(void);
+const char* tb200_error_string(int code);
+
+/* ---- radix sort ---------------------------------------------------------------------
+ * Stable LSD radix sort of n arithmetic keys, in place, optionally carrying one value
+ * array (val_bytes in {0,1,2,4,8,16}; 0 = keys only, d_vals ignored). Order: the
+ * reference's key encoding (sequential/stable_radix_sort.inl:43-141): integers by value,
+ * floating point by the bitwise total order (-0.0 before +0.0, NaNs by payload).
+ * descending != 0 gives thrust::greater<Key> with equal keys kept in input order
+ * (sequential/sort.inl:74-104). Only key bits [begin_bit, end_bit) are compared
+ * (0 and 8*sizeof(key) sort whole keys, which is what Thrust does).
+ * Replaces: thrust::cuda_cub::__radix_sort::radix_sort and the four
+ * cub::DeviceRadixSort calls behind sort / stable_sort / sort_by_key / stable_sort_by_key
+ * (thrust/system/cuda/detail/sort.h:209-380, 493-623). n is 64-bit (the reference
+ * narrows it to int, sort.h:228). */
+int tb200_radix_sort(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n,
+                     int key_dtype, int val_bytes, int descending, int begin_bit, int end_bit,
+                     tb200_stream_t stream);
+
+/* ---- scan ---------------------------------------------------------------------------
+ * Prefix sum with plus over n elements of dtype in {I32,U32,I64,U64,F32,F64}; accumulator
+ * type == element type. exclusive == 0: inclusive_scan. exclusive != 0: exclusive_scan
+ * seeded with *h_init (a HOST pointer to one element; NULL = value-initialised zero).
+ * d_out may equal d_in (exactly in place); no other overlap.
+ * Replaces: cuda_cub::detail::inclusive_scan_n_impl / exclusive_scan_n_impl and their
+ * cub::DispatchScan calls (thrust/system/cuda/detail/scan.h:50-125, 127-204). */
+int tb200_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out, uint64_t n,
+               int dtype, int exclusive, const void* h_init, tb200_stream_t stream);
+
+/* ---- reduce_by_key ------------------------------------------------------------------
+ * Runs of consecutive equal keys (thrust::equal_to<Key>) are reduced with plus over the
+ * values' own type. Emits, per run, its FIRST key (thrust/reduce.h:347) and the sum, and
+ * writes the run count to *d_num_runs (device, 8-byte aligned). Key types: any
+ * tb200_dtype; value dtype in {I32,U32,I64,U64,F32,F64}. Outputs must not overlap inputs.
+ * Replaces: cuda_cub::__reduce_by_key::reduce_by_key_dispatch / doit_step and the
+ * InitAgent + ReduceByKeyAgent kernels (thrust/system/cuda/detail/reduce_by_key.h:81-1058).
+ * Unlike the reference (reduce_by_key.h:1049-1052) the call itself does not synchronise;
+ * the caller reads *d_num_runs when it needs the end iterators. */
+int tb200_reduce_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys_in,
+                        const void* d_vals_in, void* d_keys_out, void* d_vals_out,
+                        uint64_t* d_num_runs, uint64_t n, int key_dtype, int val_dtype,
+                        tb200_stream_t stream);
+
+/* ---- sort-based histogram -----------------------------------------------------------
+ * Second half of the dense-histogram recipe (examples/histogram.cu:84-97): given SORTED
+ * data (dtype in {I32,U32,I64,U64,F32,F64}) and num_bins ascending bin values of the same
+ * type, counts[b] = upper_bound(data, bin[b]) - upper_bound(data, bin[b-1]) with
+ * operator< (so -0.0 == +0.0 here), counts[0] = upper_bound(data, bin[0]).
+ * Replaces: the vectorised thrust::upper_bound (generic/binary_search.inl:95-133 over
+ * cuda/detail/parallel_for.h:68-147) followed by thrust::adjacent_difference
+ * (cuda/detail/adjacent_difference.h:176-229), fused into one kernel. No scratch. */
+int tb200_histogram_sorted(const void* d_sorted, uint64_t n, int dtype, const void* d_bin_values,
+                           uint32_t num_bins, uint32_t* d_counts, tb200_stream_t stream);
+
+/* Status word of the last call that used d_temp: 0 or a tb200_error. Synchronises the
+ * stream (one 4-byte copy). Mirrors the reference's end-of-call synchronize + error check
+ * (thrust/system/cuda/detail/util.h:113-140, 251-299). */
+int tb200_temp_status(const void* d_temp, tb200_stream_t stream);
+
+/* ---- workspace pool -----------------------------------------------------------------
+ * The reference allocates and frees scratch with cudaMalloc/cudaFree inside every call
+ * (thrust/system/cuda/detail/malloc_and_free.h:53-118). The pool keeps one grow-only
+ * buffer per (device, stream) so steady-state calls allocate nothing.
+ * tb200_workspace_acquire returns a device buffer of at least `bytes`; it stays owned by
+ * the pool and is valid until the next acquire on the same (device, stream) or
+ * tb200_workspace_release_all(). */
+int tb200_workspace_acquire(size_t bytes, tb200_stream_t stream, void** d_ptr);
+int tb200_workspace_release_all(void);
+
+/* ---- host-buffer forms --------------------------------------------------------------
+ * The reference's flagship use is host vector -> device -> sort -> host (README.md:42-54;
+ * copies via thrust/system/cuda/detail/internal/copy_cross_system.h:51-113). These take
+ * HOST pointers (pinned for full speed), stage through pool workspace on the current
+ * device, run the device path above and copy the result back, synchronising before
+ * return. */
+int tb200_radix_sort_host(void* h_keys, void* h_vals, uint64_t n, int key_dtype, int val_bytes,
+                          int descending, tb200_stream_t stream);
+int tb200_scan_host(const void* h_in, void* h_out, uint64_t n, int dtype, int exclusive,
+                    const void* h_init, tb200_stream_t stream);
+int tb200_reduce_by_key_host(const void* h_keys_in, const void* h_vals_in, void* h_keys_out,
+                             void* h_vals_out, uint64_t* h_num_runs, uint64_t n, int key_dtype,
+                             int val_dtype, tb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THRUST_B200_H_ */

@@ -1,0 +1,137 @@
+"""TEST INFRASTRUCTURE — CPU checkers for thrust_b200. Never imported by the product.
+
+Two interchangeable checkers with the same numpy-facing methods:
+
+* ``port()``      — oracle/liboracle.so, the plain-C restatement (oracle.c);
+* ``ref("omp")`` / ``ref("cpp")`` — oracle/_ref/libthrust_ref_*.so, the unmodified
+  reference headers compiled against the reference's own OMP / CPP device system
+  (ref_shim.cpp). Built where the reference tree exists; the built files travel.
+
+Only tests/, ``__graft_entry__.smoke()`` and bench.py's CPU-baseline legs may import this.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+from typing import Optional, Tuple
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+
+I8, U8, I16, U16, I32, U32, I64, U64, F32, F64, BOOL = range(11)
+_NP_TO_DT = {
+    np.dtype(np.int8): I8, np.dtype(np.uint8): U8, np.dtype(np.int16): I16, np.dtype(np.uint16): U16,
+    np.dtype(np.int32): I32, np.dtype(np.uint32): U32, np.dtype(np.int64): I64, np.dtype(np.uint64): U64,
+    np.dtype(np.float32): F32, np.dtype(np.float64): F64, np.dtype(np.bool_): BOOL,
+}
+
+
+def dt_of(a: np.ndarray) -> int:
+    return _NP_TO_DT[a.dtype]
+
+
+def build(ref: bool = True) -> None:
+    """Compile liboracle.so and, when the reference tree is present, oracle/_ref."""
+    subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
+    if ref and Path("/root/reference/thrust/version.h").exists():
+        subprocess.run(["make", "-s", "-j2", "-C", str(HERE), "ref"], check=True)
+
+
+class CpuChecker:
+    """numpy front end over one of the CPU libraries (prefix ``oracle_`` or ``ref_``)."""
+
+    def __init__(self, path: Path, prefix: str, kind: str):
+        if not path.exists():
+            raise FileNotFoundError(f"{path} not built (run `make -C oracle`)")
+        self.kind = kind
+        self.path = path
+        self._lib = C.CDLL(str(path))
+        vp, u64, i32, u32 = C.c_void_p, C.c_uint64, C.c_int, C.c_uint32
+        self._sort = getattr(self._lib, prefix + "sort")
+        self._sort.argtypes, self._sort.restype = [vp, u64, i32, i32], i32
+        self._sbk = getattr(self._lib, prefix + "sort_by_key")
+        self._sbk.argtypes, self._sbk.restype = [vp, vp, u64, i32, i32, i32], i32
+        self._scan = getattr(self._lib, prefix + "scan")
+        self._scan.argtypes, self._scan.restype = [vp, vp, u64, i32, i32, vp], i32
+        self._rbk = getattr(self._lib, prefix + "reduce_by_key")
+        self._rbk.argtypes, self._rbk.restype = [vp, vp, vp, vp, u64, i32, i32], C.c_int64
+        self._hist = getattr(self._lib, prefix + "histogram")
+        self._hist.argtypes, self._hist.restype = [vp, u64, i32, vp, u32, vp], i32
+        self.threads = 1
+        if prefix == "ref_":
+            self._lib.ref_num_threads.restype = i32
+            self.threads = int(self._lib.ref_num_threads())
+            self._lib.ref_thrust_version.restype = i32
+            self.thrust_version = int(self._lib.ref_thrust_version())
+
+    @staticmethod
+    def _p(a: Optional[np.ndarray]):
+        return None if a is None else C.c_void_p(a.ctypes.data)
+
+    def sort(self, keys: np.ndarray, descending: bool = False) -> np.ndarray:
+        k = np.ascontiguousarray(keys).copy()
+        rc = self._sort(self._p(k), k.size, dt_of(k), int(descending))
+        assert rc == 0, rc
+        return k
+
+    def sort_inplace(self, keys: np.ndarray, descending: bool = False) -> None:
+        rc = self._sort(self._p(keys), keys.size, dt_of(keys), int(descending))
+        assert rc == 0, rc
+
+    def sort_by_key(self, keys: np.ndarray, vals: np.ndarray, descending: bool = False
+                    ) -> Tuple[np.ndarray, np.ndarray]:
+        k = np.ascontiguousarray(keys).copy()
+        v = np.ascontiguousarray(vals).copy()
+        self.sort_by_key_inplace(k, v, descending)
+        return k, v
+
+    def sort_by_key_inplace(self, k: np.ndarray, v: np.ndarray, descending: bool = False) -> None:
+        rc = self._sbk(self._p(k), self._p(v), k.size, dt_of(k), v.dtype.itemsize, int(descending))
+        assert rc == 0, rc
+
+    def scan(self, a: np.ndarray, exclusive: bool = False, init=None, inplace: bool = False) -> np.ndarray:
+        a = np.ascontiguousarray(a)
+        out = a if inplace else np.empty_like(a)
+        ini = None if init is None else np.array([init], dtype=a.dtype)
+        rc = self._scan(self._p(a), self._p(out), a.size, dt_of(a), int(exclusive), self._p(ini))
+        assert rc == 0, rc
+        return out
+
+    def reduce_by_key(self, keys: np.ndarray, vals: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+        keys = np.ascontiguousarray(keys)
+        vals = np.ascontiguousarray(vals)
+        ko = np.empty_like(keys)
+        vo = np.empty_like(vals)
+        r = self._rbk(self._p(keys), self._p(vals), self._p(ko), self._p(vo), keys.size, dt_of(keys), dt_of(vals))
+        assert r >= 0, r
+        return ko[:r].copy(), vo[:r].copy()
+
+    def histogram(self, data: np.ndarray, bin_values: np.ndarray) -> np.ndarray:
+        d = np.ascontiguousarray(data).copy()
+        b = np.ascontiguousarray(bin_values, dtype=d.dtype)
+        counts = np.empty(b.size, dtype=np.uint32)
+        rc = self._hist(self._p(d), d.size, dt_of(d), self._p(b), b.size, self._p(counts))
+        assert rc == 0, rc
+        return counts
+
+
+_cache = {}
+
+
+def port() -> CpuChecker:
+    if "port" not in _cache:
+        _cache["port"] = CpuChecker(HERE / "liboracle.so", "oracle_", "port")
+    return _cache["port"]
+
+
+def ref(system: str = "cpp") -> CpuChecker:
+    key = "ref_" + system
+    if key not in _cache:
+        _cache[key] = CpuChecker(HERE / "_ref" / f"libthrust_ref_{system}.so", "ref_", "reference")
+    return _cache[key]
+
+
+def have_ref(system: str = "cpp") -> bool:
+    return (HERE / "_ref" / f"libthrust_ref_{system}.so").exists()

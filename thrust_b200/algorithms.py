@@ -1,0 +1,199 @@
+"""Python mirror of the thrust:: algorithms this library replaces.
+
+Each function takes CUDA tensors, passes their device pointers and the current
+stream through the C ABI and, like the reference's default ``thrust::cuda::par``
+policy, synchronises and checks the device status before returning
+(thrust/system/cuda/detail/util.h:113-140) unless ``sync=False``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _capi as capi
+
+_TORCH_TO_TB = {
+    torch.int8: capi.I8, torch.uint8: capi.U8, torch.int16: capi.I16, torch.uint16: capi.U16,
+    torch.int32: capi.I32, torch.uint32: capi.U32, torch.int64: capi.I64, torch.uint64: capi.U64,
+    torch.float32: capi.F32, torch.float64: capi.F64, torch.bool: capi.BOOL,
+}
+_NUMERIC = (capi.I32, capi.U32, capi.I64, capi.U64, capi.F32, capi.F64)
+
+
+def tb200_dtype(t: torch.Tensor, dtype: Optional[int] = None) -> int:
+    """tb200_dtype code of a tensor (``dtype`` overrides, e.g. to read int64 storage as U64)."""
+    if dtype is not None:
+        if capi.DTYPE_BYTES[dtype] != t.element_size():
+            raise ValueError("dtype override must keep the element size")
+        return dtype
+    try:
+        return _TORCH_TO_TB[t.dtype]
+    except KeyError:
+        raise TypeError(f"no tb200 dtype for {t.dtype}") from None
+
+
+def _check_tensor(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (thrust_b200 has no CPU path)")
+    if not t.is_contiguous() or t.dim() != 1:
+        raise ValueError(f"{name} must be a contiguous 1-D tensor")
+
+
+def _stream(t: torch.Tensor) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _temp(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+def _finish(temp: torch.Tensor, stream, what: str, sync: bool) -> None:
+    if sync:
+        capi.check(capi.lib.tb200_temp_status(C.c_void_p(temp.data_ptr()), stream), what)
+
+
+def sort_by_key(keys: torch.Tensor, values: Optional[torch.Tensor] = None, descending: bool = False,
+                key_dtype: Optional[int] = None, begin_bit: int = 0, end_bit: Optional[int] = None,
+                sync: bool = True, temp: Optional[torch.Tensor] = None) -> None:
+    """thrust::sort_by_key / stable_sort_by_key (thrust/sort.h), in place; values=None sorts keys only."""
+    _check_tensor(keys, "keys")
+    kd = tb200_dtype(keys, key_dtype)
+    n = keys.numel()
+    vb = 0
+    vptr = None
+    if values is not None:
+        _check_tensor(values, "values")
+        if values.numel() != n:
+            raise ValueError("keys and values differ in length")
+        vb = values.element_size()
+        vptr = values.data_ptr()
+    if end_bit is None:
+        end_bit = 8 * keys.element_size()
+    with torch.cuda.device(keys.device):
+        stream = _stream(keys)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_radix_sort(None, C.byref(need), None, None, n, kd, vb, int(descending),
+                                             begin_bit, end_bit, stream), "tb200_radix_sort(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, keys.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_radix_sort(C.c_void_p(temp.data_ptr()), C.byref(have),
+                                             C.c_void_p(keys.data_ptr()), C.c_void_p(vptr), n, kd, vb,
+                                             int(descending), begin_bit, end_bit, stream), "tb200_radix_sort")
+        _finish(temp, stream, "tb200_radix_sort", sync)
+
+
+def sort(keys: torch.Tensor, descending: bool = False, **kw) -> None:
+    """thrust::sort on arithmetic keys (stable on this path, like the reference's radix path)."""
+    sort_by_key(keys, None, descending, **kw)
+
+
+stable_sort = sort
+stable_sort_by_key = sort_by_key
+
+
+def _scan(inp: torch.Tensor, out: Optional[torch.Tensor], exclusive: bool, init, dtype: Optional[int],
+          sync: bool, temp: Optional[torch.Tensor]) -> torch.Tensor:
+    _check_tensor(inp, "input")
+    dt = tb200_dtype(inp, dtype)
+    if dt not in _NUMERIC:
+        raise TypeError("scan supports 4- and 8-byte integers, float32 and float64")
+    if out is None:
+        out = torch.empty_like(inp)
+    _check_tensor(out, "output")
+    if out.numel() != inp.numel() or out.element_size() != inp.element_size():
+        raise ValueError("output must match the input")
+    n = inp.numel()
+    init_buf = None
+    if exclusive and init is not None:
+        ctype = {capi.I32: C.c_int32, capi.U32: C.c_uint32, capi.I64: C.c_int64, capi.U64: C.c_uint64,
+                 capi.F32: C.c_float, capi.F64: C.c_double}[dt]
+        init_buf = ctype(init)
+    with torch.cuda.device(inp.device):
+        stream = _stream(inp)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_scan(None, C.byref(need), None, None, n, dt, int(exclusive), None, stream),
+                   "tb200_scan(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, inp.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_scan(C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(inp.data_ptr()),
+                                       C.c_void_p(out.data_ptr()), n, dt, int(exclusive),
+                                       C.byref(init_buf) if init_buf is not None else None, stream),
+                   "tb200_scan")
+        _finish(temp, stream, "tb200_scan", sync)
+    return out
+
+
+def inclusive_scan(inp: torch.Tensor, out: Optional[torch.Tensor] = None, dtype: Optional[int] = None,
+                   sync: bool = True, temp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """thrust::inclusive_scan with plus (thrust/scan.h:99); ``out`` may be ``inp``."""
+    return _scan(inp, out, False, None, dtype, sync, temp)
+
+
+def exclusive_scan(inp: torch.Tensor, out: Optional[torch.Tensor] = None, init=None,
+                   dtype: Optional[int] = None, sync: bool = True,
+                   temp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """thrust::exclusive_scan with plus; init=None is the value-initialised default."""
+    return _scan(inp, out, True, init, dtype, sync, temp)
+
+
+def reduce_by_key(keys: torch.Tensor, values: torch.Tensor, keys_out: Optional[torch.Tensor] = None,
+                  values_out: Optional[torch.Tensor] = None, key_dtype: Optional[int] = None,
+                  val_dtype: Optional[int] = None,
+                  temp: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, int]:
+    """thrust::reduce_by_key (equal_to, plus). Returns (keys_out, values_out, number of runs);
+    like the reference it synchronises to read the run count (cuda/detail/reduce_by_key.h:1049-1052)."""
+    _check_tensor(keys, "keys")
+    _check_tensor(values, "values")
+    n = keys.numel()
+    if values.numel() != n:
+        raise ValueError("keys and values differ in length")
+    kd = tb200_dtype(keys, key_dtype)
+    vd = tb200_dtype(values, val_dtype)
+    if keys_out is None:
+        keys_out = torch.empty_like(keys)
+    if values_out is None:
+        values_out = torch.empty_like(values)
+    with torch.cuda.device(keys.device):
+        stream = _stream(keys)
+        runs = torch.zeros(1, dtype=torch.int64, device=keys.device)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_reduce_by_key(None, C.byref(need), None, None, None, None, None, n, kd, vd,
+                                                stream), "tb200_reduce_by_key(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, keys.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_reduce_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()),
+            C.c_void_p(values.data_ptr()), C.c_void_p(keys_out.data_ptr()), C.c_void_p(values_out.data_ptr()),
+            C.c_void_p(runs.data_ptr()), n, kd, vd, stream), "tb200_reduce_by_key")
+        _finish(temp, stream, "tb200_reduce_by_key", True)
+        return keys_out, values_out, int(runs.item())
+
+
+def histogram_sorted(sorted_data: torch.Tensor, bin_values: torch.Tensor, dtype: Optional[int] = None,
+                     sync: bool = True) -> torch.Tensor:
+    """upper_bound of every bin value in sorted data + adjacent_difference (examples/histogram.cu:84-97)."""
+    _check_tensor(sorted_data, "sorted_data")
+    _check_tensor(bin_values, "bin_values")
+    dt = tb200_dtype(sorted_data, dtype)
+    counts = torch.empty(bin_values.numel(), dtype=torch.int32, device=sorted_data.device)
+    with torch.cuda.device(sorted_data.device):
+        stream = _stream(sorted_data)
+        capi.check(capi.lib.tb200_histogram_sorted(C.c_void_p(sorted_data.data_ptr()), sorted_data.numel(), dt,
+                                                   C.c_void_p(bin_values.data_ptr()), bin_values.numel(),
+                                                   C.c_void_p(counts.data_ptr()), stream),
+                   "tb200_histogram_sorted")
+        if sync:
+            torch.cuda.current_stream(sorted_data.device).synchronize()
+    return counts
+
+
+def dense_histogram(data: torch.Tensor, bin_values: torch.Tensor, dtype: Optional[int] = None) -> torch.Tensor:
+    """The whole dense-histogram recipe of examples/histogram.cu:60-101: copy, sort, search, difference."""
+    work = data.clone()
+    sort(work, key_dtype=dtype)
+    return histogram_sorted(work, bin_values, dtype)

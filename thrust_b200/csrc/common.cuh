@@ -1,0 +1,135 @@
+// Shared device/host helpers of the thrust_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/thrust_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "thrust_b200 kernels are written for sm_100a only"
+#endif
+
+namespace tb200 {
+
+constexpr int kWarp = 32;
+
+// Every spin on another CTA's tile descriptor gives up after this many polls
+// (with nanosleep back-off this is on the order of a second), raises the status
+// word and lets the CTA finish without waiting again.
+constexpr unsigned kSpinLimit = 1u << 22;
+
+// Layout of the first 256 bytes of every scratch buffer.
+struct TempHeader {
+  int status;            // 0 or a tb200_error, written by kernels
+  unsigned ticket;       // dynamic tile counter of single-kernel algorithms
+  unsigned long long aux[30];
+};
+static_assert(sizeof(TempHeader) <= 256, "header must fit the first 256 bytes");
+constexpr size_t kHeaderBytes = 256;
+
+__host__ __device__ constexpr size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ inline int dtype_bytes(int dt) {
+  switch (dt) {
+    case TB200_I8: case TB200_U8: case TB200_BOOL: return 1;
+    case TB200_I16: case TB200_U16: return 2;
+    case TB200_I32: case TB200_U32: case TB200_F32: return 4;
+    case TB200_I64: case TB200_U64: case TB200_F64: return 8;
+    default: return 0;
+  }
+}
+
+#define TB200_CUDA_TRY(expr)                       \
+  do {                                             \
+    cudaError_t _e = (expr);                       \
+    if (_e != cudaSuccess) return (int)_e;         \
+  } while (0)
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ unsigned lane_id() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%laneid;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned lanemask_lt() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%lanemask_lt;" : "=r"(r));
+  return r;
+}
+
+// Relaxed, gpu-scope 64-bit accesses: single-copy atomic, never cached in L1.
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_relaxed_s32(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void backoff(unsigned polls) {
+  if (polls > 16) __nanosleep(polls > 256 ? 256 : 64);
+}
+
+// Tile descriptors of the decoupled look-back chains. A descriptor is W 64-bit
+// words; each word carries {state:32 | payload:32}. A writer stores the words one
+// by one with relaxed 8-byte stores; a reader accepts a descriptor only when all
+// W words show the same state. States only move forward (EMPTY -> AGGREGATE ->
+// PREFIX) and each word is written once per state, so equal states imply that the
+// W payloads belong together. No fences are needed.
+enum : unsigned { kStateEmpty = 0, kStateAggregate = 1, kStatePrefix = 2 };
+
+template <int W>
+struct alignas(W == 1 ? 8 : (W == 2 ? 16 : 32)) TileWords {
+  unsigned long long w[W];
+};
+
+template <int W>
+__device__ __forceinline__ void publish(TileWords<W>* d, unsigned state, const unsigned (&payload)[W]) {
+#pragma unroll
+  for (int i = 0; i < W; ++i)
+    st_relaxed_u64(&d->w[i], ((unsigned long long)state << 32) | payload[i]);
+}
+
+// Returns the common state (kStateEmpty if the words disagree or are empty).
+template <int W>
+__device__ __forceinline__ unsigned peek(const TileWords<W>* d, unsigned (&payload)[W]) {
+  unsigned long long v[W];
+  if constexpr (W == 2) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(v[0]), "=l"(v[1]) : "l"(d) : "memory");
+  } else if constexpr (W == 4) {
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(v[0]), "=l"(v[1]) : "l"(d) : "memory");
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(v[2]), "=l"(v[3]) : "l"(&d->w[2]) : "memory");
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) v[i] = ld_relaxed_u64(&d->w[i]);
+  }
+  unsigned st = (unsigned)(v[0] >> 32);
+  bool same = true;
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    payload[i] = (unsigned)v[i];
+    same = same && ((unsigned)(v[i] >> 32) == st);
+  }
+  return same ? st : kStateEmpty;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tb200

@@ -1,0 +1,341 @@
+// reduce_by_key (equal_to / plus) as ONE streaming kernel: a segmented scan of
+// (head-count, open-run sum) pairs with a decoupled look-back chain across tiles.
+//
+// For element i let head(i) = (i == 0 || key[i] != key[i-1]). The scan state
+// before element i is (c, s): c = number of heads in [0, i), s = sum of the run
+// that is open at i-1. At every head i > 0 the run that just closed is emitted:
+// values_out[c-1] = s, and the new run's FIRST key: keys_out[c] = key[i]. The
+// last tile emits the final open run and the run count. Sums are formed left to
+// right inside a thread and in scan-tree order across lanes, warps and tiles:
+// exact for integers, re-associated for floating point.
+//
+// Tile layout is the one of the scan kernel (warp-contiguous slices, lane-strided
+// vectors), so key and value loads are full-width and coalesced.
+#include "common.cuh"
+
+namespace tb200 {
+namespace {
+
+constexpr int kRbkThreads = 256;
+constexpr int kRbkWarps = kRbkThreads / kWarp;
+constexpr int kRbkChunks = 4;
+
+template <typename T, int E>
+struct alignas(sizeof(T) * E) Pack {
+  T v[E];
+};
+
+template <typename V>
+struct Seg {
+  unsigned cnt;
+  V val;
+};
+
+template <typename V>
+__device__ __forceinline__ Seg<V> seg_combine(const Seg<V>& a, const Seg<V>& b) {
+  Seg<V> r;
+  r.cnt = a.cnt + b.cnt;
+  r.val = b.cnt ? b.val : a.val + b.val;
+  return r;
+}
+
+template <typename V>
+struct SegWords {
+  static constexpr int W = 4;  // {count lo, count hi, value lo, value hi}
+  __device__ static void pack(unsigned long long cnt, V val, unsigned (&p)[W]) {
+    p[0] = (unsigned)cnt;
+    p[1] = (unsigned)(cnt >> 32);
+    if constexpr (sizeof(V) == 4) {
+      p[2] = __builtin_bit_cast(unsigned, val);
+      p[3] = 0;
+    } else {
+      unsigned long long b = __builtin_bit_cast(unsigned long long, val);
+      p[2] = (unsigned)b;
+      p[3] = (unsigned)(b >> 32);
+    }
+  }
+  __device__ static void unpack(const unsigned (&p)[W], unsigned long long& cnt, V& val) {
+    cnt = ((unsigned long long)p[1] << 32) | p[0];
+    if constexpr (sizeof(V) == 4) val = __builtin_bit_cast(V, p[2]);
+    else val = __builtin_bit_cast(V, ((unsigned long long)p[3] << 32) | p[2]);
+  }
+};
+
+// Look-back of warp 0 over (count, value) descriptors; the operator is not
+// commutative, so far predecessors are combined on the left of near ones.
+template <typename V>
+__device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* status,
+                             unsigned long long& out_cnt, V& out_val) {
+  const unsigned lane = lane_id();
+  unsigned long long acc_cnt = 0;
+  V acc_val = V(0);
+  long long base = (long long)tile - 1;
+  bool timed_out = false;
+  while (true) {
+    const long long idx = base - lane;
+    unsigned st = kStatePrefix;
+    unsigned long long cnt = 0;
+    V val = V(0);
+    if (idx >= 0) {
+      unsigned payload[4];
+      unsigned polls = 0;
+      while ((st = peek<4>(&tiles[idx], payload)) == kStateEmpty) {
+        backoff(++polls);
+        if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+          timed_out = true;
+          st = kStatePrefix;
+          break;
+        }
+      }
+      if (!timed_out) SegWords<V>::unpack(payload, cnt, val);
+    }
+    const unsigned pm = __ballot_sync(0xffffffffu, st == kStatePrefix);
+    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+    if (lane > first) { cnt = 0; val = V(0); }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
+      const V ov = __shfl_down_sync(0xffffffffu, val, off);
+      if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val)
+        val = cnt ? val : ov + val;
+        cnt = oc + cnt;
+      }
+    }
+    cnt = __shfl_sync(0xffffffffu, cnt, 0);
+    val = __shfl_sync(0xffffffffu, val, 0);
+    // this window lies to the left of everything accumulated so far
+    acc_val = acc_cnt ? acc_val : val + acc_val;
+    acc_cnt = cnt + acc_cnt;
+    if (pm) break;
+    base -= 32;
+  }
+  if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+  out_cnt = acc_cnt;
+  out_val = acc_val;
+}
+
+template <typename K, typename V, bool ALIGNED>
+__global__ void __launch_bounds__(kRbkThreads)
+reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __restrict__ keys_out,
+                     V* __restrict__ vals_out, unsigned long long* __restrict__ num_runs, uint64_t n,
+                     unsigned num_tiles, TempHeader* hdr, TileWords<4>* tiles) {
+  constexpr int E = 16 / (sizeof(K) > sizeof(V) ? sizeof(K) : sizeof(V));
+  constexpr int C = kRbkChunks;
+  constexpr int WARP_ITEMS = kWarp * C * E;
+  constexpr int TILE = kRbkThreads * C * E;
+
+  __shared__ unsigned s_tile;
+  __shared__ unsigned s_warp_cnt[kRbkWarps];
+  __shared__ V s_warp_val[kRbkWarps];
+  __shared__ unsigned long long s_prefix_cnt;
+  __shared__ V s_prefix_val;
+
+  if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->ticket, 1u);
+  __syncthreads();
+  const unsigned tile = s_tile;
+  const unsigned warp = threadIdx.x / kWarp;
+  const unsigned lane = lane_id();
+  const uint64_t tile_base = (uint64_t)tile * TILE;
+  const uint64_t warp_base = tile_base + (uint64_t)warp * WARP_ITEMS;
+  const bool full = tile_base + TILE <= n;
+
+  K k[C][E];
+  V v[C][E];
+  if (ALIGNED && full) {
+    const Pack<K, E>* ksrc = reinterpret_cast<const Pack<K, E>*>(keys + warp_base);
+    const Pack<V, E>* vsrc = reinterpret_cast<const Pack<V, E>*>(vals + warp_base);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const Pack<K, E> kk = ksrc[c * kWarp + lane];
+      const Pack<V, E> vv = vsrc[c * kWarp + lane];
+#pragma unroll
+      for (int e = 0; e < E; ++e) { k[c][e] = kk.v[e]; v[c][e] = vv.v[e]; }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const uint64_t i = warp_base + (uint64_t)(c * kWarp + lane) * E + e;
+        k[c][e] = i < n ? keys[i] : K(0);
+        v[c][e] = i < n ? vals[i] : V(0);
+      }
+  }
+
+  // key just before this warp's slice (lane 0 of chunk 0 needs it)
+  K slice_prev = K(0);
+  if (lane == 0 && warp_base > 0 && warp_base <= n) slice_prev = keys[warp_base - 1];
+
+  unsigned heads = 0;  // bit (c*E+e) set when the element starts a run
+  Seg<V> excl[C];
+  Seg<V> carry{0u, V(0)};
+  K prev_chunk_last = slice_prev;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    K prev = __shfl_up_sync(0xffffffffu, k[c][E - 1], 1);
+    if (lane == 0) prev = prev_chunk_last;
+    prev_chunk_last = __shfl_sync(0xffffffffu, k[c][E - 1], 31);
+    Seg<V> mine{0u, V(0)};
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const uint64_t i = warp_base + (uint64_t)(c * kWarp + lane) * E + e;
+      const bool head = i < n && (i == 0 || !(k[c][e] == prev));
+      prev = k[c][e];
+      if (head) { heads |= 1u << (c * E + e); mine.cnt += 1; mine.val = v[c][e]; }
+      else mine.val = mine.val + v[c][e];
+    }
+    Seg<V> s = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      Seg<V> o;
+      o.cnt = __shfl_up_sync(0xffffffffu, s.cnt, off);
+      o.val = __shfl_up_sync(0xffffffffu, s.val, off);
+      if (lane >= off) s = seg_combine(o, s);
+    }
+    Seg<V> e1;
+    e1.cnt = __shfl_up_sync(0xffffffffu, s.cnt, 1);
+    e1.val = __shfl_up_sync(0xffffffffu, s.val, 1);
+    if (lane == 0) { e1.cnt = 0; e1.val = V(0); }
+    excl[c] = seg_combine(carry, e1);
+    Seg<V> tot;
+    tot.cnt = __shfl_sync(0xffffffffu, s.cnt, 31);
+    tot.val = __shfl_sync(0xffffffffu, s.val, 31);
+    carry = seg_combine(carry, tot);
+  }
+  if (lane == 31) { s_warp_cnt[warp] = carry.cnt; s_warp_val[warp] = carry.val; }
+  __syncthreads();
+
+  Seg<V> warp_prefix{0u, V(0)}, tile_total{0u, V(0)};
+#pragma unroll
+  for (int w = 0; w < kRbkWarps; ++w) {
+    const Seg<V> t{s_warp_cnt[w], s_warp_val[w]};
+    if (w < (int)warp) warp_prefix = seg_combine(warp_prefix, t);
+    tile_total = seg_combine(tile_total, t);
+  }
+
+  if (warp == 0) {
+    unsigned payload[4];
+    unsigned long long pc = 0;
+    V pv = V(0);
+    if (tile != 0) {
+      if (lane == 0) {
+        SegWords<V>::pack(tile_total.cnt, tile_total.val, payload);
+        publish<4>(&tiles[tile], kStateAggregate, payload);
+      }
+      lookback_seg<V>(tiles, tile, &hdr->status, pc, pv);
+    }
+    if (lane == 0) {
+      const unsigned long long ic = pc + tile_total.cnt;
+      const V iv = tile_total.cnt ? tile_total.val : pv + tile_total.val;
+      SegWords<V>::pack(ic, iv, payload);
+      publish<4>(&tiles[tile], kStatePrefix, payload);
+      s_prefix_cnt = pc;
+      s_prefix_val = pv;
+      if (tile == num_tiles - 1) {  // close the last run and report the count
+        if (ic > 0) vals_out[ic - 1] = iv;
+        *num_runs = ic;
+      }
+    }
+  }
+  __syncthreads();
+
+  // exclusive state of this thread's first element of every chunk, then walk
+  const unsigned long long tile_cnt = s_prefix_cnt;
+  const V tile_val = s_prefix_val;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    // (tile prefix) (+) (warp prefix) (+) (lane-exclusive inside the warp)
+    Seg<V> local = seg_combine(warp_prefix, excl[c]);
+    unsigned long long cnt = tile_cnt + local.cnt;
+    V run = local.cnt ? local.val : tile_val + local.val;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (heads & (1u << (c * E + e))) {
+        if (cnt > 0) vals_out[cnt - 1] = run;
+        keys_out[cnt] = k[c][e];
+        cnt += 1;
+        run = v[c][e];
+      } else {
+        run = run + v[c][e];
+      }
+    }
+  }
+}
+
+template <typename K, typename V>
+int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vin, void* kout, void* vout,
+               uint64_t* d_num_runs, uint64_t n, cudaStream_t stream) {
+  constexpr int E = 16 / (sizeof(K) > sizeof(V) ? sizeof(K) : sizeof(V));
+  constexpr uint64_t TILE = (uint64_t)kRbkThreads * kRbkChunks * E;
+  const uint64_t tiles = (n + TILE - 1) / TILE;
+  const size_t need = kHeaderBytes + (size_t)tiles * sizeof(TileWords<4>);
+  if (d_temp == nullptr) {
+    *temp_bytes = need;
+    return TB200_OK;
+  }
+  if (*temp_bytes < need) return TB200_ERR_TEMP_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(d_temp) % 256) return TB200_ERR_INVALID_ARGUMENT;
+  if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
+  if (d_num_runs == nullptr || reinterpret_cast<uintptr_t>(d_num_runs) % 8) return TB200_ERR_INVALID_ARGUMENT;
+  TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, need, stream));
+  TB200_CUDA_TRY(cudaMemsetAsync(d_num_runs, 0, sizeof(uint64_t), stream));
+  if (n == 0) return TB200_OK;
+  if (!kin || !vin || !kout || !vout) return TB200_ERR_INVALID_ARGUMENT;
+  auto* hdr = static_cast<TempHeader*>(d_temp);
+  auto* desc = reinterpret_cast<TileWords<4>*>(static_cast<char*>(d_temp) + kHeaderBytes);
+  const bool aligned = reinterpret_cast<uintptr_t>(kin) % (sizeof(K) * E) == 0 &&
+                       reinterpret_cast<uintptr_t>(vin) % (sizeof(V) * E) == 0;
+  const dim3 grid((unsigned)tiles), block(kRbkThreads);
+  auto* nr = reinterpret_cast<unsigned long long*>(d_num_runs);
+  if (aligned)
+    reduce_by_key_kernel<K, V, true><<<grid, block, 0, stream>>>(
+        static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout), static_cast<V*>(vout), nr,
+        n, (unsigned)tiles, hdr, desc);
+  else
+    reduce_by_key_kernel<K, V, false><<<grid, block, 0, stream>>>(
+        static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout), static_cast<V*>(vout), nr,
+        n, (unsigned)tiles, hdr, desc);
+  return (int)cudaGetLastError();
+}
+
+template <typename K>
+int launch_rbk_vals(int val_dtype, void* d_temp, size_t* temp_bytes, const void* kin, const void* vin,
+                    void* kout, void* vout, uint64_t* d_num_runs, uint64_t n, cudaStream_t stream) {
+  switch (val_dtype) {
+    case TB200_I32: case TB200_U32:
+      return launch_rbk<K, uint32_t>(d_temp, temp_bytes, kin, vin, kout, vout, d_num_runs, n, stream);
+    case TB200_I64: case TB200_U64:
+      return launch_rbk<K, unsigned long long>(d_temp, temp_bytes, kin, vin, kout, vout, d_num_runs, n, stream);
+    case TB200_F32:
+      return launch_rbk<K, float>(d_temp, temp_bytes, kin, vin, kout, vout, d_num_runs, n, stream);
+    case TB200_F64:
+      return launch_rbk<K, double>(d_temp, temp_bytes, kin, vin, kout, vout, d_num_runs, n, stream);
+    default:
+      return TB200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_reduce_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys_in,
+                                   const void* d_vals_in, void* d_keys_out, void* d_vals_out,
+                                   uint64_t* d_num_runs, uint64_t n, int key_dtype, int val_dtype,
+                                   tb200_stream_t stream) {
+  using namespace tb200;
+  if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+#define RBK_KEYS(K) \
+  return launch_rbk_vals<K>(val_dtype, d_temp, temp_bytes, d_keys_in, d_vals_in, d_keys_out, d_vals_out, \
+                            d_num_runs, n, stream)
+  switch (key_dtype) {
+    // integer keys compare by bit pattern; floating-point keys with IEEE ==
+    case TB200_I8: case TB200_U8: case TB200_BOOL: RBK_KEYS(uint8_t);
+    case TB200_I16: case TB200_U16: RBK_KEYS(uint16_t);
+    case TB200_I32: case TB200_U32: RBK_KEYS(uint32_t);
+    case TB200_I64: case TB200_U64: RBK_KEYS(unsigned long long);
+    case TB200_F32: RBK_KEYS(float);
+    case TB200_F64: RBK_KEYS(double);
+    default: return TB200_ERR_UNSUPPORTED;
+  }
+#undef RBK_KEYS
+}

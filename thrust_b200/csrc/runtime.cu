@@ -1,0 +1,203 @@
+// Host-side runtime of the C ABI: status read-back, error strings, the workspace
+// pool and the host-buffer entry points (stage in, run the device path, copy out).
+#include "common.cuh"
+
+#include <map>
+#include <mutex>
+#include <utility>
+
+namespace tb200 {
+namespace {
+
+struct PoolEntry {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+std::mutex g_pool_mutex;
+std::map<std::pair<int, cudaStream_t>, PoolEntry> g_pool;
+
+// Two pool buffers per (device, stream) would alias, so host-buffer forms carve
+// their staging arrays and the algorithm scratch out of ONE acquisition.
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  void* take(size_t bytes) {
+    void* r = base ? base + off : nullptr;
+    off += align_up(bytes, 256);
+    return r;
+  }
+};
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_version(void) { return 100; }
+
+extern "C" const char* tb200_error_string(int code) {
+  switch (code) {
+    case TB200_OK: return "success";
+    case TB200_ERR_UNSUPPORTED: return "tb200: unsupported type or size";
+    case TB200_ERR_INVALID_ARGUMENT: return "tb200: invalid argument";
+    case TB200_ERR_TEMP_TOO_SMALL: return "tb200: temporary storage too small";
+    case TB200_ERR_WAIT_TIMEOUT: return "tb200: bounded look-back wait ran out";
+    case TB200_ERR_OVERFLOW: return "tb200: fixed-capacity buffer overflow";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "tb200: unknown error";
+  }
+}
+
+extern "C" int tb200_temp_status(const void* d_temp, tb200_stream_t stream) {
+  if (d_temp == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  int st = 0;
+  TB200_CUDA_TRY(cudaMemcpyAsync(&st, d_temp, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  TB200_CUDA_TRY(cudaStreamSynchronize(stream));
+  return st;
+}
+
+extern "C" int tb200_workspace_acquire(size_t bytes, tb200_stream_t stream, void** d_ptr) {
+  using namespace tb200;
+  if (d_ptr == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  int dev = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  PoolEntry& e = g_pool[std::make_pair(dev, (cudaStream_t)stream)];
+  if (e.bytes < bytes) {
+    if (e.ptr) {
+      // the old buffer may still be in use by work queued on this stream
+      TB200_CUDA_TRY(cudaStreamSynchronize(stream));
+      TB200_CUDA_TRY(cudaFree(e.ptr));
+      e.ptr = nullptr;
+      e.bytes = 0;
+    }
+    const size_t want = align_up(bytes + bytes / 16, (size_t)2 << 20);
+    cudaError_t err = cudaMalloc(&e.ptr, want);
+    if (err != cudaSuccess) {
+      (void)cudaGetLastError();  // clear the sticky allocation error, as the reference does
+      e.ptr = nullptr;
+      return (int)err;
+    }
+    e.bytes = want;
+  }
+  *d_ptr = e.ptr;
+  return TB200_OK;
+}
+
+extern "C" int tb200_workspace_release_all(void) {
+  using namespace tb200;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  int rc = TB200_OK;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (auto& kv : g_pool) {
+    if (kv.second.ptr) {
+      cudaSetDevice(kv.first.first);
+      cudaError_t e = cudaFree(kv.second.ptr);
+      if (e != cudaSuccess) rc = (int)e;
+    }
+  }
+  g_pool.clear();
+  cudaSetDevice(cur);
+  return rc;
+}
+
+extern "C" int tb200_scan_host(const void* h_in, void* h_out, uint64_t n, int dtype, int exclusive,
+                               const void* h_init, tb200_stream_t stream) {
+  using namespace tb200;
+  const int eb = dtype_bytes(dtype);
+  if (eb == 0) return TB200_ERR_UNSUPPORTED;
+  if (n == 0) return TB200_OK;
+  if (!h_in || !h_out) return TB200_ERR_INVALID_ARGUMENT;
+  size_t temp_bytes = 0;
+  int rc = tb200_scan(nullptr, &temp_bytes, nullptr, nullptr, n, dtype, exclusive, h_init, stream);
+  if (rc) return rc;
+  Carver size(nullptr);
+  size.take(temp_bytes);
+  size.take((size_t)n * eb);
+  void* ws = nullptr;
+  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  if (rc) return rc;
+  Carver c(ws);
+  void* d_temp = c.take(temp_bytes);
+  void* d_data = c.take((size_t)n * eb);
+  TB200_CUDA_TRY(cudaMemcpyAsync(d_data, h_in, (size_t)n * eb, cudaMemcpyHostToDevice, stream));
+  rc = tb200_scan(d_temp, &temp_bytes, d_data, d_data, n, dtype, exclusive, h_init, stream);
+  if (rc) return rc;
+  TB200_CUDA_TRY(cudaMemcpyAsync(h_out, d_data, (size_t)n * eb, cudaMemcpyDeviceToHost, stream));
+  return tb200_temp_status(d_temp, stream);
+}
+
+extern "C" int tb200_radix_sort_host(void* h_keys, void* h_vals, uint64_t n, int key_dtype, int val_bytes,
+                                     int descending, tb200_stream_t stream) {
+  using namespace tb200;
+  const int kb = dtype_bytes(key_dtype);
+  if (kb == 0) return TB200_ERR_UNSUPPORTED;
+  if (n == 0) return TB200_OK;
+  if (!h_keys || (val_bytes && !h_vals)) return TB200_ERR_INVALID_ARGUMENT;
+  size_t temp_bytes = 0;
+  int rc = tb200_radix_sort(nullptr, &temp_bytes, nullptr, nullptr, n, key_dtype, val_bytes, descending, 0,
+                            8 * kb, stream);
+  if (rc) return rc;
+  Carver size(nullptr);
+  size.take(temp_bytes);
+  size.take((size_t)n * kb);
+  size.take((size_t)n * val_bytes);
+  void* ws = nullptr;
+  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  if (rc) return rc;
+  Carver c(ws);
+  void* d_temp = c.take(temp_bytes);
+  void* d_keys = c.take((size_t)n * kb);
+  void* d_vals = c.take((size_t)n * val_bytes);
+  TB200_CUDA_TRY(cudaMemcpyAsync(d_keys, h_keys, (size_t)n * kb, cudaMemcpyHostToDevice, stream));
+  if (val_bytes)
+    TB200_CUDA_TRY(cudaMemcpyAsync(d_vals, h_vals, (size_t)n * val_bytes, cudaMemcpyHostToDevice, stream));
+  rc = tb200_radix_sort(d_temp, &temp_bytes, d_keys, val_bytes ? d_vals : nullptr, n, key_dtype, val_bytes,
+                        descending, 0, 8 * kb, stream);
+  if (rc) return rc;
+  TB200_CUDA_TRY(cudaMemcpyAsync(h_keys, d_keys, (size_t)n * kb, cudaMemcpyDeviceToHost, stream));
+  if (val_bytes)
+    TB200_CUDA_TRY(cudaMemcpyAsync(h_vals, d_vals, (size_t)n * val_bytes, cudaMemcpyDeviceToHost, stream));
+  return tb200_temp_status(d_temp, stream);
+}
+
+extern "C" int tb200_reduce_by_key_host(const void* h_keys_in, const void* h_vals_in, void* h_keys_out,
+                                        void* h_vals_out, uint64_t* h_num_runs, uint64_t n, int key_dtype,
+                                        int val_dtype, tb200_stream_t stream) {
+  using namespace tb200;
+  const int kb = dtype_bytes(key_dtype), vb = dtype_bytes(val_dtype);
+  if (kb == 0 || vb == 0) return TB200_ERR_UNSUPPORTED;
+  if (!h_num_runs) return TB200_ERR_INVALID_ARGUMENT;
+  *h_num_runs = 0;
+  if (n == 0) return TB200_OK;
+  if (!h_keys_in || !h_vals_in || !h_keys_out || !h_vals_out) return TB200_ERR_INVALID_ARGUMENT;
+  size_t temp_bytes = 0;
+  int rc = tb200_reduce_by_key(nullptr, &temp_bytes, nullptr, nullptr, nullptr, nullptr, nullptr, n,
+                               key_dtype, val_dtype, stream);
+  if (rc) return rc;
+  Carver size(nullptr);
+  size.take(temp_bytes);
+  size.take(256);
+  for (int i = 0; i < 2; ++i) { size.take((size_t)n * kb); size.take((size_t)n * vb); }
+  void* ws = nullptr;
+  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  if (rc) return rc;
+  Carver c(ws);
+  void* d_temp = c.take(temp_bytes);
+  auto* d_runs = static_cast<uint64_t*>(c.take(256));
+  void* d_kin = c.take((size_t)n * kb);
+  void* d_vin = c.take((size_t)n * vb);
+  void* d_kout = c.take((size_t)n * kb);
+  void* d_vout = c.take((size_t)n * vb);
+  TB200_CUDA_TRY(cudaMemcpyAsync(d_kin, h_keys_in, (size_t)n * kb, cudaMemcpyHostToDevice, stream));
+  TB200_CUDA_TRY(cudaMemcpyAsync(d_vin, h_vals_in, (size_t)n * vb, cudaMemcpyHostToDevice, stream));
+  rc = tb200_reduce_by_key(d_temp, &temp_bytes, d_kin, d_vin, d_kout, d_vout, d_runs, n, key_dtype,
+                           val_dtype, stream);
+  if (rc) return rc;
+  uint64_t runs = 0;
+  TB200_CUDA_TRY(cudaMemcpyAsync(&runs, d_runs, sizeof(runs), cudaMemcpyDeviceToHost, stream));
+  TB200_CUDA_TRY(cudaStreamSynchronize(stream));
+  TB200_CUDA_TRY(cudaMemcpyAsync(h_keys_out, d_kout, (size_t)runs * kb, cudaMemcpyDeviceToHost, stream));
+  TB200_CUDA_TRY(cudaMemcpyAsync(h_vals_out, d_vout, (size_t)runs * vb, cudaMemcpyDeviceToHost, stream));
+  *h_num_runs = runs;
+  return tb200_temp_status(d_temp, stream);
+}
