@@ -1,0 +1,200 @@
+"""Parity of tb200_radix_sort (through the C ABI) with the CPU oracle — bit exact.
+
+Mirrors the reference's sort tests: TestSortSimple / TestSortByKeySimple known answers
+(testing/sort.cu:42-76, testing/sort_by_key.cu:44-85), ascending and descending keys of every
+arithmetic type over many sizes (testing/sort.cu:80-134), stable sort_by_key with independent
+random values so that stability is observable (testing/stable_sort_by_key.cu:99-116), and keys
+masked to 0, 3, 6, ... bits, which makes whole digit passes constant
+(testing/sort_variable_bits.cu:18-43, testing/sort_by_key_variable_bits.cu:18-50).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import thrust_b200 as tb
+from thrust_b200 import _capi as capi
+from util import random_keys, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+ALL_TYPES = [np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.int64, np.uint64,
+             np.float32, np.float64, np.bool_]
+SIZES = [0, 1, 2, 3, 31, 32, 33, 255, 1000, 3071, 3072, 3073, 4095, 4096, 4097, 6143, 6144, 6145,
+         10027, 65537, 300007]
+
+
+@pytest.mark.parametrize("dtype", ALL_TYPES)
+def test_sort_keys_all_sizes(cuda_device, dtype):
+    chk = oracle.port()
+    for n in SIZES:
+        rng = np.random.default_rng(1000 + n)
+        k = random_keys(rng, n, dtype)
+        for desc in (False, True):
+            d = to_device(k)
+            tb.sort(d, descending=desc)
+            assert to_host(d, dtype).tobytes() == chk.sort(k, desc).tobytes(), (n, desc)
+
+
+@pytest.mark.parametrize("dtype", ALL_TYPES)
+def test_stable_sort_by_key_independent_values(cuda_device, dtype):
+    chk = oracle.port()
+    for n in [0, 1, 2, 33, 1000, 6145, 65537, 300007]:
+        rng = np.random.default_rng(2000 + n)
+        k = random_keys(rng, n, dtype)
+        v = rng.integers(0, 1 << 32, size=n, dtype=np.uint32)
+        for desc in (False, True):
+            dk, dv = to_device(k), to_device(v)
+            tb.sort_by_key(dk, dv, descending=desc)
+            wk, wv = chk.sort_by_key(k, v, desc)
+            assert to_host(dk, dtype).tobytes() == wk.tobytes(), (n, desc)
+            assert to_host(dv, np.uint32).tobytes() == wv.tobytes(), (n, desc, "values (stability)")
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.uint16, np.uint32, np.uint64])
+def test_sort_variable_bits(cuda_device, dtype):
+    chk = oracle.port()
+    n = 40009
+    for bits in range(0, 8 * np.dtype(dtype).itemsize, 3):
+        rng = np.random.default_rng(3000 + bits)
+        k = random_keys(rng, n, dtype, bits=bits)
+        d = to_device(k)
+        tb.sort(d)
+        assert to_host(d, dtype).tobytes() == np.sort(k).tobytes(), bits
+        dk, dv = to_device(k), to_device(np.arange(n, dtype=np.uint32))
+        tb.sort_by_key(dk, dv)
+        wk, wv = chk.sort_by_key(k, np.arange(n, dtype=np.uint32))
+        assert to_host(dk, dtype).tobytes() == wk.tobytes(), bits
+        assert to_host(dv, np.uint32).tobytes() == wv.tobytes(), bits
+
+
+@pytest.mark.parametrize("vdtype", [np.uint8, np.uint16, np.uint32, np.uint64])
+@pytest.mark.parametrize("kdtype", [np.int32, np.uint64, np.float32, np.int16])
+def test_sort_by_key_value_widths(cuda_device, kdtype, vdtype):
+    rng = np.random.default_rng(4000)
+    n = 50021
+    k = random_keys(rng, n, kdtype, bits=12)  # many duplicates
+    v = rng.integers(0, np.iinfo(vdtype).max, size=n, dtype=vdtype)
+    dk, dv = to_device(k), to_device(v)
+    tb.sort_by_key(dk, dv)
+    wk, wv = oracle.port().sort_by_key(k, v)
+    assert to_host(dk, kdtype).tobytes() == wk.tobytes()
+    assert to_host(dv, vdtype).tobytes() == wv.tobytes()
+
+
+def test_sort_by_key_16_byte_values(cuda_device):
+    rng = np.random.default_rng(4100)
+    n = 30011
+    k = random_keys(rng, n, np.uint32, bits=10)
+    v = rng.integers(0, 1 << 62, size=(n, 2), dtype=np.uint64)
+    dk = to_device(k)
+    dv = torch.from_numpy(v.view(np.int64)).to("cuda:0")
+    flat = dv.view(-1)
+    need = capi.C.c_size_t(0) if hasattr(capi, "C") else None
+    import ctypes as C
+    need = C.c_size_t(0)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    capi.check(capi.lib.tb200_radix_sort(None, C.byref(need), None, None, n, capi.U32, 16, 0, 0, 32, stream), "size")
+    temp = torch.empty(need.value, dtype=torch.uint8, device="cuda:0")
+    capi.check(capi.lib.tb200_radix_sort(C.c_void_p(temp.data_ptr()), C.byref(need), C.c_void_p(dk.data_ptr()),
+                                         C.c_void_p(flat.data_ptr()), n, capi.U32, 16, 0, 0, 32, stream), "run")
+    capi.check(capi.lib.tb200_temp_status(C.c_void_p(temp.data_ptr()), stream), "status")
+    order = np.argsort(k, kind="stable")
+    assert to_host(dk, np.uint32).tobytes() == k[order].tobytes()
+    assert dv.cpu().numpy().view(np.uint64).tobytes() == v[order].tobytes()
+
+
+@pytest.mark.parametrize("n", [(1 << 22) + 77, 1 << 24])
+def test_sort_many_tiles(cuda_device, n):
+    """Long look-back chains: thousands of tiles per pass."""
+    rng = np.random.default_rng(5000)
+    k = random_keys(rng, n, np.int32)
+    d = to_device(k)
+    tb.sort(d)
+    assert to_host(d, np.int32).tobytes() == np.sort(k).tobytes()
+    k64 = random_keys(rng, n // 4, np.uint64)
+    v = np.arange(n // 4, dtype=np.uint32)
+    dk, dv = to_device(k64), to_device(v)
+    tb.sort_by_key(dk, dv)
+    order = np.argsort(k64, kind="stable")
+    assert to_host(dk, np.uint64).tobytes() == k64[order].tobytes()
+    assert to_host(dv, np.uint32).tobytes() == v[order].astype(np.uint32).tobytes()
+
+
+def test_sort_low_entropy_and_float_specials(cuda_device):
+    rng = np.random.default_rng(6000)
+    n = 200003
+    chk = oracle.port()
+    # AND of three words: heavy duplicates, many zeros / subnormals, both signs of zero
+    bits = (rng.integers(0, 1 << 32, size=n, dtype=np.uint32) & rng.integers(0, 1 << 32, size=n, dtype=np.uint32)
+            & rng.integers(0, 1 << 32, size=n, dtype=np.uint32))
+    k = bits.view(np.float32).copy()
+    k[:8] = [0.0, -0.0, np.inf, -np.inf, np.nan, -np.nan, 1e-45, -1e-45]
+    v = np.arange(n, dtype=np.int32)
+    for desc in (False, True):
+        dk, dv = to_device(k), to_device(v)
+        tb.sort_by_key(dk, dv, descending=desc)
+        wk, wv = chk.sort_by_key(k, v, desc)
+        assert to_host(dk, np.float32).tobytes() == wk.tobytes()
+        assert to_host(dv, np.int32).tobytes() == wv.tobytes()
+    same = np.full(n, 42, dtype=np.int64)  # every pass is constant: nothing moves
+    dk, dv = to_device(same), to_device(v)
+    tb.sort_by_key(dk, dv)
+    assert to_host(dv, np.int32).tobytes() == v.tobytes()
+
+
+def test_sort_unaligned_pointers(cuda_device):
+    rng = np.random.default_rng(7000)
+    n = 70001
+    for kdtype in (np.int32, np.uint8, np.uint64):
+        k = random_keys(rng, n, kdtype)
+        v = rng.integers(0, 1 << 32, size=n, dtype=np.uint32)
+        dk, dv = to_device(k, offset_elems=1), to_device(v, offset_elems=3)
+        tb.sort_by_key(dk, dv)
+        wk, wv = oracle.port().sort_by_key(k, v)
+        assert to_host(dk, kdtype).tobytes() == wk.tobytes()
+        assert to_host(dv, np.uint32).tobytes() == wv.tobytes()
+
+
+def test_sort_bit_range(cuda_device):
+    rng = np.random.default_rng(8000)
+    n = 30011
+    k = random_keys(rng, n, np.uint32)
+    v = np.arange(n, dtype=np.uint32)
+    dk, dv = to_device(k), to_device(v)
+    tb.sort_by_key(dk, dv, begin_bit=4, end_bit=15)
+    order = np.argsort((k >> 4) & ((1 << 11) - 1), kind="stable")
+    assert to_host(dk, np.uint32).tobytes() == k[order].tobytes()
+    assert to_host(dv, np.uint32).tobytes() == v[order].tobytes()
+
+
+def test_sort_known_answers(cuda_device):
+    # testing/sort.cu:42-62 and testing/sort_by_key.cu:44-70
+    k = np.array([1, 3, 6, 5, 2, 0, 4], dtype=np.int32)
+    d = to_device(k)
+    tb.sort(d)
+    assert to_host(d, np.int32).tolist() == [0, 1, 2, 3, 4, 5, 6]
+    dk, dv = to_device(k), to_device(np.arange(7, dtype=np.int32))
+    tb.sort_by_key(dk, dv)
+    assert to_host(dk, np.int32).tolist() == [0, 1, 2, 3, 4, 5, 6]
+    assert to_host(dv, np.int32).tolist() == [5, 0, 4, 1, 6, 3, 2]
+    # greater<int>, n = 10027 (testing/sort.cu:92-110)
+    rng = np.random.default_rng(9)
+    k = rng.integers(-(1 << 31), 1 << 31, size=10027).astype(np.int32)
+    d = to_device(k)
+    tb.sort(d, descending=True)
+    assert to_host(d, np.int32).tobytes() == np.sort(k)[::-1].tobytes()
+
+
+def test_sort_rejects_bad_arguments(cuda_device):
+    import ctypes as C
+    need = C.c_size_t(0)
+    assert capi.lib.tb200_radix_sort(None, C.byref(need), None, None, 10, 99, 0, 0, 0, 32, None) == capi.ERR_UNSUPPORTED
+    assert capi.lib.tb200_radix_sort(None, C.byref(need), None, None, 10, capi.I32, 3, 0, 0, 32, None) == capi.ERR_UNSUPPORTED
+    assert capi.lib.tb200_radix_sort(None, C.byref(need), None, None, 10, capi.I32, 0, 0, 0, 40, None) == capi.ERR_INVALID_ARGUMENT
+    capi.check(capi.lib.tb200_radix_sort(None, C.byref(need), None, None, 1000, capi.I32, 0, 0, 0, 32, None), "size")
+    small = C.c_size_t(need.value - 1)
+    t = torch.empty(need.value, dtype=torch.uint8, device="cuda:0")
+    k = torch.zeros(1000, dtype=torch.int32, device="cuda:0")
+    assert capi.lib.tb200_radix_sort(C.c_void_p(t.data_ptr()), C.byref(small), C.c_void_p(k.data_ptr()), None, 1000,
+                                     capi.I32, 0, 0, 0, 32, None) == capi.ERR_TEMP_TOO_SMALL

@@ -21,7 +21,8 @@ ROOT = PKG.parent
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC,-O3", "-I", str(ROOT / "include"),
+    "--expt-relaxed-constexpr", "--extended-lambda", "-ccbin", "/usr/bin/g++",
+    "-Xcompiler", "-fPIC,-O3,-fopenmp", "-I", str(ROOT / "include"),
 ]
 
 
@@ -65,7 +66,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             list(ex.map(lambda s: _compile(s, verbose), todo))
     objs = [OBJ / (s.stem + ".o") for s in srcs]
     if todo or not LIB.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-ccbin", "/usr/bin/g++", "-lcudart", "-lgomp"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

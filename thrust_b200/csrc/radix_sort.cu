@@ -1,0 +1,603 @@
+// Onesweep LSD radix sort, 8-bit digits, written for sm_100a.
+//
+//   1. histogram_kernel   one read of the keys builds the digit histogram of EVERY
+//                         pass (shared-memory atomics, then 64-bit global atomics);
+//                         the last CTA to finish turns each histogram into exclusive
+//                         global digit offsets, marks passes in which one digit holds
+//                         all n keys as skipped, and fixes the ping-pong parity.
+//   2. onesweep_kernel    one launch per pass, 1 read + 1 write per element. A CTA
+//                         takes the next tile by atomic ticket, ranks its keys with
+//                         warp-level match (per-warp digit counters in shared memory),
+//                         publishes its 256 digit counts to a decoupled look-back
+//                         chain, resolves its global digit prefixes from predecessor
+//                         tiles, reorders keys (and values) through shared memory so
+//                         each digit leaves as one contiguous run, and scatters them.
+//   3. copy_back_kernel   only when an odd number of passes ran (result in the
+//                         alternate buffer); decided on the device, no host sync.
+//
+// Stability: inside a warp keys are ranked in (round, lane) order, which is their
+// order in memory (round j of lane l holds element j*32+l of the warp's slice);
+// warps, tiles and passes are combined in order. Equal keys therefore keep their
+// input order, which is what makes sort_by_key's values bit-exact.
+//
+// Key encoding (order-preserving map to unsigned, applied on the first executed
+// pass's load and undone on the last executed pass's store): signed -> flip the
+// sign bit; floating point -> flip all bits of negatives, the sign bit of the
+// rest (bitwise total order); descending -> complement.
+#include "common.cuh"
+
+#include <type_traits>
+
+#ifndef TB200_MATCH_MODE
+#define TB200_MATCH_MODE 0  // 0: match.any instruction, 1: eight ballots
+#endif
+
+namespace tb200 {
+namespace {
+
+constexpr int kRadix = 256;
+constexpr int kMaxPasses = 8;
+
+struct SortCtl {
+  int status;                    // must stay first: tb200_temp_status reads it
+  unsigned hist_done;            // CTAs of the histogram kernel that have finished
+  unsigned total_exec;           // number of passes that are not skipped
+  unsigned last_pass;            // index of the last executed pass
+  unsigned tickets[kMaxPasses];  // dynamic tile counters, one per pass
+  unsigned skip[kMaxPasses];
+  unsigned exec_before[kMaxPasses];  // executed passes before pass p (ping-pong parity)
+  unsigned long long hist[kMaxPasses][kRadix];
+  unsigned long long offs[kMaxPasses][kRadix];
+};
+
+struct Encoding {
+  unsigned long long cmask;  // constant xor (sign bit for signed and float keys)
+  unsigned long long fmask;  // all ones for floating point, else 0
+  unsigned long long dmask;  // all ones for descending, else 0
+};
+
+template <typename UK>
+__device__ __forceinline__ UK encode_key(UK x, const Encoding& e) {
+  using SK = typename std::make_signed<UK>::type;
+  const UK sra = (UK)((SK)x >> (8 * sizeof(UK) - 1));
+  return x ^ (UK)((sra & (UK)e.fmask) | (UK)e.cmask) ^ (UK)e.dmask;
+}
+template <typename UK>
+__device__ __forceinline__ UK decode_key(UK y, const Encoding& e) {
+  using SK = typename std::make_signed<UK>::type;
+  y ^= (UK)e.dmask;
+  const UK sra = (UK)((SK)y >> (8 * sizeof(UK) - 1));
+  return y ^ (UK)(((UK)~sra & (UK)e.fmask) | (UK)e.cmask);
+}
+
+template <typename UK>
+__device__ __forceinline__ unsigned digit_of(UK k, int shift, unsigned mask) {
+  return (unsigned)(k >> shift) & mask;
+}
+
+template <int BYTES> struct ValueOf;
+template <> struct ValueOf<1> { using type = uint8_t; };
+template <> struct ValueOf<2> { using type = uint16_t; };
+template <> struct ValueOf<4> { using type = uint32_t; };
+template <> struct ValueOf<8> { using type = unsigned long long; };
+template <> struct ValueOf<16> { using type = uint4; };
+template <> struct ValueOf<0> { using type = uint8_t; };  // unused
+
+// ---------------------------------------------------------------------------------
+// 1. upfront histogram of all passes
+// ---------------------------------------------------------------------------------
+constexpr int kHistThreads = 512;
+constexpr int kHistUnroll = 4;
+
+template <typename UK>
+struct alignas(16) KeyVec {
+  UK v[16 / sizeof(UK)];
+};
+
+template <typename UK>
+__global__ void __launch_bounds__(kHistThreads)
+histogram_kernel(const UK* __restrict__ keys, uint64_t n, int begin_bit, int end_bit, int num_passes,
+                 Encoding enc, SortCtl* ctl, int aligned) {
+  constexpr int P = sizeof(UK);
+  constexpr int VEC = 16 / sizeof(UK);
+  __shared__ unsigned s_hist[P][kRadix];
+  __shared__ unsigned s_last;
+  __shared__ unsigned long long s_warp_tot[8];
+
+  for (int i = threadIdx.x; i < P * kRadix; i += kHistThreads) (&s_hist[0][0])[i] = 0;
+  __syncthreads();
+
+  auto count = [&](UK raw) {
+    const UK k = encode_key(raw, enc);
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      if (p < num_passes) {
+        const int shift = begin_bit + 8 * p;
+        const int bits = min(8, end_bit - shift);
+        atomicAdd(&s_hist[p][digit_of(k, shift, (1u << bits) - 1u)], 1u);
+      }
+    }
+  };
+
+  constexpr uint64_t CHUNK = (uint64_t)kHistThreads * VEC * kHistUnroll;
+  const uint64_t full_chunks = aligned ? n / CHUNK : 0;
+  for (uint64_t c = blockIdx.x; c < full_chunks; c += gridDim.x) {
+    const KeyVec<UK>* src = reinterpret_cast<const KeyVec<UK>*>(keys + c * CHUNK);
+    KeyVec<UK> v[kHistUnroll];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u) v[u] = src[u * kHistThreads + threadIdx.x];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) count(v[u].v[j]);
+  }
+  // remainder (and everything, when the pointer is not 16-byte aligned)
+  for (uint64_t i = full_chunks * CHUNK + (uint64_t)blockIdx.x * kHistThreads + threadIdx.x; i < n;
+       i += (uint64_t)gridDim.x * kHistThreads)
+    count(keys[i]);
+  __syncthreads();
+
+  for (int i = threadIdx.x; i < num_passes * kRadix; i += kHistThreads) {
+    const unsigned c = (&s_hist[0][0])[i];
+    if (c) atomicAdd(&ctl->hist[0][0] + i, (unsigned long long)c);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&ctl->hist_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  // last CTA: exclusive offsets per pass, skip flags, ping-pong bookkeeping
+  unsigned exec = 0, last = 0;
+  for (int p = 0; p < num_passes; ++p) {
+    unsigned long long c = 0;
+    if (threadIdx.x < kRadix) c = ld_relaxed_u64(&ctl->hist[p][threadIdx.x]);
+    const int all_here = __syncthreads_or(threadIdx.x < kRadix && c == n);
+    // block-exclusive scan over the 256 digits (threads 0..255 = 8 warps)
+    unsigned long long s = c;
+    const unsigned lane = lane_id(), warp = threadIdx.x / kWarp;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long t = __shfl_up_sync(0xffffffffu, s, off);
+      if (lane >= off) s += t;
+    }
+    if (threadIdx.x < kRadix && lane == 31) s_warp_tot[warp] = s;
+    __syncthreads();
+    if (threadIdx.x < kRadix) {
+      unsigned long long base = 0;
+      for (unsigned w = 0; w < warp; ++w) base += s_warp_tot[w];
+      ctl->offs[p][threadIdx.x] = base + s - c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ctl->skip[p] = all_here ? 1u : 0u;
+      ctl->exec_before[p] = exec;
+    }
+    if (!all_here) { last = p; ++exec; }
+  }
+  if (threadIdx.x == 0) {
+    ctl->total_exec = exec;
+    ctl->last_pass = last;
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// 2. one onesweep pass
+// ---------------------------------------------------------------------------------
+struct PassParams {
+  void* keys_main;
+  void* keys_alt;
+  void* vals_main;
+  void* vals_alt;
+  uint64_t n;
+  unsigned num_tiles;
+  int pass;
+  int shift;
+  unsigned mask;
+  Encoding enc;
+  SortCtl* ctl;
+  void* desc;
+};
+
+template <typename DescT> struct DescBits;
+template <> struct DescBits<unsigned> {
+  static constexpr int kShift = 30;
+  static constexpr unsigned kValueMask = (1u << 30) - 1;
+};
+template <> struct DescBits<unsigned long long> {
+  static constexpr int kShift = 62;
+  static constexpr unsigned long long kValueMask = (1ull << 62) - 1;
+};
+
+template <typename DescT>
+__device__ __forceinline__ DescT ld_desc(const DescT* p) {
+  if constexpr (sizeof(DescT) == 4) return ld_relaxed_u32(p);
+  else return ld_relaxed_u64(p);
+}
+template <typename DescT>
+__device__ __forceinline__ void st_desc(DescT* p, DescT v) {
+  if constexpr (sizeof(DescT) == 4) st_relaxed_u32(p, v);
+  else st_relaxed_u64(p, v);
+}
+
+__device__ __forceinline__ unsigned match_digit(unsigned d) {
+#if TB200_MATCH_MODE == 0
+  return __match_any_sync(0xffffffffu, d);
+#else
+  unsigned peers = 0xffffffffu;
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const bool bit = (d >> b) & 1u;
+    const unsigned m = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? m : ~m;
+  }
+  return peers;
+#endif
+}
+
+template <typename UK, int VB, int THREADS, int ITEMS>
+struct PassShape {
+  using V = typename ValueOf<VB>::type;
+  static constexpr int kWarps = THREADS / kWarp;
+  static constexpr int kTile = THREADS * ITEMS;
+  static constexpr int kWarpItems = kWarp * ITEMS;
+  static constexpr size_t kKeysBytes = (size_t)kTile * sizeof(UK);
+  static constexpr size_t kValsBytes = VB ? align_up((size_t)kTile * VB, 16) : 0;
+  static constexpr size_t kWhistBytes = (size_t)kWarps * kRadix * sizeof(unsigned);
+  static constexpr size_t kSmem = align_up(kKeysBytes, 16) + kValsBytes + kWhistBytes;
+};
+
+template <typename UK, int VB, int THREADS, int ITEMS, typename DescT>
+__global__ void __launch_bounds__(THREADS)
+onesweep_kernel(const PassParams prm) {
+  using Shape = PassShape<UK, VB, THREADS, ITEMS>;
+  using V = typename Shape::V;
+  constexpr int WARPS = Shape::kWarps;
+  constexpr int TILE = Shape::kTile;
+  constexpr int DSH = DescBits<DescT>::kShift;
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  UK* s_keys = reinterpret_cast<UK*>(smem);
+  V* s_vals = reinterpret_cast<V*>(smem + align_up(Shape::kKeysBytes, 16));
+  unsigned* s_whist = reinterpret_cast<unsigned*>(smem + align_up(Shape::kKeysBytes, 16) + Shape::kValsBytes);
+  __shared__ unsigned long long s_gbase[kRadix];
+  __shared__ unsigned s_scan[kRadix / kWarp];
+  __shared__ unsigned s_tile;
+
+  SortCtl* ctl = prm.ctl;
+  const int pass = prm.pass;
+  if (ctl->skip[pass]) return;
+  const unsigned before = ctl->exec_before[pass];
+  const bool first_exec = before == 0;
+  const bool last_exec = ctl->last_pass == (unsigned)pass;
+  const bool from_alt = before & 1u;
+  const UK* src_keys = static_cast<const UK*>(from_alt ? prm.keys_alt : prm.keys_main);
+  UK* dst_keys = static_cast<UK*>(from_alt ? prm.keys_main : prm.keys_alt);
+  const V* src_vals = static_cast<const V*>(from_alt ? prm.vals_alt : prm.vals_main);
+  V* dst_vals = static_cast<V*>(from_alt ? prm.vals_main : prm.vals_alt);
+  // descriptor states rotate with the parity of executed passes, so the chain
+  // needs zeroing only once per sort: after a pass every entry reads kPrefix of
+  // that pass, which is kEmpty of the next one.
+  const unsigned st_empty = (2u * (before & 1u)) & 3u;
+  const unsigned st_agg = (st_empty + 1u) & 3u;
+  const unsigned st_prefix = (st_empty + 2u) & 3u;
+
+  if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->tickets[pass], 1u);
+  for (int i = threadIdx.x; i < WARPS * kRadix; i += THREADS) s_whist[i] = 0;
+  __syncthreads();
+  const unsigned tile = s_tile;
+  const unsigned warp = threadIdx.x / kWarp;
+  const unsigned lane = lane_id();
+  const uint64_t tile_base = (uint64_t)tile * TILE;
+  const uint64_t remaining = prm.n - tile_base;
+  const unsigned tile_valid = remaining < (uint64_t)TILE ? (unsigned)remaining : (unsigned)TILE;
+  const unsigned warp_off = warp * Shape::kWarpItems;
+  const int shift = prm.shift;
+  const unsigned mask = prm.mask;
+
+  // ---- load (warp-striped: round j of lane l is element j*32+l of the warp's slice)
+  UK key[ITEMS];
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const unsigned local = warp_off + j * kWarp + lane;
+    UK k = (UK)~(UK)0;  // padding sorts to the end of the tile
+    if (local < tile_valid) {
+      k = src_keys[tile_base + local];
+      if (first_exec) k = encode_key(k, prm.enc);
+    }
+    key[j] = k;
+  }
+
+  // ---- rank inside the warp
+  unsigned* whist = s_whist + warp * kRadix;
+  unsigned short rank[ITEMS];
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const unsigned d = digit_of(key[j], shift, mask);
+    const unsigned peers = match_digit(d);
+    const unsigned leader = __ffs(peers) - 1;
+    unsigned old = 0;
+    if (lane == leader) {
+      old = whist[d];
+      whist[d] = old + __popc(peers);
+    }
+    old = __shfl_sync(0xffffffffu, old, leader);
+    rank[j] = (unsigned short)(old + __popc(peers & lanemask_lt()));
+    __syncwarp();
+  }
+  __syncthreads();
+
+  // ---- per-digit tile totals, warp offsets, look-back (thread d owns digit d)
+  unsigned count = 0;
+  if (threadIdx.x < kRadix) {
+    const unsigned d = threadIdx.x;
+#pragma unroll 4
+    for (int w = 0; w < WARPS; ++w) {
+      const unsigned c = s_whist[w * kRadix + d];
+      s_whist[w * kRadix + d] = count;
+      count += c;
+    }
+    if (d == mask) count -= (unsigned)TILE - tile_valid;  // padding carries the largest digit
+    DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
+    if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
+    else           st_desc<DescT>(mine, ((DescT)st_agg << DSH) | count);
+  }
+  // exclusive scan of the 256 tile totals -> first slot of each digit in the sorted tile
+  unsigned incl = count;
+  if (threadIdx.x < kRadix) {
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    if (lane == 31) s_scan[warp] = incl;
+  }
+  __syncthreads();
+  if (threadIdx.x < kRadix) {
+    const unsigned d = threadIdx.x;
+    unsigned digit_start = incl - count;
+    for (unsigned w = 0; w < warp; ++w) digit_start += s_scan[w];
+#pragma unroll 4
+    for (int w = 0; w < WARPS; ++w) s_whist[w * kRadix + d] += digit_start;
+
+    unsigned long long excl = 0;
+    if (tile != 0) {
+      const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
+      long long t = (long long)tile - 1;
+      bool timed_out = false;
+      while (true) {
+        DescT v;
+        unsigned polls = 0;
+        while ((unsigned)((v = ld_desc<DescT>(chain + (size_t)t * kRadix)) >> DSH) == st_empty) {
+          backoff(++polls);
+          if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
+            timed_out = true;
+            break;
+          }
+        }
+        if (timed_out) break;
+        excl += (unsigned long long)(v & DescBits<DescT>::kValueMask);
+        if ((unsigned)(v >> DSH) == st_prefix) break;
+        --t;
+      }
+      if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
+      DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
+      st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + count) & DescBits<DescT>::kValueMask));
+    }
+    s_gbase[d] = ctl->offs[pass][d] + excl - digit_start;
+  }
+  __syncthreads();
+
+  // ---- reorder keys through shared memory
+  unsigned short slot[ITEMS];
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const unsigned d = digit_of(key[j], shift, mask);
+    const unsigned q = whist[d] + rank[j];
+    slot[j] = (unsigned short)q;
+    s_keys[q] = key[j];
+  }
+  V val[VB ? ITEMS : 1];
+  if constexpr (VB != 0) {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+      const unsigned local = warp_off + j * kWarp + lane;
+      if (local < tile_valid) val[j] = src_vals[tile_base + local];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const unsigned pos = threadIdx.x + i * THREADS;
+    if (pos < tile_valid) {
+      const UK k = s_keys[pos];
+      const unsigned d = digit_of(k, shift, mask);
+      dst_keys[s_gbase[d] + pos] = last_exec ? decode_key(k, prm.enc) : k;
+    }
+  }
+  if constexpr (VB != 0) {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) s_vals[slot[j]] = val[j];
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const unsigned pos = threadIdx.x + i * THREADS;
+      if (pos < tile_valid) {
+        const unsigned d = digit_of(s_keys[pos], shift, mask);
+        dst_vals[s_gbase[d] + pos] = s_vals[pos];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// 3. copy back when the result ended in the alternate buffer
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+copy_back_kernel(uint4* __restrict__ keys_main, const uint4* __restrict__ keys_alt, uint64_t key_bytes,
+                 uint4* __restrict__ vals_main, const uint4* __restrict__ vals_alt, uint64_t val_bytes,
+                 const SortCtl* ctl) {
+  if ((ctl->total_exec & 1u) == 0) return;
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // both buffers are at least 16-byte aligned only when the caller's are; copy the
+  // bulk as bytes if not. The alternate buffer is always 256-byte aligned.
+  auto copy = [&](uint4* dst, const uint4* src, uint64_t bytes) {
+    if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      const uint64_t nvec = bytes / 16;
+      for (uint64_t i = tid; i < nvec; i += stride) dst[i] = src[i];
+      unsigned char* d8 = reinterpret_cast<unsigned char*>(dst);
+      const unsigned char* s8 = reinterpret_cast<const unsigned char*>(src);
+      for (uint64_t i = nvec * 16 + tid; i < bytes; i += stride) d8[i] = s8[i];
+    } else {
+      unsigned char* d8 = reinterpret_cast<unsigned char*>(dst);
+      const unsigned char* s8 = reinterpret_cast<const unsigned char*>(src);
+      for (uint64_t i = tid; i < bytes; i += stride) d8[i] = s8[i];
+    }
+  };
+  copy(keys_main, keys_alt, key_bytes);
+  if (val_bytes) copy(vals_main, vals_alt, val_bytes);
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+template <typename UK, int VB>
+struct Tuning {
+  // threads x items per thread of one onesweep tile
+  static constexpr int kThreads = 512;
+  static constexpr int kItems = sizeof(UK) == 8 ? (VB >= 8 ? 6 : 8) : (VB == 16 ? 6 : (VB == 8 ? 8 : 12));
+};
+
+struct Layout {
+  size_t ctl_off, desc_off, keys_off, vals_off, total, clear_bytes;
+};
+
+inline Layout make_layout(uint64_t n, int key_bytes, int val_bytes, uint64_t tiles, size_t desc_elem) {
+  Layout l;
+  l.ctl_off = 0;
+  l.desc_off = align_up(sizeof(SortCtl), 256);
+  l.clear_bytes = l.desc_off + align_up((size_t)tiles * kRadix * desc_elem, 256);
+  l.keys_off = l.clear_bytes;
+  l.vals_off = l.keys_off + align_up((size_t)n * key_bytes, 256);
+  l.total = l.vals_off + align_up((size_t)n * val_bytes, 256);
+  return l;
+}
+
+template <typename UK, int VB>
+int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n, int kind,
+              int descending, int begin_bit, int end_bit, cudaStream_t stream) {
+  using T = Tuning<UK, VB>;
+  using Shape = PassShape<UK, VB, T::kThreads, T::kItems>;
+  constexpr uint64_t TILE = Shape::kTile;
+  const uint64_t tiles = (n + TILE - 1) / TILE;
+  const bool wide = n > (1ull << 30);
+  const Layout lay = make_layout(n, sizeof(UK), VB, tiles, wide ? 8 : 4);
+  if (d_temp == nullptr) {
+    *temp_bytes = lay.total;
+    return TB200_OK;
+  }
+  if (*temp_bytes < lay.total) return TB200_ERR_TEMP_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(d_temp) % 256) return TB200_ERR_INVALID_ARGUMENT;
+  if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
+  char* base = static_cast<char*>(d_temp);
+  auto* ctl = reinterpret_cast<SortCtl*>(base + lay.ctl_off);
+  if (n <= 1 || begin_bit >= end_bit) {
+    TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, sizeof(int), stream));
+    return TB200_OK;
+  }
+  if (d_keys == nullptr || (VB && d_vals == nullptr)) return TB200_ERR_INVALID_ARGUMENT;
+  TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
+
+  Encoding enc;
+  const unsigned long long sign = 1ull << (8 * sizeof(UK) - 1);
+  enc.cmask = kind == 0 ? 0ull : sign;
+  enc.fmask = kind == 2 ? ~0ull : 0ull;
+  enc.dmask = descending ? ~0ull : 0ull;
+  const int num_passes = (end_bit - begin_bit + 7) / 8;
+
+  int dev = 0, sms = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+  {
+    const uint64_t chunk = (uint64_t)kHistThreads * (16 / sizeof(UK)) * kHistUnroll;
+    const uint64_t want = (n + chunk - 1) / chunk;
+    const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
+    const int aligned = reinterpret_cast<uintptr_t>(d_keys) % 16 == 0;
+    histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n, begin_bit,
+                                                            end_bit, num_passes, enc, ctl, aligned);
+    TB200_CUDA_TRY(cudaGetLastError());
+  }
+
+  PassParams prm;
+  prm.keys_main = d_keys;
+  prm.keys_alt = base + lay.keys_off;
+  prm.vals_main = d_vals;
+  prm.vals_alt = base + lay.vals_off;
+  prm.n = n;
+  prm.num_tiles = (unsigned)tiles;
+  prm.enc = enc;
+  prm.ctl = ctl;
+  prm.desc = base + lay.desc_off;
+  auto launch = [&](auto kernel) -> int {
+    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
+    for (int p = 0; p < num_passes; ++p) {
+      prm.pass = p;
+      prm.shift = begin_bit + 8 * p;
+      const int bits = end_bit - prm.shift < 8 ? end_bit - prm.shift : 8;
+      prm.mask = (1u << bits) - 1u;
+      kernel<<<(unsigned)tiles, T::kThreads, Shape::kSmem, stream>>>(prm);
+      TB200_CUDA_TRY(cudaGetLastError());
+    }
+    return TB200_OK;
+  };
+  int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, unsigned long long>)
+                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, unsigned>);
+  if (rc) return rc;
+
+  copy_back_kernel<<<sms * 4, 256, 0, stream>>>(
+      static_cast<uint4*>(d_keys), reinterpret_cast<const uint4*>(base + lay.keys_off), n * sizeof(UK),
+      static_cast<uint4*>(d_vals), reinterpret_cast<const uint4*>(base + lay.vals_off), n * (uint64_t)VB, ctl);
+  return (int)cudaGetLastError();
+}
+
+template <typename UK>
+int sort_vals(int val_bytes, void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n, int kind,
+              int descending, int begin_bit, int end_bit, cudaStream_t stream) {
+  switch (val_bytes) {
+    case 0: return sort_impl<UK, 0>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 1: return sort_impl<UK, 1>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 2: return sort_impl<UK, 2>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 4: return sort_impl<UK, 4>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 8: return sort_impl<UK, 8>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 16: return sort_impl<UK, 16>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    default: return TB200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_radix_sort(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n,
+                                int key_dtype, int val_bytes, int descending, int begin_bit, int end_bit,
+                                tb200_stream_t stream) {
+  using namespace tb200;
+  if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  const int kb = dtype_bytes(key_dtype);
+  if (kb == 0) return TB200_ERR_UNSUPPORTED;
+  if (begin_bit < 0 || end_bit > 8 * kb || begin_bit > end_bit) return TB200_ERR_INVALID_ARGUMENT;
+  int kind = 0;  // 0 unsigned / bool, 1 signed, 2 floating point
+  switch (key_dtype) {
+    case TB200_I8: case TB200_I16: case TB200_I32: case TB200_I64: kind = 1; break;
+    case TB200_F32: case TB200_F64: kind = 2; break;
+    default: kind = 0;
+  }
+  switch (kb) {
+    case 1: return sort_vals<uint8_t>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 2: return sort_vals<uint16_t>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 4: return sort_vals<uint32_t>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    default: return sort_vals<unsigned long long>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+  }
+}
