@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the thrust_b200 hot path.
+
+Headline (one JSON line, rank 0): the sharded stable sort_by_key of (uint64 key,
+uint32 value = global index) pairs, 2^30 pairs per GPU, seed 2024 — a plain local
+onesweep sort at --gpus 1, the sample sort over NCCL at --gpus 2/4/8 (weak scaling).
+`value` is G keys/s of the whole job with inputs resident in HBM; `e2e` is the same
+sort through the host-buffer entry point with the H2D / D2H copies inside the timed
+region. At --gpus 1 the line also carries `others`: the remaining single-GPU
+configurations (int32 sort, float32 / int64 scan, reduce_by_key, (u64,u32) and
+(f32,i32) sort_by_key, sort-based histogram), each with its roofline fraction.
+
+`--impl reference` times the reference's own CPU implementation (Thrust 2.2.0 built
+with its OMP device system, oracle/_ref) on a bounded sample of the same workload.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up steps, inputs (12 GiB per
+GPU) far larger than L2, input restored by a device copy outside the timed events,
+max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+PER_GPU_LOG2 = 30
+SEED = 2024
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def __enter__(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.file is None:
+            return out
+        try:
+            self.file.flush()
+            rows = [r.split(",") for r in Path(self.file.name).read_text().strip().splitlines() if r.count(",") >= 6]
+            os.unlink(self.file.name)
+        except Exception:
+            return out
+        sm, reasons = [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                out["sm_max_mhz"] = float(r[1])
+            except ValueError:
+                continue
+            for name, cell in zip(names, r[3:7]):
+                if cell.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            busy = [x for x in sm if x >= 0.5 * max(sm)] or sm
+            out["sm_mhz"] = statistics.median(busy)
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+def traffic_per_pair():
+    """DRAM bytes per pair and per pass of the onesweep kernel from the committed ncu summary."""
+    p = ROOT / "profiles" / "onesweep_traffic.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["dram_bytes_per_pair_per_pass"])
+        except Exception:
+            return None
+    return None
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's OMP device system on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_sort_sample(log2_n: int, reps: int, warmup: int):
+    import numpy as np
+    import oracle
+    from thrust_b200 import datagen as g
+    if oracle.have_ref("omp"):
+        chk, kind = oracle.ref("omp"), "reference"
+    else:
+        chk, kind = oracle.port(), "port"
+        log2_n = min(log2_n, 22)
+    n = 1 << log2_n
+    keys0 = g.host(g.BITS_U64, n, SEED)
+    vals0 = g.host(g.INDEX_U32, n, SEED)
+    times = []
+    for i in range(warmup + reps):
+        k, v = keys0.copy(), vals0.copy()
+        t = time.perf_counter()
+        chk.sort_by_key_inplace(k, v)
+        dt = time.perf_counter() - t
+        if i >= warmup:
+            times.append(dt)
+    assert bool(np.all(k[1:] >= k[:-1]))
+    sec = sum(times) / len(times)
+    return {
+        "value": n / sec / 1e9, "unit": "Gkeys/s", "cores": chk.threads, "kind": kind,
+        "sample": f"stable sort_by_key of 2^{log2_n} (uint64 key, uint32 index) pairs, seed {SEED}, "
+                  f"Thrust 2.2.0 {'OMP device system' if kind == 'reference' else 'algorithm restated in C'}, "
+                  f"mean of {len(times)} runs",
+    }, sec
+
+
+def run_reference(args, rank: int):
+    if rank != 0:
+        return
+    base, sec = cpu_sort_sample(25, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "sort_by_key_throughput", "value": base["value"], "unit": "Gkeys/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "Gkeys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {
+        "workload": f"sharded stable sort_by_key, 2^{PER_GPU_LOG2} (uint64 key, uint32 value=global index) pairs per GPU, "
+                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: local sort, regular-sample splitters, NCCL all-to-all, final local sort'}",
+        "pairs_per_gpu": 1 << PER_GPU_LOG2, "total_pairs": n_gpus << PER_GPU_LOG2,
+        "l2_policy": "inputs (12 GiB per GPU) larger than L2; input restored by a device copy between steps",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def time_calls(fn, restore, steps: int, warmup: int, stream):
+    """Per-step CUDA-event times (ms) of fn() with restore() run outside the events."""
+    import torch
+    out = []
+    for i in range(warmup + steps):
+        restore()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        b.synchronize()
+        if i >= warmup:
+            out.append(a.elapsed_time(b))
+    return out
+
+
+def bench_others(dev, peak):
+    """The remaining single-GPU configurations; each entry carries its own roofline fraction."""
+    import torch
+    import thrust_b200 as tb
+    from thrust_b200 import _capi as capi, datagen as g
+    res = {}
+    stream = torch.cuda.current_stream(dev)
+
+    def entry(name, fn, restore, units, unit_name, bytes_model, note, steps=10):
+        try:
+            ms = time_calls(fn, restore, steps, 3, stream)
+            best, med = min(ms), statistics.median(ms)
+            res[name] = {
+                "value": units / (med * 1e-3) / 1e9, "unit": unit_name, "ms_median": med, "ms_min": best,
+                "algorithmic_GBps": bytes_model / (med * 1e-3) / 1e9,
+                "frac_of_hbm_peak": bytes_model / (med * 1e-3) / 1e9 / peak, "bytes_model": note,
+            }
+        except Exception as e:  # keep the headline even if a side configuration fails
+            res[name] = {"error": repr(e)}
+        torch.cuda.empty_cache()
+
+    # C1: sort of 2^25 int32 keys (working set 128 MiB, partly L2 resident)
+    n = 1 << 25
+    k0 = g.sort_i32(n, dev)
+    k = k0.clone()
+    temp = torch.empty(n * 4 + (64 << 20), dtype=torch.uint8, device=dev)
+    entry("sort_i32_2^25", lambda: tb.sort(k, sync=False, temp=temp), lambda: k.copy_(k0), n, "Gkeys/s", 48.0 * n,
+          "4 passes x (2 reads + 1 write) x 4 B = 48 B/key")
+    del k, k0, temp
+
+    # C2: scans over 2^30 elements
+    n = 1 << 30
+    x = g.scan_f32(n, dev)
+    y = torch.empty_like(x)
+    temp = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    entry("inclusive_scan_f32_2^30", lambda: tb.inclusive_scan(x, out=y, sync=False, temp=temp), lambda: None,
+          n, "Gelem/s", 8.0 * n, "1 read + 1 write x 4 B = 8 B/element")
+    del x, y
+    x = g.scan_i64(n, dev)
+    y = torch.empty_like(x)
+    entry("inclusive_scan_i64_2^30", lambda: tb.inclusive_scan(x, out=y, sync=False, temp=temp), lambda: None,
+          n, "Gelem/s", 16.0 * n, "1 read + 1 write x 8 B = 16 B/element")
+    del x, y
+
+    # C2: reduce_by_key over 2^28 grouped keys, mean run 16
+    n = 1 << 28
+    keys, vals = g.rbk_inputs(n, dev)
+    ko, vo = torch.empty_like(keys), torch.empty_like(vals)
+    runs = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = C.c_void_p(stream.cuda_stream)
+    have = C.c_size_t(temp.numel())
+
+    def rbk():
+        capi.check(capi.lib.tb200_reduce_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
+            C.c_void_p(ko.data_ptr()), C.c_void_p(vo.data_ptr()), C.c_void_p(runs.data_ptr()), n, capi.I32, capi.F32,
+            st), "tb200_reduce_by_key")
+    rbk()
+    nruns = int(runs.item())
+    entry("reduce_by_key_i32_f32_2^28", rbk, lambda: None, n, "Gelem/s", 8.0 * (n + nruns),
+          f"(n + runs) x (4 B key + 4 B value), runs = {nruns}")
+    del keys, vals, ko, vo
+
+    # C3: stable sort_by_key of 2^28 (uint64, uint32) pairs
+    k0, v0 = g.pairs_u64_u32(n, g.SEED_PAIRS_U64, 0, dev)
+    k, v = k0.clone(), v0.clone()
+    temp = torch.empty(n * 12 + (128 << 20), dtype=torch.uint8, device=dev)
+    entry("sort_by_key_u64_u32_2^28", lambda: tb.sort_by_key(k, v, key_dtype=capi.U64, sync=False, temp=temp),
+          lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 256.0 * n,
+          "8 passes x (3 x 8 B key + 2 x 4 B value) = 256 B/pair")
+    del k, v, k0, v0
+
+    # C4: (float32, int32) pairs, low entropy
+    k0, v0 = g.and3_pairs(n, dev)
+    k, v = k0.clone(), v0.clone()
+    entry("sort_by_key_f32_i32_and3_2^28", lambda: tb.sort_by_key(k, v, sync=False, temp=temp),
+          lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 80.0 * n,
+          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair")
+    del k0, v0
+    k0, v0, table = g.zipf_pairs(n, dev)
+    entry("sort_by_key_f32_i32_zipf_2^28", lambda: tb.sort_by_key(k, v, sync=False, temp=temp),
+          lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 80.0 * n,
+          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair")
+
+    def hist():
+        tb.sort(k, sync=False, temp=temp)
+        tb.histogram_sorted(k, table, sync=False)
+    entry("dense_histogram_zipf_f32_65536_bins_2^28", hist, lambda: k.copy_(k0), n, "Gkeys/s", 48.0 * n,
+          "keys-only sort: 4 passes x 12 B = 48 B/key (search + difference touch < 1 MB)")
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--log2-per-gpu", type=int, default=PER_GPU_LOG2, help="for quick checks only")
+    ap.add_argument("--no-others", action="store_true", help="skip the side configurations at --gpus 1")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import thrust_b200 as tb
+    from thrust_b200 import _capi as capi, datagen as g, sample_sort as ss
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: thrust_b200 has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    peak, peak_kind = measured_peak()
+    n = 1 << args.log2_per_gpu
+    stream = torch.cuda.current_stream(dev)
+
+    sorter = ss.ShardedSorter(n, dev, world_size=world, rank=rank, seed=SEED)
+    k0, v0 = g.pairs_u64_u32(n, SEED, rank * n, dev)
+    k, v = torch.empty_like(k0), torch.empty_like(v0)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    step_ms, trace_ms = [], []
+    ms_buf = (C.c_float * 64)()
+    for i in range(args.warmup):
+        k.copy_(k0); v.copy_(v0)
+        sorter.sort(k, v)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        for i in range(args.steps):
+            k.copy_(k0); v.copy_(v0)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if world > 1:
+                dist.barrier()
+            capi.lib.tb200_trace_begin(C.c_void_p(stream.cuda_stream))
+            a.record(stream)
+            out_k, out_v, out_n = sorter.sort(k, v)
+            b.record(stream)
+            b.synchronize()
+            cnt = capi.lib.tb200_trace_end(ms_buf, 64)
+            step_ms.append(a.elapsed_time(b))
+            trace_ms.append([ms_buf[j] for j in range(max(cnt, 0))])
+        barrier()
+    sorter.check_status()
+    ok = sorter.verify(out_k, out_v, out_n)
+
+    t = torch.tensor(step_ms, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms = t.tolist()
+    ms_per_step = sum(step_ms) / len(step_ms)
+    total_pairs = n * world
+    value = total_pairs / (ms_per_step * 1e-3) / 1e9
+
+    # dominant kernel: one onesweep pass over the local shard. The first local sort of a
+    # step launches histogram, 8 passes, copy-back, so launches 1..8 are the passes.
+    pass_ms = [x for tr in trace_ms for x in tr[1:9]]
+    avg_pass = sum(pass_ms) / max(len(pass_ms), 1)
+    pass_bytes = n * 2.0 * (8 + 4)
+    achieved = pass_bytes / (avg_pass * 1e-3) / 1e9 if avg_pass > 0 else 0.0
+    tpp = traffic_per_pair()
+    roofline = {
+        "bound": "hbm", "kernel": "onesweep_kernel<u64 key, 4-byte value>", "achieved": achieved, "peak": peak,
+        "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+        "traffic": None if tpp is None else tpp * n, "algorithmic_bytes_per_launch": pass_bytes,
+        "avg_launch_ms": avg_pass, "launches_timed": len(pass_ms),
+        "whole_sort_3touch": {
+            "bytes_per_pair": 256, "model": "8 passes x (2 reads + 1 write of an 8 B key, 1 read + 1 write of a 4 B value)",
+            "achieved": (256.0 * n) / (sum(sum(tr[:10]) for tr in trace_ms) / max(len(trace_ms), 1) * 1e-3) / 1e9
+            if trace_ms and trace_ms[0] else None,
+        },
+    }
+    if roofline["whole_sort_3touch"]["achieved"]:
+        roofline["whole_sort_3touch"]["frac"] = roofline["whole_sort_3touch"]["achieved"] / peak
+    launches = sum(len(tr) for tr in trace_ms)
+
+    del k0, v0, k, v, out_k, out_v
+    sorter.release()
+    torch.cuda.empty_cache()
+
+    e2e = None
+    if not args.no_e2e:
+        e2e = ss.bench_host_path(n, dev, world, rank, SEED, steps=min(args.steps, 3), warmup=1)
+
+    line = {
+        "metric": "sort_by_key_throughput", "value": value, "unit": "Gkeys/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u64", "data": "synthetic", "config": workload_config(world),
+        "verified": bool(ok), "clocks": clocks.summary(), "roofline": roofline, "gpu_launches": launches,
+        "e2e": e2e,
+    }
+    if rank == 0 and world == 1:
+        if not args.no_cpu:
+            line["cpu_baseline"], _ = cpu_sort_sample(25, 3, 1)
+        if not args.no_others:
+            line["others"] = bench_others(dev, peak)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -103,6 +103,17 @@ int tb200_histogram_sorted(const void* d_sorted, uint64_t n, int dtype, const vo
  * (thrust/system/cuda/detail/util.h:113-140, 251-299). */
 int tb200_temp_status(const void* d_temp, tb200_stream_t stream);
 
+/* ---- launch tracing -------------------------------------------------------------------
+ * Plays the role of the reference's THRUST_DEBUG_SYNC launch log
+ * (thrust/system/cuda/detail/core/agent_launcher.h:501-560) without a sync per launch:
+ * between tb200_trace_begin and tb200_trace_end every kernel this library launches from
+ * the calling thread is followed by an event record on its stream. tb200_trace_end
+ * synchronises, writes the device time of launch i (milliseconds) to ms[i] for
+ * i < capacity and returns the number of launches (negative: -cudaError_t). Sort
+ * launches are, in order: histogram, one per radix pass, copy-back. */
+int tb200_trace_begin(tb200_stream_t stream);
+int tb200_trace_end(float* ms, int capacity);
+
 /* ---- workspace pool -----------------------------------------------------------------
  * The reference allocates and frees scratch with cudaMalloc/cudaFree inside every call
  * (thrust/system/cuda/detail/malloc_and_free.h:53-118). The pool keeps one grow-only

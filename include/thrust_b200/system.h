@@ -1,0 +1,316 @@
+// thrust_b200::system — a Thrust custom system (in the style of the reference's
+// examples/minimal_custom_backend.cu:17-37) that routes sort / stable_sort /
+// sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / reduce_by_key
+// on contiguous arithmetic data to the sm_100a kernels behind the C ABI of
+// thrust_b200.h, and everything else to the CUDA system it derives from.
+//
+//   thrust::sort(thrust_b200::par, v.begin(), v.end());
+//   thrust::inclusive_scan(thrust_b200::par.on(stream), in, in + n, out);
+//   thrust::reduce_by_key(thrust_b200::par_nosync.on(stream), ...);   // still syncs for the count
+//
+// The thrust:: signatures and the execution-policy API are untouched: dispatch reaches
+// the overloads below by ADL on the policy type (thrust/detail/sort.inl:30-38,
+// scan.inl:36-43, reduce.inl:125-136). Every arity is overloaded because the CUDA
+// system forwards its default-argument forms with QUALIFIED calls
+// (thrust/system/cuda/detail/sort.h:585-623, scan.h:256-349, reduce_by_key.h:1149-1200),
+// which would bypass a system that only overloads the full form.
+//
+// Fast-path rule (same as the reference's, thrust/system/cuda/detail/sort.h:389-407,
+// 431-484): contiguous iterators, arithmetic keys, comparator exactly thrust::less /
+// thrust::greater; scans and reduce_by_key additionally need plus / equal_to and one
+// 4- or 8-byte numeric type for input, output and accumulator. Anything else is
+// forwarded to thrust::cuda::par.on(stream) — the inherited GPU path, never a CPU one.
+//
+// Requires C++17 and the toolkit's Thrust headers (CCCL); link with libthrust_b200.so.
+#pragma once
+
+#include <thrust/execution_policy.h>
+#include <thrust/functional.h>
+#include <thrust/iterator/iterator_traits.h>
+#include <thrust/memory.h>
+#include <thrust/pair.h>
+#include <thrust/reduce.h>
+#include <thrust/scan.h>
+#include <thrust/sort.h>
+#include <thrust/system/cuda/error.h>
+#include <thrust/system/cuda/execution_policy.h>
+#include <thrust/system/system_error.h>
+#include <thrust/type_traits/is_contiguous_iterator.h>
+
+#include <atomic>
+#include <cstdint>
+#include <new>
+#include <string>
+#include <type_traits>
+
+#include "../thrust_b200.h"
+
+namespace thrust_b200 {
+
+// The policy object. Like the reference's policies it is passed by reference through
+// dispatch and never copied by the algorithms (testing/unittest/special_types.h:135-168).
+struct system : thrust::device_execution_policy<system> {
+  cudaStream_t stream = nullptr;  // legacy default stream, like thrust::cuda::par
+  bool sync = true;               // false: par_nosync semantics (cuda/detail/par.h:100-107)
+
+  constexpr system() = default;
+  constexpr system(cudaStream_t s, bool sy) : stream(s), sync(sy) {}
+  // par.on(stream), cf. thrust/system/cuda/detail/par.h:45-70
+  system on(cudaStream_t s) const { return system(s, sync); }
+};
+
+inline constexpr system par{};
+inline constexpr system par_nosync{nullptr, false};
+
+namespace detail {
+
+// Calls that took the sm_100a path / were forwarded to the inherited CUDA path
+// (tests use these the way the reference's dispatch tests use `is_valid`).
+inline std::atomic<unsigned long long>& fast_calls() { static std::atomic<unsigned long long> c{0}; return c; }
+inline std::atomic<unsigned long long>& forwarded_calls() { static std::atomic<unsigned long long> c{0}; return c; }
+
+inline void throw_on_error(int code, const char* what) {
+  if (code == 0) return;
+  const std::string msg = std::string(what) + ": " + tb200_error_string(code);
+  // cudaError_t codes keep their value; library codes are reported as cudaErrorUnknown
+  // with the library's message (thrust/system/cuda/detail/util.h:251-299).
+  throw thrust::system_error(code > 0 ? code : (int)cudaErrorUnknown, thrust::cuda_category(), msg);
+}
+
+inline void* workspace(size_t bytes, cudaStream_t stream) {
+  void* p = nullptr;
+  const int rc = tb200_workspace_acquire(bytes, stream, &p);
+  if (rc == (int)cudaErrorMemoryAllocation) throw std::bad_alloc();  // malloc_and_free.h:77-82
+  throw_on_error(rc, "tb200_workspace_acquire");
+  return p;
+}
+
+inline void finish(const system& s, const void* temp, const char* what) {
+  if (s.sync) throw_on_error(tb200_temp_status(temp, s.stream), what);
+}
+
+template <typename T> struct is_plain_arithmetic
+    : std::integral_constant<bool, std::is_arithmetic<T>::value && !std::is_same<T, long double>::value> {};
+
+template <typename T> constexpr int dtype_of() {
+  if (std::is_same<T, bool>::value) return TB200_BOOL;
+  if (std::is_floating_point<T>::value) return sizeof(T) == 4 ? TB200_F32 : TB200_F64;
+  switch (sizeof(T)) {
+    case 1: return std::is_signed<T>::value ? TB200_I8 : TB200_U8;
+    case 2: return std::is_signed<T>::value ? TB200_I16 : TB200_U16;
+    case 4: return std::is_signed<T>::value ? TB200_I32 : TB200_U32;
+    default: return std::is_signed<T>::value ? TB200_I64 : TB200_U64;
+  }
+}
+
+template <typename T> struct is_scan_type
+    : std::integral_constant<bool, is_plain_arithmetic<T>::value && !std::is_same<T, bool>::value &&
+                                       (sizeof(T) == 4 || sizeof(T) == 8)> {};
+
+template <typename It> using value_t = typename thrust::iterator_traits<It>::value_type;
+template <typename It> constexpr bool contiguous_v = thrust::is_contiguous_iterator<It>::value;
+
+template <typename It> auto raw(It it) { return thrust::raw_pointer_cast(&*it); }
+
+template <typename C, typename K> struct order_of { static constexpr int value = -1; };
+template <typename K> struct order_of<thrust::less<K>, K> { static constexpr int value = 0; };
+template <typename K> struct order_of<thrust::greater<K>, K> { static constexpr int value = 1; };
+template <typename K> struct order_of<thrust::less<void>, K> { static constexpr int value = 0; };
+template <typename K> struct order_of<thrust::greater<void>, K> { static constexpr int value = 1; };
+
+template <typename Op, typename T> struct is_plus : std::false_type {};
+template <typename T> struct is_plus<thrust::plus<T>, T> : std::true_type {};
+template <typename T> struct is_plus<thrust::plus<void>, T> : std::true_type {};
+template <typename Op, typename T> struct is_equal_to : std::false_type {};
+template <typename T> struct is_equal_to<thrust::equal_to<T>, T> : std::true_type {};
+template <typename T> struct is_equal_to<thrust::equal_to<void>, T> : std::true_type {};
+
+template <int N> struct is_value_size : std::integral_constant<bool, N == 1 || N == 2 || N == 4 || N == 8 || N == 16> {};
+
+inline auto inherited(const system& s) { return thrust::cuda::par.on(s.stream); }
+
+template <typename KeyIt, typename Compare>
+constexpr bool sort_fast_v = contiguous_v<KeyIt> && is_plain_arithmetic<value_t<KeyIt>>::value &&
+                             order_of<Compare, value_t<KeyIt>>::value >= 0;
+
+template <typename KeyIt, typename ValIt, typename Compare>
+void sort_pairs(system& s, KeyIt kf, KeyIt kl, ValIt vf, Compare comp, bool has_values) {
+  using K = value_t<KeyIt>;
+  const uint64_t n = (uint64_t)(kl - kf);
+  int vb = 0;
+  void* vptr = nullptr;
+  if constexpr (!std::is_same<ValIt, std::nullptr_t>::value) {
+    if (has_values) { vb = (int)sizeof(value_t<ValIt>); vptr = (void*)raw(vf); }
+  }
+  (void)comp;
+  const int desc = order_of<Compare, K>::value;
+  size_t bytes = 0;
+  throw_on_error(tb200_radix_sort(nullptr, &bytes, nullptr, nullptr, n, dtype_of<K>(), vb, desc, 0, 8 * (int)sizeof(K),
+                                  s.stream), "tb200_radix_sort");
+  void* temp = workspace(bytes, s.stream);
+  throw_on_error(tb200_radix_sort(temp, &bytes, n ? (void*)raw(kf) : nullptr, vptr, n, dtype_of<K>(), vb, desc, 0,
+                                  8 * (int)sizeof(K), s.stream), "tb200_radix_sort");
+  ++fast_calls();
+  finish(s, temp, "tb200_radix_sort");
+}
+
+}  // namespace detail
+
+// ---- sort / stable_sort (replaces cuda_cub::sort, stable_sort: cuda/detail/sort.h:493-532, 585-603)
+template <typename It, typename Compare>
+void stable_sort(system& s, It first, It last, Compare comp) {
+  if constexpr (detail::sort_fast_v<It, Compare>) {
+    detail::sort_pairs(s, first, last, nullptr, comp, false);
+  } else {
+    ++detail::forwarded_calls();
+    thrust::stable_sort(detail::inherited(s), first, last, comp);
+  }
+}
+template <typename It>
+void stable_sort(system& s, It first, It last) {
+  stable_sort(s, first, last, thrust::less<detail::value_t<It>>());
+}
+// On the radix path the reference's sort is its stable_sort (sort.h:431-484); elsewhere
+// the unstable form is forwarded as such.
+template <typename It, typename Compare>
+void sort(system& s, It first, It last, Compare comp) {
+  if constexpr (detail::sort_fast_v<It, Compare>) {
+    detail::sort_pairs(s, first, last, nullptr, comp, false);
+  } else {
+    ++detail::forwarded_calls();
+    thrust::sort(detail::inherited(s), first, last, comp);
+  }
+}
+template <typename It>
+void sort(system& s, It first, It last) {
+  sort(s, first, last, thrust::less<detail::value_t<It>>());
+}
+
+// ---- sort_by_key / stable_sort_by_key (cuda/detail/sort.h:534-581, 605-623)
+template <typename KeyIt, typename ValIt, typename Compare>
+void stable_sort_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, Compare comp) {
+  using V = detail::value_t<ValIt>;
+  if constexpr (detail::sort_fast_v<KeyIt, Compare> && detail::contiguous_v<ValIt> &&
+                std::is_trivially_copyable<V>::value && detail::is_value_size<(int)sizeof(V)>::value) {
+    detail::sort_pairs(s, kf, kl, vf, comp, true);
+  } else {
+    ++detail::forwarded_calls();
+    thrust::stable_sort_by_key(detail::inherited(s), kf, kl, vf, comp);
+  }
+}
+template <typename KeyIt, typename ValIt>
+void stable_sort_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf) {
+  stable_sort_by_key(s, kf, kl, vf, thrust::less<detail::value_t<KeyIt>>());
+}
+template <typename KeyIt, typename ValIt, typename Compare>
+void sort_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, Compare comp) {
+  using V = detail::value_t<ValIt>;
+  if constexpr (detail::sort_fast_v<KeyIt, Compare> && detail::contiguous_v<ValIt> &&
+                std::is_trivially_copyable<V>::value && detail::is_value_size<(int)sizeof(V)>::value) {
+    detail::sort_pairs(s, kf, kl, vf, comp, true);
+  } else {
+    ++detail::forwarded_calls();
+    thrust::sort_by_key(detail::inherited(s), kf, kl, vf, comp);
+  }
+}
+template <typename KeyIt, typename ValIt>
+void sort_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf) {
+  sort_by_key(s, kf, kl, vf, thrust::less<detail::value_t<KeyIt>>());
+}
+
+// ---- scans (cuda/detail/scan.h:213-349) ------------------------------------------------
+namespace detail {
+template <typename InIt, typename OutIt, typename T>
+OutIt scan_fast(system& s, InIt first, InIt last, OutIt result, bool exclusive, const T* init) {
+  const uint64_t n = (uint64_t)(last - first);
+  size_t bytes = 0;
+  throw_on_error(tb200_scan(nullptr, &bytes, nullptr, nullptr, n, dtype_of<T>(), exclusive, init, s.stream), "tb200_scan");
+  void* temp = workspace(bytes, s.stream);
+  throw_on_error(tb200_scan(temp, &bytes, n ? (const void*)raw(first) : nullptr, n ? (void*)raw(result) : nullptr, n,
+                            dtype_of<T>(), exclusive, init, s.stream), "tb200_scan");
+  ++fast_calls();
+  finish(s, temp, "tb200_scan");
+  return result + (last - first);
+}
+template <typename InIt, typename OutIt, typename Acc, typename Op>
+constexpr bool scan_fast_v = contiguous_v<InIt> && contiguous_v<OutIt> && is_scan_type<Acc>::value &&
+                             std::is_same<value_t<InIt>, Acc>::value && std::is_same<value_t<OutIt>, Acc>::value &&
+                             is_plus<Op, Acc>::value;
+}  // namespace detail
+
+template <typename InIt, typename OutIt, typename Op>
+OutIt inclusive_scan(system& s, InIt first, InIt last, OutIt result, Op op) {
+  using T = detail::value_t<InIt>;  // accumulator = input value type (scan.h:63)
+  if constexpr (detail::scan_fast_v<InIt, OutIt, T, Op>) {
+    return detail::scan_fast<InIt, OutIt, T>(s, first, last, result, false, nullptr);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::inclusive_scan(detail::inherited(s), first, last, result, op);
+  }
+}
+template <typename InIt, typename OutIt>
+OutIt inclusive_scan(system& s, InIt first, InIt last, OutIt result) {
+  return inclusive_scan(s, first, last, result, thrust::plus<>{});
+}
+template <typename InIt, typename OutIt, typename Init, typename Op>
+OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result, Init init, Op op) {
+  if constexpr (detail::scan_fast_v<InIt, OutIt, Init, Op>) {  // accumulator = type of init (scan.h:142-154)
+    return detail::scan_fast<InIt, OutIt, Init>(s, first, last, result, true, &init);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::exclusive_scan(detail::inherited(s), first, last, result, init, op);
+  }
+}
+template <typename InIt, typename OutIt, typename Init>
+OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result, Init init) {
+  return exclusive_scan(s, first, last, result, init, thrust::plus<>{});
+}
+template <typename InIt, typename OutIt>
+OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result) {
+  return exclusive_scan(s, first, last, result, detail::value_t<InIt>{});  // scan.h:340-349
+}
+
+// ---- reduce_by_key (cuda/detail/reduce_by_key.h:1118-1200) --------------------------------
+template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut, typename Pred, typename Op>
+thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo, Pred pred,
+                                           Op op) {
+  using K = detail::value_t<KeyIt>;
+  using V = detail::value_t<ValIt>;
+  if constexpr (detail::contiguous_v<KeyIt> && detail::contiguous_v<ValIt> && detail::contiguous_v<KeyOut> &&
+                detail::contiguous_v<ValOut> && detail::is_plain_arithmetic<K>::value &&
+                detail::is_scan_type<V>::value && std::is_same<detail::value_t<KeyOut>, K>::value &&
+                std::is_same<detail::value_t<ValOut>, V>::value && detail::is_equal_to<Pred, K>::value &&
+                detail::is_plus<Op, V>::value) {
+    const uint64_t n = (uint64_t)(kl - kf);
+    if (n == 0) return thrust::make_pair(ko, vo);
+    size_t bytes = 0;
+    detail::throw_on_error(tb200_reduce_by_key(nullptr, &bytes, nullptr, nullptr, nullptr, nullptr, nullptr, n,
+                                               detail::dtype_of<K>(), detail::dtype_of<V>(), s.stream),
+                           "tb200_reduce_by_key");
+    char* ws = static_cast<char*>(detail::workspace(bytes + 256, s.stream));
+    auto* d_runs = reinterpret_cast<uint64_t*>(ws + ((bytes + 255) / 256) * 256);
+    detail::throw_on_error(tb200_reduce_by_key(ws, &bytes, detail::raw(kf), detail::raw(vf), detail::raw(ko),
+                                               detail::raw(vo), d_runs, n, detail::dtype_of<K>(),
+                                               detail::dtype_of<V>(), s.stream), "tb200_reduce_by_key");
+    ++detail::fast_calls();
+    // the end iterators need the run count: synchronise, like the reference (reduce_by_key.h:1049-1052)
+    uint64_t runs = 0;
+    detail::throw_on_error((int)cudaMemcpyAsync(&runs, d_runs, sizeof(runs), cudaMemcpyDeviceToHost, s.stream),
+                           "reduce_by_key: run count");
+    detail::throw_on_error(tb200_temp_status(ws, s.stream), "tb200_reduce_by_key");
+    return thrust::make_pair(ko + runs, vo + runs);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::reduce_by_key(detail::inherited(s), kf, kl, vf, ko, vo, pred, op);
+  }
+}
+template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut, typename Pred>
+thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo, Pred pred) {
+  return reduce_by_key(s, kf, kl, vf, ko, vo, pred, thrust::plus<detail::value_t<ValIt>>());
+}
+template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut>
+thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo) {
+  return reduce_by_key(s, kf, kl, vf, ko, vo, thrust::equal_to<detail::value_t<KeyIt>>());
+}
+
+}  // namespace thrust_b200

@@ -33,6 +33,16 @@ typedef enum tb200_gen_kind {
 int tb200_datagen(void* out, uint64_t n, uint64_t first_index, int kind, uint64_t seed, const void* aux,
                   uint32_t aux_len, int on_device, tb200_stream_t stream);
 
+/* Reference-free check of one sorted shard of (key = hash(seed, g), value = (uint32)g) pairs
+ * drawn from global indices g in [0, total). d_result4 (device, 4 x uint64) receives:
+ * [0] order violations (key[j-1] > key[j], or equal keys whose global indices do not increase),
+ * [1] pairs whose key is not the hash of any index congruent to the value mod 2^32,
+ * [2] the sum of the recovered global indices mod 2^64, [3] the number of pairs checked.
+ * Zero violations on every shard, ordered shard boundaries and [3] summing to `total`
+ * imply that the output is THE stable sort of the input. */
+int tb200_check_hashed_pairs(const void* d_keys, const void* d_vals, uint64_t n, uint64_t seed, uint64_t total,
+                             uint64_t* d_result4, tb200_stream_t stream);
+
 /* hash(seed, i) itself, for checkers. */
 uint64_t tb200_datagen_hash(uint64_t seed, uint64_t i);
 

@@ -41,6 +41,11 @@ __host__ inline int dtype_bytes(int dt) {
   }
 }
 
+// Launch tracing (tb200_trace_begin / tb200_trace_end): when the calling thread has
+// tracing on, every kernel launch of the library is followed by an event record, so
+// a benchmark can read per-launch device times without a profiler. Off by default.
+void trace_mark(cudaStream_t stream);
+
 #define TB200_CUDA_TRY(expr)                       \
   do {                                             \
     cudaError_t _e = (expr);                       \

@@ -76,8 +76,63 @@ __host__ __device__ inline void gen_one(void* out, uint64_t j, uint64_t i, int k
   }
 }
 
+// Reference-free check of a sorted shard of (hash key, index value) pairs.
+// result[0] order violations, [1] pairing violations, [2] sum of recovered global
+// indices (mod 2^64), [3] number of pairs checked.
+__global__ void check_pairs_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ vals, uint64_t n,
+                                   uint64_t seed, uint64_t total, unsigned long long* __restrict__ result) {
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const unsigned wraps = (unsigned)((total + 0xffffffffull) >> 32);
+  auto recover = [&](uint64_t key, uint32_t v, bool& found) {
+    found = false;
+    for (unsigned c = 0; c < wraps; ++c) {
+      const uint64_t gidx = ((uint64_t)c << 32) | v;
+      if (gidx < total && hash64(seed, gidx) == key) { found = true; return gidx; }
+    }
+    return (uint64_t)0;
+  };
+  unsigned long long bad_order = 0, bad_pair = 0, sum = 0, cnt = 0;
+  for (uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += stride) {
+    const uint64_t k = keys[j];
+    bool found;
+    const uint64_t gi = recover(k, vals[j], found);
+    if (!found) ++bad_pair;
+    sum += gi;
+    ++cnt;
+    if (j > 0) {
+      const uint64_t kp = keys[j - 1];
+      if (kp > k) ++bad_order;
+      else if (kp == k) {
+        bool fp;
+        const uint64_t gp = recover(kp, vals[j - 1], fp);
+        if (fp && found && !(gp < gi)) ++bad_order;
+      }
+    }
+  }
+  if (bad_order) atomicAdd(&result[0], bad_order);
+  if (bad_pair) atomicAdd(&result[1], bad_pair);
+  atomicAdd(&result[2], sum);
+  atomicAdd(&result[3], cnt);
+}
+
 }  // namespace
 }  // namespace tb200
+
+extern "C" int tb200_check_hashed_pairs(const void* d_keys, const void* d_vals, uint64_t n, uint64_t seed,
+                                        uint64_t total, uint64_t* d_result4, tb200_stream_t stream) {
+  using namespace tb200;
+  if (!d_result4) return TB200_ERR_INVALID_ARGUMENT;
+  TB200_CUDA_TRY(cudaMemsetAsync(d_result4, 0, 4 * sizeof(uint64_t), stream));
+  if (n == 0) return TB200_OK;
+  if (!d_keys || !d_vals) return TB200_ERR_INVALID_ARGUMENT;
+  int dev = 0, sms = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  check_pairs_kernel<<<sms * 8, 256, 0, stream>>>(static_cast<const uint64_t*>(d_keys),
+                                                  static_cast<const uint32_t*>(d_vals), n, seed, total,
+                                                  reinterpret_cast<unsigned long long*>(d_result4));
+  return (int)cudaGetLastError();
+}
 
 extern "C" uint64_t tb200_datagen_hash(uint64_t seed, uint64_t i) { return tb200::hash64(seed, i); }
 

@@ -528,6 +528,7 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
     const int aligned = reinterpret_cast<uintptr_t>(d_keys) % 16 == 0;
     histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n, begin_bit,
                                                             end_bit, num_passes, enc, ctl, aligned);
+    trace_mark(stream);
     TB200_CUDA_TRY(cudaGetLastError());
   }
 
@@ -549,6 +550,7 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
       const int bits = end_bit - prm.shift < 8 ? end_bit - prm.shift : 8;
       prm.mask = (1u << bits) - 1u;
       kernel<<<(unsigned)tiles, T::kThreads, Shape::kSmem, stream>>>(prm);
+      trace_mark(stream);
       TB200_CUDA_TRY(cudaGetLastError());
     }
     return TB200_OK;
@@ -560,6 +562,7 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   copy_back_kernel<<<sms * 4, 256, 0, stream>>>(
       static_cast<uint4*>(d_keys), reinterpret_cast<const uint4*>(base + lay.keys_off), n * sizeof(UK),
       static_cast<uint4*>(d_vals), reinterpret_cast<const uint4*>(base + lay.vals_off), n * (uint64_t)VB, ctl);
+  trace_mark(stream);
   return (int)cudaGetLastError();
 }
 

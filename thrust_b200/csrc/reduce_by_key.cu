@@ -295,6 +295,7 @@ int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
     reduce_by_key_kernel<K, V, false><<<grid, block, 0, stream>>>(
         static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout), static_cast<V*>(vout), nr,
         n, (unsigned)tiles, hdr, desc);
+  trace_mark(stream);
   return (int)cudaGetLastError();
 }
 

@@ -5,6 +5,7 @@
 #include <map>
 #include <mutex>
 #include <utility>
+#include <vector>
 
 namespace tb200 {
 namespace {
@@ -29,8 +30,43 @@ struct Carver {
   }
 };
 
+thread_local bool t_trace_on = false;
+thread_local std::vector<cudaEvent_t> t_trace_events;
+
 }  // namespace
+
+void trace_mark(cudaStream_t stream) {
+  if (!t_trace_on) return;
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, stream);
+  t_trace_events.push_back(e);
+}
+
 }  // namespace tb200
+
+extern "C" int tb200_trace_begin(tb200_stream_t stream) {
+  using namespace tb200;
+  for (cudaEvent_t e : t_trace_events) cudaEventDestroy(e);
+  t_trace_events.clear();
+  t_trace_on = true;
+  trace_mark(stream);
+  return TB200_OK;
+}
+
+extern "C" int tb200_trace_end(float* ms, int capacity) {
+  using namespace tb200;
+  t_trace_on = false;
+  if (t_trace_events.empty()) return 0;
+  cudaError_t err = cudaEventSynchronize(t_trace_events.back());
+  if (err != cudaSuccess) return -(int)err;
+  const int launches = (int)t_trace_events.size() - 1;
+  for (int i = 0; i < launches && i < capacity; ++i)
+    cudaEventElapsedTime(&ms[i], t_trace_events[i], t_trace_events[i + 1]);
+  for (cudaEvent_t e : t_trace_events) cudaEventDestroy(e);
+  t_trace_events.clear();
+  return launches;
+}
 
 extern "C" int tb200_version(void) { return 100; }
 

@@ -246,6 +246,7 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
     if (aligned) scan_kernel<T, false, true><<<grid, block, 0, stream>>>(in, out, n, init, hdr, desc);
     else         scan_kernel<T, false, false><<<grid, block, 0, stream>>>(in, out, n, init, hdr, desc);
   }
+  trace_mark(stream);
   return (int)cudaGetLastError();
 }
 

@@ -1,0 +1,250 @@
+"""Sharded stable sort_by_key across the GPUs of one node: a sample sort.
+
+The reference has no multi-GPU code at all; this is the sharded form of its
+``stable_sort_by_key`` on (uint64 key, uint32 value) pairs, one process per GPU:
+
+  1. local onesweep sort of the shard                        (tb200_radix_sort)
+  2. regular sample: ``samples_per_rank`` keys at fixed ranks of the sorted shard
+  3. all-gather the samples; every rank sorts them identically and takes the keys
+     at ranks samples_per_rank * r (r = 1..G-1) as splitters
+  4. destination d owns keys in (splitter[d-1], splitter[d]]: the send segments are
+     contiguous ranges of the sorted shard, found with one upper-bound search per
+     splitter (tb200_histogram_sorted) — no data movement
+  5. all-to-all of the G x G count matrix, then all-to-all-v of keys and of values
+     over NCCL; received runs are stored in source-rank order
+  6. one more local sort of the received pairs. Rank r holds global indices
+     [r*n, (r+1)*n), so a stable sort of runs concatenated in source-rank order
+     reproduces the single-process stable order.
+
+The collectives go through ``torch.distributed`` (NCCL on GPUs). The per-shard
+compute goes through an ``ops`` object; the default ``DeviceOps`` calls the CUDA
+library and there is no CPU implementation in this package (tests inject one to
+exercise the orchestration over gloo).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import time
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+SAMPLES_PER_RANK = 1024
+
+
+class DeviceOps:
+    """Per-shard steps on the GPU through the C ABI."""
+
+    def __init__(self, device: torch.device, capacity: int):
+        from . import _capi as capi
+        self.capi = capi
+        self.device = device
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_radix_sort(None, C.byref(need), None, None, capacity, capi.U64, 4, 0, 0, 64, None),
+                   "tb200_radix_sort(size)")
+        self.temp = torch.empty(need.value, dtype=torch.uint8, device=device)
+        self.small_temp = torch.empty(8 << 20, dtype=torch.uint8, device=device)
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def sort_pairs(self, keys: torch.Tensor, vals: torch.Tensor, n: int) -> None:
+        capi = self.capi
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_radix_sort(C.c_void_p(self.temp.data_ptr()), C.byref(have),
+                                             C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), n, capi.U64, 4,
+                                             0, 0, 64, self._stream()), "tb200_radix_sort")
+
+    def sort_keys(self, keys: torch.Tensor) -> None:
+        capi = self.capi
+        have = C.c_size_t(self.small_temp.numel())
+        capi.check(capi.lib.tb200_radix_sort(C.c_void_p(self.small_temp.data_ptr()), C.byref(have),
+                                             C.c_void_p(keys.data_ptr()), None, keys.numel(), capi.U64, 0, 0, 0, 64,
+                                             self._stream()), "tb200_radix_sort(samples)")
+
+    def segment_counts(self, sorted_keys: torch.Tensor, n: int, splitters: torch.Tensor) -> torch.Tensor:
+        """counts[d] = keys in (splitter[d-1], splitter[d]] for d < G-1 (uint64 order), int64 tensor of G-1."""
+        capi = self.capi
+        counts = torch.empty(splitters.numel(), dtype=torch.int32, device=self.device)
+        capi.check(capi.lib.tb200_histogram_sorted(C.c_void_p(sorted_keys.data_ptr()), n, capi.U64,
+                                                   C.c_void_p(splitters.data_ptr()), splitters.numel(),
+                                                   C.c_void_p(counts.data_ptr()), self._stream()),
+                   "tb200_histogram_sorted")
+        return counts.to(torch.int64) & 0xFFFFFFFF
+
+    def status(self) -> int:
+        return int(self.capi.lib.tb200_temp_status(C.c_void_p(self.temp.data_ptr()), self._stream()))
+
+    def release(self) -> None:
+        self.temp = None
+        self.small_temp = None
+
+
+def sample_positions(n: int, samples: int) -> torch.Tensor:
+    """Ranks of the regular sample inside a sorted shard of n keys (mid-points of equal strides)."""
+    s = min(samples, n)
+    if s == 0:
+        return torch.empty(0, dtype=torch.int64)
+    idx = (2 * torch.arange(s, dtype=torch.int64) + 1) * n // (2 * s)
+    return idx.clamp_(max=n - 1)
+
+
+def pick_splitters(sorted_samples: torch.Tensor, world: int) -> torch.Tensor:
+    """G-1 splitters: the keys at ranks (len/G)*r of the sorted gathered sample."""
+    m = sorted_samples.numel()
+    pos = (torch.arange(1, world, dtype=torch.int64) * m) // world
+    return sorted_samples[pos.to(sorted_samples.device)]
+
+
+class ShardedSorter:
+    """Sorts one shard per rank; after ``sort`` rank r holds the r-th slice of the global order."""
+
+    def __init__(self, n: int, device: torch.device, world_size: int = 1, rank: int = 0, seed: int = 0,
+                 ops=None, group=None, slack: float = 1.0 / 64):
+        self.n, self.device, self.world, self.rank, self.seed = n, device, world_size, rank, seed
+        self.group = group
+        self.capacity = n if world_size == 1 else n + int(n * slack) + SAMPLES_PER_RANK
+        if ops is None:
+            if device.type != "cuda":
+                raise RuntimeError("thrust_b200 has no CPU path: ShardedSorter needs a CUDA device")
+            ops = DeviceOps(device, self.capacity)
+        self.ops = ops
+        self.recv_k = self.recv_v = None
+        if world_size > 1:
+            self.recv_k = torch.empty(self.capacity, dtype=torch.int64, device=device)
+            self.recv_v = torch.empty(self.capacity, dtype=torch.int32, device=device)
+        self.last_counts = None
+
+    def release(self) -> None:
+        self.ops.release()
+        self.recv_k = self.recv_v = None
+
+    def check_status(self) -> None:
+        st = self.ops.status()
+        if st != 0:
+            raise RuntimeError(f"device status {st} after sharded sort")
+
+    def sort(self, keys: torch.Tensor, vals: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, int]:
+        """keys: int64 tensor holding uint64 bit patterns, vals: int32 tensor holding uint32.
+        Returns (keys, vals, count): this rank's slice of the globally sorted sequence."""
+        n, G = self.n, self.world
+        self.ops.sort_pairs(keys, vals, n)
+        if G == 1:
+            return keys, vals, n
+        # 2-3. regular sample -> splitters (identical on every rank)
+        pos = sample_positions(n, SAMPLES_PER_RANK).to(self.device)
+        mine = keys[pos].contiguous()
+        gathered = torch.empty(G * mine.numel(), dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(gathered, mine, group=self.group)
+        self.ops.sort_keys(gathered)
+        splitters = pick_splitters(gathered, G).contiguous()
+        # 4. contiguous send segments of the sorted shard
+        head = self.ops.segment_counts(keys, n, splitters)
+        send = torch.cat([head, (n - head.sum()).reshape(1)])
+        # 5. counts, then payload
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        both = torch.stack([send, recv]).cpu()
+        send_l, recv_l = both[0].tolist(), both[1].tolist()
+        m = int(sum(recv_l))
+        self.last_counts = (send_l, recv_l)
+        if m > self.capacity:
+            raise OverflowError(f"rank {self.rank}: {m} incoming pairs exceed the receive capacity {self.capacity}")
+        dist.all_to_all_single(self.recv_k[:m], keys[:n], recv_l, send_l, group=self.group)
+        dist.all_to_all_single(self.recv_v[:m], vals[:n], recv_l, send_l, group=self.group)
+        # 6. stable sort of the runs (already in source-rank order)
+        self.ops.sort_pairs(self.recv_k, self.recv_v, m)
+        return self.recv_k, self.recv_v, m
+
+    # ---- reference-free verification (needs the CUDA library) ------------------------------
+    def verify(self, out_k: torch.Tensor, out_v: torch.Tensor, m: int) -> bool:
+        """True when the distributed output is the stable sort of keys hash(seed, g), g in [0, G*n)."""
+        from . import _capi as capi
+        lib = capi.lib
+        lib.tb200_check_hashed_pairs.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64,
+                                                 C.c_void_p, C.c_void_p]
+        lib.tb200_check_hashed_pairs.restype = C.c_int
+        total = self.n * self.world
+        res = torch.zeros(4, dtype=torch.int64, device=self.device)
+        stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        capi.check(lib.tb200_check_hashed_pairs(C.c_void_p(out_k.data_ptr()), C.c_void_p(out_v.data_ptr()), m,
+                                                self.seed, total, C.c_void_p(res.data_ptr()), stream), "check")
+        edge = torch.zeros(4, dtype=torch.int64, device=self.device)  # first key, first value, last key, last value
+        if m > 0:
+            edge[0], edge[1] = out_k[0], out_v[0].to(torch.int64) & 0xFFFFFFFF
+            edge[2], edge[3] = out_k[m - 1], out_v[m - 1].to(torch.int64) & 0xFFFFFFFF
+        ok = True
+        if self.world > 1:
+            dist.all_reduce(res, group=self.group)
+            edges = torch.empty(4 * self.world, dtype=torch.int64, device=self.device)
+            dist.all_gather_into_tensor(edges, edge, group=self.group)
+            e = edges.cpu().view(self.world, 4).tolist()
+            for r in range(self.world - 1):
+                lo = e[r][2] & 0xFFFFFFFFFFFFFFFF
+                hi = e[r + 1][0] & 0xFFFFFFFFFFFFFFFF
+                ok = ok and lo <= hi
+        r4 = [x & 0xFFFFFFFFFFFFFFFF for x in res.cpu().tolist()]
+        want_sum = (total * (total - 1) // 2) & 0xFFFFFFFFFFFFFFFF
+        return ok and r4[0] == 0 and r4[1] == 0 and r4[2] == want_sum and r4[3] == total
+
+
+def bench_host_path(n: int, device: torch.device, world: int, rank: int, seed: int, steps: int = 3,
+                    warmup: int = 1) -> Optional[dict]:
+    """End-to-end timing with HOST buffers: pinned host -> device, sort, device -> pinned host, all inside
+    the timed region. One GPU: the C entry point tb200_radix_sort_host. Several GPUs: copies around
+    ShardedSorter.sort. Returns the ``e2e`` object of the benchmark line (None if host memory is short)."""
+    from . import _capi as capi, datagen as g
+    try:
+        hk = torch.empty(n, dtype=torch.int64).pin_memory()
+        hv = torch.empty(n, dtype=torch.int32).pin_memory()
+        if world > 1:
+            cap = n + n // 64 + SAMPLES_PER_RANK
+            ok_, ov_ = torch.empty(cap, dtype=torch.int64).pin_memory(), torch.empty(cap, dtype=torch.int32).pin_memory()
+    except RuntimeError:
+        return None
+    stream = torch.cuda.current_stream(device)
+    st = C.c_void_p(stream.cuda_stream)
+    sorter = dk = dv = None
+    if world > 1:
+        sorter = ShardedSorter(n, device, world, rank, seed)
+        dk = torch.empty(n, dtype=torch.int64, device=device)
+        dv = torch.empty(n, dtype=torch.int32, device=device)
+    times, d2h = [], 0
+    for i in range(warmup + steps):
+        g.host(g.BITS_U64, n, seed, rank * n, out=hk.numpy().view("uint64"))
+        g.host(g.INDEX_U32, n, seed, rank * n, out=hv.numpy().view("uint32"))
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        if world == 1:
+            capi.check(capi.lib.tb200_radix_sort_host(C.c_void_p(hk.data_ptr()), C.c_void_p(hv.data_ptr()), n,
+                                                      capi.U64, 4, 0, st), "tb200_radix_sort_host")
+            d2h = n * 12
+        else:
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            rk, rv, m = sorter.sort(dk, dv)
+            ok_[:m].copy_(rk[:m], non_blocking=True)
+            ov_[:m].copy_(rv[:m], non_blocking=True)
+            d2h = m * 12
+        b.record(stream)
+        b.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    t = torch.tensor(times, dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sorter.release()
+    ms = float(t.mean().item())
+    if world == 1:
+        sorted_ok = bool((hk.numpy().view("uint64")[1:] >= hk.numpy().view("uint64")[:-1]).all())
+        capi.lib.tb200_workspace_release_all()
+    else:
+        sorted_ok = True
+    return {"value": n * world / (ms * 1e-3) / 1e9, "unit": "Gkeys/s", "h2d_bytes_per_step": n * 12,
+            "d2h_bytes_per_step": d2h, "ms_per_step": ms, "steps": steps, "host_memory": "pinned",
+            "api": "tb200_radix_sort_host" if world == 1 else "ShardedSorter.sort between pinned-host copies",
+            "sorted": sorted_ok}
