@@ -1,0 +1,266 @@
+// Boundary tests of thrust_b200::system: the thrust:: algorithms, called with the
+// custom policy (or through iterators retagged with it), must reach the sm_100a path
+// for arithmetic data and the inherited CUDA path for everything else, and must give
+// the results of the host (CPP) system — the same device==host comparison the
+// reference's unit tests make (testing/sort.cu:80-90, scan.cu:379-415,
+// reduce_by_key.cu:115-156). Known-answer vectors are the reference's own
+// (testing/sort.cu:42-62, sort_by_key.cu:44-70, scan.cu:44-104, reduce_by_key.cu:15-112).
+#include <thrust/device_vector.h>
+#include <thrust/host_vector.h>
+#include <thrust/iterator/counting_iterator.h>
+#include <thrust/iterator/retag.h>
+#include <thrust/sequence.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <numeric>
+#include <cstdlib>
+#include <random>
+#include <vector>
+
+#include "thrust_b200/system.h"
+
+static int g_failed = 0, g_checks = 0;
+static char g_ctx[128] = "";
+#define CHECK(cond)                                                             \
+  do {                                                                          \
+    ++g_checks;                                                                 \
+    if (!(cond)) { ++g_failed; std::printf("FAIL %s:%d  %s   [%s]\n", __FILE__, __LINE__, #cond, g_ctx); } \
+  } while (0)
+
+namespace tb = thrust_b200;
+static unsigned long long fast() { return tb::detail::fast_calls().load(); }
+static unsigned long long fwd() { return tb::detail::forwarded_calls().load(); }
+
+template <typename T>
+thrust::host_vector<T> random_vec(size_t n, unsigned seed, long long lo, long long hi) {
+  std::mt19937_64 rng(seed);
+  thrust::host_vector<T> h(n);
+  for (size_t i = 0; i < n; ++i) h[i] = (T)(lo + (long long)(rng() % (unsigned long long)(hi - lo + 1)));
+  return h;
+}
+
+// Host-side expectation for the sorts: std::stable_sort (the toolkit's own host radix sort
+// is not used as the comparator; for int keys it orders negative values after positive ones).
+template <typename T, typename Cmp>
+void host_stable_sort_by_key(thrust::host_vector<T>& k, thrust::host_vector<unsigned>* v, Cmp cmp) {
+  std::vector<size_t> idx(k.size());
+  std::iota(idx.begin(), idx.end(), (size_t)0);
+  std::stable_sort(idx.begin(), idx.end(), [&](size_t a, size_t b) { return cmp(k[a], k[b]); });
+  thrust::host_vector<T> k2(k.size());
+  thrust::host_vector<unsigned> v2(k.size());
+  for (size_t i = 0; i < idx.size(); ++i) { k2[i] = k[idx[i]]; if (v) v2[i] = (*v)[idx[i]]; }
+  k = k2;
+  if (v) *v = v2;
+}
+
+template <typename T> struct less_div_10 {
+  __host__ __device__ bool operator()(const T& a, const T& b) const { return (int)a / 10 < (int)b / 10; }
+};
+
+template <typename T>
+void test_sort_type(size_t n, long long lo, long long hi) {
+  std::snprintf(g_ctx, sizeof g_ctx, "sort %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<T> h = random_vec<T>(n, 17 + (unsigned)n, lo, hi);
+  thrust::device_vector<T> d = h;
+  const auto f0 = fast();
+  thrust::sort(tb::par, d.begin(), d.end());
+  CHECK(fast() == f0 + 1);
+  host_stable_sort_by_key(h, nullptr, std::less<T>());
+  CHECK(thrust::host_vector<T>(d) == h);
+
+  h = random_vec<T>(n, 18 + (unsigned)n, lo, hi);
+  d = h;
+  thrust::stable_sort(tb::par, d.begin(), d.end(), thrust::greater<T>());
+  host_stable_sort_by_key(h, nullptr, std::greater<T>());
+  CHECK(thrust::host_vector<T>(d) == h);
+
+  // stability is observable: narrow keys, independent values
+  thrust::host_vector<T> hk = random_vec<T>(n, 19 + (unsigned)n, lo / 64, hi / 64);
+  thrust::host_vector<unsigned> hv = random_vec<unsigned>(n, 20, 0, 1 << 30);
+  thrust::device_vector<T> dk = hk;
+  thrust::device_vector<unsigned> dv = hv;
+  thrust::stable_sort_by_key(tb::par, dk.begin(), dk.end(), dv.begin());
+  host_stable_sort_by_key(hk, &hv, std::less<T>());
+  CHECK(thrust::host_vector<T>(dk) == hk);
+  CHECK(thrust::host_vector<unsigned>(dv) == hv);
+  dk = hk = random_vec<T>(n, 21 + (unsigned)n, lo / 64, hi / 64);
+  dv = hv = random_vec<unsigned>(n, 22, 0, 1 << 30);
+  thrust::sort_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), thrust::greater<T>());
+  host_stable_sort_by_key(hk, &hv, std::greater<T>());
+  CHECK(thrust::host_vector<T>(dk) == hk);
+  CHECK(thrust::host_vector<unsigned>(dv) == hv);
+}
+
+template <typename T>
+void test_scan_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "scan %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<T> h = random_vec<T>(n, 31 + (unsigned)n, -1000, 1000);
+  thrust::device_vector<T> d = h, out(n);
+  thrust::host_vector<T> hout(n);
+  const auto f0 = fast();
+  auto e = thrust::inclusive_scan(tb::par, d.begin(), d.end(), out.begin());
+  CHECK(e == out.end());
+  CHECK(fast() == f0 + 1);
+  thrust::inclusive_scan(thrust::host, h.begin(), h.end(), hout.begin());
+  CHECK(thrust::host_vector<T>(out) == hout);
+  thrust::exclusive_scan(tb::par, d.begin(), d.end(), out.begin());
+  thrust::exclusive_scan(thrust::host, h.begin(), h.end(), hout.begin());
+  CHECK(thrust::host_vector<T>(out) == hout);
+  thrust::exclusive_scan(tb::par, d.begin(), d.end(), out.begin(), (T)11);
+  thrust::exclusive_scan(thrust::host, h.begin(), h.end(), hout.begin(), (T)11);
+  CHECK(thrust::host_vector<T>(out) == hout);
+  thrust::exclusive_scan(tb::par, d.begin(), d.end(), out.begin(), (T)11, thrust::plus<T>());
+  CHECK(thrust::host_vector<T>(out) == hout);
+  CHECK(fast() == f0 + 4);
+  // in place
+  thrust::inclusive_scan(tb::par, d.begin(), d.end(), d.begin());
+  thrust::inclusive_scan(thrust::host, h.begin(), h.end(), h.begin());
+  CHECK(thrust::host_vector<T>(d) == h);
+}
+
+template <typename K, typename V>
+void test_rbk_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "rbk %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<K> hk(n);
+  std::mt19937 rng(41 + (unsigned)n);
+  K cur = 0;
+  for (size_t i = 0; i < n; ++i) { if (rng() % 3 == 0) cur = (K)(cur + 1); hk[i] = cur; }
+  thrust::host_vector<V> hv = random_vec<V>(n, 43, 0, 1000);
+  thrust::device_vector<K> dk = hk, dko(n);
+  thrust::device_vector<V> dv = hv, dvo(n);
+  thrust::host_vector<K> hko(n);
+  thrust::host_vector<V> hvo(n);
+  const auto f0 = fast();
+  auto de = thrust::reduce_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), dko.begin(), dvo.begin());
+  CHECK(fast() == f0 + (n ? 1 : 0));
+  auto he = thrust::reduce_by_key(thrust::host, hk.begin(), hk.end(), hv.begin(), hko.begin(), hvo.begin());
+  const size_t runs = he.first - hko.begin();
+  CHECK((size_t)(de.first - dko.begin()) == runs);
+  CHECK((size_t)(de.second - dvo.begin()) == runs);
+  dko.resize(runs); dvo.resize(runs); hko.resize(runs); hvo.resize(runs);
+  CHECK(thrust::host_vector<K>(dko) == hko);
+  CHECK(thrust::host_vector<V>(dvo) == hvo);
+}
+
+int main() {
+  // ---- known answers -------------------------------------------------------------------
+  {
+    const int raw[7] = {1, 3, 6, 5, 2, 0, 4};
+    thrust::device_vector<int> k(raw, raw + 7);
+    thrust::sort(tb::par, k.begin(), k.end());
+    for (int i = 0; i < 7; ++i) CHECK(k[i] == i);
+    thrust::device_vector<int> k2(raw, raw + 7), v2(7);
+    thrust::sequence(v2.begin(), v2.end());
+    thrust::sort_by_key(tb::par, k2.begin(), k2.end(), v2.begin());
+    const int want_v[7] = {5, 0, 4, 1, 6, 3, 2};
+    for (int i = 0; i < 7; ++i) { CHECK(k2[i] == i); CHECK(v2[i] == want_v[i]); }
+  }
+  {
+    const int raw[5] = {1, 3, -2, 4, -5};
+    thrust::device_vector<int> in(raw, raw + 5), out(5);
+    thrust::inclusive_scan(tb::par, in.begin(), in.end(), out.begin());
+    const int w1[5] = {1, 4, 2, 6, 1};
+    for (int i = 0; i < 5; ++i) CHECK(out[i] == w1[i]);
+    thrust::exclusive_scan(tb::par, in.begin(), in.end(), out.begin());
+    const int w2[5] = {0, 1, 4, 2, 6};
+    for (int i = 0; i < 5; ++i) CHECK(out[i] == w2[i]);
+    thrust::exclusive_scan(tb::par, in.begin(), in.end(), out.begin(), 3);
+    const int w3[5] = {3, 4, 7, 5, 9};
+    for (int i = 0; i < 5; ++i) CHECK(out[i] == w3[i]);
+    thrust::inclusive_scan(tb::par, in.begin(), in.end(), in.begin());  // in place
+    for (int i = 0; i < 5; ++i) CHECK(in[i] == w1[i]);
+  }
+  {
+    const int rk[9] = {11, 11, 21, 20, 21, 21, 21, 37, 37};
+    thrust::device_vector<int> k(rk, rk + 9), v(9), ko(9), vo(9);
+    thrust::sequence(v.begin(), v.end());
+    auto e = thrust::reduce_by_key(tb::par, k.begin(), k.end(), v.begin(), ko.begin(), vo.begin());
+    CHECK(e.first - ko.begin() == 5);
+    CHECK(e.second - vo.begin() == 5);
+    const int wk[5] = {11, 21, 20, 21, 37}, wv[5] = {1, 2, 3, 15, 15};
+    for (int i = 0; i < 5; ++i) { CHECK(ko[i] == wk[i]); CHECK(vo[i] == wv[i]); }
+    e = thrust::reduce_by_key(tb::par, k.begin(), k.end(), v.begin(), ko.begin(), vo.begin(),
+                              thrust::equal_to<int>(), thrust::plus<int>());
+    CHECK(e.first - ko.begin() == 5);
+    for (int i = 0; i < 5; ++i) { CHECK(ko[i] == wk[i]); CHECK(vo[i] == wv[i]); }
+  }
+
+  // ---- device == host over types and sizes ---------------------------------------------------
+  for (size_t n : {(size_t)0, (size_t)1, (size_t)33, (size_t)10027, (size_t)300007}) {
+    test_sort_type<signed char>(n, -128, 127);
+    test_sort_type<unsigned short>(n, 0, 65535);
+    test_sort_type<int>(n, -2000000000LL, 2000000000LL);
+    test_sort_type<unsigned int>(n, 0, 4000000000LL);
+    test_sort_type<long long>(n, -(1LL << 60), 1LL << 60);
+    test_sort_type<unsigned long long>(n, 0, 1LL << 62);
+    test_sort_type<float>(n, -100000, 100000);
+    test_sort_type<double>(n, -100000, 100000);
+    test_scan_type<int>(n);
+    test_scan_type<unsigned int>(n);
+    test_scan_type<long long>(n);
+    test_rbk_type<int, unsigned int>(n);
+    test_rbk_type<unsigned char, long long>(n);
+    test_rbk_type<long long, int>(n);
+  }
+
+  // ---- everything else is forwarded to the inherited CUDA path and still correct --------------
+  {
+    thrust::host_vector<int> h = random_vec<int>(5000, 7, 0, 999);
+    thrust::device_vector<int> d = h;
+    const auto w0 = fwd(), f0 = fast();
+    thrust::stable_sort(tb::par, d.begin(), d.end(), less_div_10<int>());
+    thrust::stable_sort(thrust::host, h.begin(), h.end(), less_div_10<int>());
+    CHECK(fwd() == w0 + 1 && fast() == f0);
+    CHECK(thrust::host_vector<int>(d) == h);
+    // a max-scan is not plus
+    thrust::device_vector<int> out(5000);
+    thrust::host_vector<int> hout(5000);
+    thrust::inclusive_scan(tb::par, d.begin(), d.end(), out.begin(), thrust::maximum<int>());
+    thrust::inclusive_scan(thrust::host, h.begin(), h.end(), hout.begin(), thrust::maximum<int>());
+    CHECK(fwd() == w0 + 2);
+    CHECK(thrust::host_vector<int>(out) == hout);
+    // a counting iterator is not contiguous
+    thrust::inclusive_scan(tb::par, thrust::counting_iterator<int>(0), thrust::counting_iterator<int>(5000), out.begin());
+    CHECK(fwd() == w0 + 3);
+    CHECK(out[4999] == 4999 * 5000 / 2);
+    // mixed types: the accumulator is the init's type (testing/scan.cu:250-320)
+    thrust::device_vector<float> fin(4, 1.5f);
+    thrust::device_vector<int> iout(4);
+    thrust::exclusive_scan(tb::par, fin.begin(), fin.end(), iout.begin(), (int)0);
+    CHECK(fwd() == w0 + 4);
+    CHECK(iout[0] == 0 && iout[1] == 1 && iout[2] == 2 && iout[3] == 3);
+  }
+
+  // ---- dispatch by iterator tag, streams, nosync ---------------------------------------------
+  {
+    thrust::device_vector<int> d = random_vec<int>(4096, 9, -5000, 5000);
+    const auto f0 = fast();
+    thrust::sort(thrust::retag<tb::system>(d.begin()), thrust::retag<tb::system>(d.end()));
+    CHECK(fast() == f0 + 1);
+    CHECK(thrust::is_sorted(d.begin(), d.end()));
+
+    cudaStream_t s;
+    cudaStreamCreate(&s);
+    thrust::device_vector<long long> a = random_vec<long long>(100000, 10, -1000, 1000), b(100000);
+    thrust::host_vector<long long> ha = a, hb(100000);
+    thrust::inclusive_scan(tb::par_nosync.on(s), a.begin(), a.end(), b.begin());
+    cudaStreamSynchronize(s);
+    thrust::inclusive_scan(thrust::host, ha.begin(), ha.end(), hb.begin());
+    CHECK(thrust::host_vector<long long>(b) == hb);
+    thrust::sort(tb::par.on(s), a.begin(), a.end());
+    std::sort(ha.begin(), ha.end());
+    CHECK(thrust::host_vector<long long>(a) == ha);
+    // raw device pointers work too
+    int* raw = thrust::raw_pointer_cast(d.data());
+    thrust::sort(tb::par.on(s), raw, raw + d.size(), thrust::greater<int>());
+    CHECK(thrust::is_sorted(d.begin(), d.end(), thrust::greater<int>()));
+    cudaStreamDestroy(s);
+  }
+
+  CHECK(cudaGetLastError() == cudaSuccess);
+  tb200_workspace_release_all();
+  std::printf("%s: %d checks, %d failed (fast-path calls %llu, forwarded %llu)\n", g_failed ? "FAILED" : "PASSED",
+              g_checks, g_failed, fast(), fwd());
+  return g_failed ? 1 : 0;
+}

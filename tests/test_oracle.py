@@ -1,0 +1,133 @@
+"""Pins the CPU oracle (oracle/oracle.c): against the reference's known-answer vectors,
+against outputs of the unmodified reference committed as tests/golden/reference_vectors.npz,
+and — where oracle/_ref is built — against the reference's CPP and OMP systems live."""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import oracle
+
+GOLD = Path(__file__).resolve().parent / "golden"
+KA = json.loads((GOLD / "known_answers.json").read_text())
+TYPES = ["int8", "uint8", "int16", "uint16", "int32", "uint32", "int64", "uint64", "float32", "float64", "bool"]
+NUMERIC = ["int32", "uint32", "int64", "uint64", "float32", "float64"]
+
+
+@pytest.fixture(scope="module")
+def port():
+    oracle.build(ref=False)
+    return oracle.port()
+
+
+@pytest.fixture(scope="module")
+def vectors():
+    return np.load(GOLD / "reference_vectors.npz")
+
+
+def test_known_answers(port):
+    s = KA["sort_simple"]
+    assert port.sort(np.array(s["keys"], dtype=np.int32)).tolist() == s["sorted"]
+    s = KA["sort_by_key_simple"]
+    k, v = port.sort_by_key(np.array(s["keys"], dtype=np.int32), np.array(s["values"], dtype=np.int32))
+    assert k.tolist() == s["sorted_keys"] and v.tolist() == s["sorted_values"]
+    s = KA["scan_simple"]
+    a = np.array(s["input"], dtype=np.int32)
+    assert port.scan(a).tolist() == s["inclusive"]
+    assert port.scan(a, True).tolist() == s["exclusive"]
+    assert port.scan(a, True, 3).tolist() == s["exclusive_init_3"]
+    assert port.scan(a.copy(), inplace=True).tolist() == s["inclusive"]
+    s = KA["scan_mixed_types"]
+    f = np.array(s["float_input"], dtype=np.float32)
+    assert port.scan(f).tolist() == s["float_inclusive"]
+    assert port.scan(f, True, 5.5).tolist() == s["float_exclusive_init_5.5"]
+    assert port.scan(np.array(s["int_input"], dtype=np.int32)).tolist() == s["int_inclusive"]
+    s = KA["reduce_by_key_simple"]
+    for dt in (np.int8, np.int32, np.uint64):
+        ko, vo = port.reduce_by_key(np.array(s["keys"], dtype=dt), np.array(s["values"], dtype=np.int32))
+        assert ko.tolist() == s["out_keys"] and vo.tolist() == s["out_values"]
+    s = KA["dense_histogram_example"]
+    data = np.array(s["data"], dtype=np.int32)
+    assert port.sort(data).tolist() == s["sorted"]
+    assert port.histogram(data, np.arange(9, dtype=np.int32)).tolist() == s["histogram"]
+    assert np.cumsum(s["histogram"]).tolist() == s["cumulative"]
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_sort_matches_reference_vectors(port, vectors, t):
+    k, v = vectors[f"sort/{t}/keys"], vectors[f"sort/{t}/vals"]
+    for desc in (0, 1):
+        assert port.sort(k, bool(desc)).tobytes() == vectors[f"sort/{t}/desc{desc}/keys_only"].tobytes()
+        sk, sv = port.sort_by_key(k, v, bool(desc))
+        assert sk.tobytes() == vectors[f"sort/{t}/desc{desc}/by_key_keys"].tobytes()
+        assert sv.tobytes() == vectors[f"sort/{t}/desc{desc}/by_key_vals"].tobytes()
+
+
+@pytest.mark.parametrize("t", NUMERIC)
+def test_scan_and_rbk_match_reference_vectors(port, vectors, t):
+    a = vectors[f"scan/{t}/in"]
+    assert port.scan(a).tobytes() == vectors[f"scan/{t}/inclusive"].tobytes()
+    assert port.scan(a, True).tobytes() == vectors[f"scan/{t}/exclusive"].tobytes()
+    assert port.scan(a, True, 11).tobytes() == vectors[f"scan/{t}/exclusive_init11"].tobytes()
+    ko, vo = port.reduce_by_key(vectors[f"rbk/{t}/keys"], vectors[f"rbk/{t}/vals"])
+    assert ko.tobytes() == vectors[f"rbk/{t}/out_keys"].tobytes()
+    assert vo.tobytes() == vectors[f"rbk/{t}/out_vals"].tobytes()
+
+
+def test_histogram_matches_reference_vectors(port, vectors):
+    assert port.histogram(vectors["hist/data"], vectors["hist/bins"]).tolist() == vectors["hist/counts"].tolist()
+
+
+def test_edge_cases(port):
+    for t in TYPES:
+        e = np.empty(0, dtype=t)
+        assert port.sort(e).size == 0
+        one = np.ones(1, dtype=t)
+        assert port.sort(one, True).tolist() == one.tolist()
+    k, v = port.reduce_by_key(np.empty(0, dtype=np.int32), np.empty(0, dtype=np.float32))
+    assert k.size == 0 and v.size == 0
+    # float keys: bitwise total order, -0.0 before +0.0, NaNs at the ends by sign
+    f = np.array([0.0, -0.0, np.inf, -np.inf, 1.0, -1.0], dtype=np.float32)
+    assert port.sort(f).view(np.uint32).tolist() == np.array([-np.inf, -1.0, -0.0, 0.0, 1.0, np.inf], dtype=np.float32).view(np.uint32).tolist()
+    # descending sort_by_key keeps equal keys in input order
+    k, v = port.sort_by_key(np.array([1, 2, 1, 2], dtype=np.int16), np.array([0, 1, 2, 3], dtype=np.uint32), True)
+    assert k.tolist() == [2, 2, 1, 1] and v.tolist() == [1, 3, 0, 2]
+
+
+@pytest.mark.skipif(not oracle.have_ref("cpp"), reason="oracle/_ref not built (no reference tree on this machine)")
+@pytest.mark.parametrize("system", ["cpp", "omp"])
+def test_port_matches_live_reference(port, system):
+    if not oracle.have_ref(system):
+        pytest.skip(system)
+    ref = oracle.ref(system)
+    assert ref.thrust_version == 200200
+    rng = np.random.default_rng(5)
+    for t in TYPES:
+        n = 20011
+        dt = np.dtype(t)
+        if t == "bool":
+            k = rng.integers(0, 2, size=n).astype(np.bool_)
+        elif dt.kind == "f":
+            # finite keys without -0.0: the OMP system's merge step treats -0.0 == +0.0, so its
+            # order of mixed zeros depends on the thread count (omp/detail/sort.inl:48-60)
+            k = rng.uniform(-1e6, 1e6, size=n).astype(dt)
+        else:
+            k = rng.integers(np.iinfo(dt).min, np.iinfo(dt).max, size=n, dtype=dt, endpoint=True)
+        v = rng.integers(0, 1 << 32, size=n, dtype=np.uint32)
+        for desc in (False, True):
+            assert port.sort(k, desc).tobytes() == ref.sort(k, desc).tobytes()
+            a, b = port.sort_by_key(k, v, desc), ref.sort_by_key(k, v, desc)
+            assert a[0].tobytes() == b[0].tobytes() and a[1].tobytes() == b[1].tobytes()
+    for t in NUMERIC:
+        dt = np.dtype(t)
+        a = rng.uniform(-1, 1, size=30011).astype(dt) if dt.kind == "f" else rng.integers(0, 1000, size=30011).astype(dt)
+        for ex, init in [(False, None), (True, None), (True, 7)]:
+            assert port.scan(a, ex, init).tobytes() == ref.scan(a, ex, init).tobytes()
+        keys = np.cumsum(rng.random(30011) < 0.1).astype(np.int64)
+        x, y = port.reduce_by_key(keys, a), ref.reduce_by_key(keys, a)
+        assert x[0].tobytes() == y[0].tobytes()
+        if dt.kind != "f" or system == "cpp":  # the OMP system reduces through a parallel scan: float order differs
+            assert x[1].tobytes() == y[1].tobytes()
+        else:
+            assert np.allclose(x[1], y[1], rtol=1e-4, atol=1e-3)

@@ -38,14 +38,14 @@ def _newest_header() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _compile(src: Path, verbose: bool) -> Path:
-    obj = OBJ / (src.stem + ".o")
-    cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+def _compile(src: Path, verbose: bool, obj_dir: Path = OBJ, extra=()) -> Path:
+    obj = obj_dir / (src.stem + ".o")
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)
     if verbose and r.stderr:
-        (OBJ / (src.stem + ".ptxas.txt")).write_text(r.stderr)
+        (obj_dir / (src.stem + ".ptxas.txt")).write_text(r.stderr)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
     return obj

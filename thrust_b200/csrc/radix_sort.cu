@@ -29,7 +29,7 @@
 #include <type_traits>
 
 #ifndef TB200_MATCH_MODE
-#define TB200_MATCH_MODE 0  // 0: match.any instruction, 1: eight ballots
+#define TB200_MATCH_MODE 1  // 0: match.any instruction (slow on sm_100), 1: eight ballots
 #endif
 
 namespace tb200 {
@@ -221,6 +221,8 @@ __device__ __forceinline__ void st_desc(DescT* p, DescT v) {
   else st_relaxed_u64(p, v);
 }
 
+// Lanes of the warp that hold the same 8-bit digit. One ballot per bit; a lane keeps
+// the voters that agree with its own bit: peers &= ~(ballot ^ sign_extend(bit)).
 __device__ __forceinline__ unsigned match_digit(unsigned d) {
 #if TB200_MATCH_MODE == 0
   return __match_any_sync(0xffffffffu, d);
@@ -228,9 +230,9 @@ __device__ __forceinline__ unsigned match_digit(unsigned d) {
   unsigned peers = 0xffffffffu;
 #pragma unroll
   for (int b = 0; b < 8; ++b) {
-    const bool bit = (d >> b) & 1u;
-    const unsigned m = __ballot_sync(0xffffffffu, bit);
-    peers &= bit ? m : ~m;
+    const unsigned m = __ballot_sync(0xffffffffu, (d >> b) & 1u);
+    const unsigned t = 0u - ((d >> b) & 1u);  // all ones when the lane's bit is set
+    peers &= ~(m ^ t);
   }
   return peers;
 #endif
@@ -248,8 +250,8 @@ struct PassShape {
   static constexpr size_t kSmem = align_up(kKeysBytes, 16) + kValsBytes + kWhistBytes;
 };
 
-template <typename UK, int VB, int THREADS, int ITEMS, typename DescT>
-__global__ void __launch_bounds__(THREADS)
+template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT>
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 onesweep_kernel(const PassParams prm) {
   using Shape = PassShape<UK, VB, THREADS, ITEMS>;
   using V = typename Shape::V;
@@ -309,26 +311,39 @@ onesweep_kernel(const PassParams prm) {
     key[j] = k;
   }
 
-  // ---- rank inside the warp
+#ifdef TB200_EARLY_VALUES
+  V val[VB ? ITEMS : 1];
+  if constexpr (VB != 0) {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+      const unsigned local = warp_off + j * kWarp + lane;
+      if (local < tile_valid) val[j] = src_vals[tile_base + local];
+    }
+  }
+#endif
+
+  // ---- rank inside the warp. All lanes read the warp's running count of their digit,
+  // then the lowest lane of every group of equal digits advances it. Shared-memory
+  // accesses of one warp execute in program order, so round j+1 reads what round j
+  // wrote; the only register dependency inside a round is load -> add -> store.
   unsigned* whist = s_whist + warp * kRadix;
   unsigned short rank[ITEMS];
 #pragma unroll
   for (int j = 0; j < ITEMS; ++j) {
     const unsigned d = digit_of(key[j], shift, mask);
     const unsigned peers = match_digit(d);
-    const unsigned leader = __ffs(peers) - 1;
-    unsigned old = 0;
-    if (lane == leader) {
-      old = whist[d];
-      whist[d] = old + __popc(peers);
-    }
-    old = __shfl_sync(0xffffffffu, old, leader);
-    rank[j] = (unsigned short)(old + __popc(peers & lanemask_lt()));
+    const unsigned before = __popc(peers & lanemask_lt());
+    const unsigned old = whist[d];
     __syncwarp();
+    if (before == 0) whist[d] = old + __popc(peers);
+    __syncwarp();
+    rank[j] = (unsigned short)(old + before);
   }
   __syncthreads();
 
-  // ---- per-digit tile totals, warp offsets, look-back (thread d owns digit d)
+  // ---- per-digit tile totals and warp offsets (thread d owns digit d). The tile's
+  // counts are published BEFORE any local reordering so that successor tiles can
+  // use them while this CTA is still busy.
   unsigned count = 0;
   if (threadIdx.x < kRadix) {
     const unsigned d = threadIdx.x;
@@ -354,32 +369,69 @@ onesweep_kernel(const PassParams prm) {
     if (lane == 31) s_scan[warp] = incl;
   }
   __syncthreads();
+  unsigned digit_start = 0;
   if (threadIdx.x < kRadix) {
     const unsigned d = threadIdx.x;
-    unsigned digit_start = incl - count;
+    digit_start = incl - count;
     for (unsigned w = 0; w < warp; ++w) digit_start += s_scan[w];
 #pragma unroll 4
     for (int w = 0; w < WARPS; ++w) s_whist[w * kRadix + d] += digit_start;
+  }
+  __syncthreads();
 
+  // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j) {
+    const unsigned d = digit_of(key[j], shift, mask);
+    const unsigned q = whist[d] + rank[j];
+    rank[j] = (unsigned short)q;
+    s_keys[q] = key[j];
+  }
+  if constexpr (VB != 0) {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+      const unsigned local = warp_off + j * kWarp + lane;
+#ifdef TB200_EARLY_VALUES
+      if (local < tile_valid) s_vals[rank[j]] = val[j];
+#else
+      if (local < tile_valid) s_vals[rank[j]] = src_vals[tile_base + local];
+#endif
+    }
+  }
+
+  // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
+  // fetches kWindow descriptors at once and consumes them nearest first.
+  if (threadIdx.x < kRadix) {
+    const unsigned d = threadIdx.x;
     unsigned long long excl = 0;
     if (tile != 0) {
+      constexpr int kWindow = 4;
       const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
+      const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
       long long t = (long long)tile - 1;
-      bool timed_out = false;
-      while (true) {
-        DescT v;
-        unsigned polls = 0;
-        while ((unsigned)((v = ld_desc<DescT>(chain + (size_t)t * kRadix)) >> DSH) == st_empty) {
-          backoff(++polls);
-          if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
-            timed_out = true;
-            break;
+      bool timed_out = false, done = false;
+      while (!done && !timed_out) {
+        DescT v[kWindow];
+#pragma unroll
+        for (int i = 0; i < kWindow; ++i)
+          v[i] = t - i >= 0 ? ld_desc<DescT>(chain + (size_t)(t - i) * kRadix) : below_first;
+#pragma unroll
+        for (int i = 0; i < kWindow; ++i) {
+          if (done || timed_out) break;
+          unsigned polls = 0;
+          while ((unsigned)(v[i] >> DSH) == st_empty) {
+            backoff(++polls);
+            if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
+              timed_out = true;
+              break;
+            }
+            v[i] = ld_desc<DescT>(chain + (size_t)(t - i) * kRadix);
           }
+          if (timed_out) break;
+          excl += (unsigned long long)(v[i] & DescBits<DescT>::kValueMask);
+          done = (unsigned)(v[i] >> DSH) == st_prefix;
         }
-        if (timed_out) break;
-        excl += (unsigned long long)(v & DescBits<DescT>::kValueMask);
-        if ((unsigned)(v >> DSH) == st_prefix) break;
-        --t;
+        t -= kWindow;
       }
       if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
       DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
@@ -389,44 +441,15 @@ onesweep_kernel(const PassParams prm) {
   }
   __syncthreads();
 
-  // ---- reorder keys through shared memory
-  unsigned short slot[ITEMS];
-#pragma unroll
-  for (int j = 0; j < ITEMS; ++j) {
-    const unsigned d = digit_of(key[j], shift, mask);
-    const unsigned q = whist[d] + rank[j];
-    slot[j] = (unsigned short)q;
-    s_keys[q] = key[j];
-  }
-  V val[VB ? ITEMS : 1];
-  if constexpr (VB != 0) {
-#pragma unroll
-    for (int j = 0; j < ITEMS; ++j) {
-      const unsigned local = warp_off + j * kWarp + lane;
-      if (local < tile_valid) val[j] = src_vals[tile_base + local];
-    }
-  }
-  __syncthreads();
+  // ---- scatter: every digit leaves as one contiguous run
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const unsigned pos = threadIdx.x + i * THREADS;
     if (pos < tile_valid) {
       const UK k = s_keys[pos];
-      const unsigned d = digit_of(k, shift, mask);
-      dst_keys[s_gbase[d] + pos] = last_exec ? decode_key(k, prm.enc) : k;
-    }
-  }
-  if constexpr (VB != 0) {
-#pragma unroll
-    for (int j = 0; j < ITEMS; ++j) s_vals[slot[j]] = val[j];
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      const unsigned pos = threadIdx.x + i * THREADS;
-      if (pos < tile_valid) {
-        const unsigned d = digit_of(s_keys[pos], shift, mask);
-        dst_vals[s_gbase[d] + pos] = s_vals[pos];
-      }
+      const unsigned long long g = s_gbase[digit_of(k, shift, mask)] + pos;
+      dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
+      if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
     }
   }
 }
@@ -465,9 +488,16 @@ copy_back_kernel(uint4* __restrict__ keys_main, const uint4* __restrict__ keys_a
 // ---------------------------------------------------------------------------------
 template <typename UK, int VB>
 struct Tuning {
-  // threads x items per thread of one onesweep tile
+  // threads x items per thread of one onesweep tile, and CTAs the register budget must allow per SM
+#ifdef TB200_TUNE_THREADS
+  static constexpr int kThreads = TB200_TUNE_THREADS;
+  static constexpr int kItems = TB200_TUNE_ITEMS;
+  static constexpr int kMinCtas = TB200_TUNE_MINB;
+#else
   static constexpr int kThreads = 512;
-  static constexpr int kItems = sizeof(UK) == 8 ? (VB >= 8 ? 6 : 8) : (VB == 16 ? 6 : (VB == 8 ? 8 : 12));
+  static constexpr int kItems = sizeof(UK) == 8 ? (VB >= 8 ? 8 : 12) : (VB == 16 ? 6 : (VB == 8 ? 12 : 16));
+  static constexpr int kMinCtas = 2;
+#endif
 };
 
 struct Layout {
@@ -555,8 +585,8 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
     }
     return TB200_OK;
   };
-  int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, unsigned long long>)
-                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, unsigned>);
+  int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long>)
+                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned>);
   if (rc) return rc;
 
   copy_back_kernel<<<sms * 4, 256, 0, stream>>>(

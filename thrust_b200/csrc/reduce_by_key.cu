@@ -16,9 +16,12 @@
 namespace tb200 {
 namespace {
 
+// 256 threads x 8 chunks: 8192 elements (64 KiB of keys + values for 4-byte types)
+// per tile, two tiles resident per SM. Large tiles keep the tile rate below what the
+// look-back chain resolves (64 predecessors per L2 round trip).
 constexpr int kRbkThreads = 256;
 constexpr int kRbkWarps = kRbkThreads / kWarp;
-constexpr int kRbkChunks = 4;
+constexpr int kRbkChunks = 8;
 
 template <typename T, int E>
 struct alignas(sizeof(T) * E) Pack {
@@ -61,8 +64,9 @@ struct SegWords {
   }
 };
 
-// Look-back of warp 0 over (count, value) descriptors; the operator is not
-// commutative, so far predecessors are combined on the left of near ones.
+// Look-back of warp 0 over (count, value) descriptors, 64 per round (two per lane,
+// loads in flight together). The operator is not commutative, so far predecessors
+// are combined on the left of near ones.
 template <typename V>
 __device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* status,
                              unsigned long long& out_cnt, V& out_val) {
@@ -72,42 +76,54 @@ __device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* stat
   long long base = (long long)tile - 1;
   bool timed_out = false;
   while (true) {
-    const long long idx = base - lane;
-    unsigned st = kStatePrefix;
-    unsigned long long cnt = 0;
-    V val = V(0);
-    if (idx >= 0) {
-      unsigned payload[4];
-      unsigned polls = 0;
-      while ((st = peek<4>(&tiles[idx], payload)) == kStateEmpty) {
-        backoff(++polls);
-        if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
-          timed_out = true;
-          st = kStatePrefix;
-          break;
+    unsigned st[2] = {kStatePrefix, kStatePrefix};
+    unsigned payload[2][4];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const long long idx = base - 32 * s - lane;
+      if (idx >= 0) st[s] = peek<4>(&tiles[idx], payload[s]);
+    }
+    bool found = false;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (found) break;
+      const long long idx = base - 32 * s - lane;
+      unsigned long long cnt = 0;
+      V val = V(0);
+      if (idx >= 0) {
+        unsigned polls = 0;
+        while (st[s] == kStateEmpty) {
+          backoff(++polls);
+          if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+            timed_out = true;
+            st[s] = kStatePrefix;
+            break;
+          }
+          st[s] = peek<4>(&tiles[idx], payload[s]);
+        }
+        if (!timed_out) SegWords<V>::unpack(payload[s], cnt, val);
+      }
+      const unsigned pm = __ballot_sync(0xffffffffu, st[s] == kStatePrefix);
+      const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+      if (lane > first) { cnt = 0; val = V(0); }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
+        const V ov = __shfl_down_sync(0xffffffffu, val, off);
+        if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val)
+          val = cnt ? val : ov + val;
+          cnt = oc + cnt;
         }
       }
-      if (!timed_out) SegWords<V>::unpack(payload, cnt, val);
+      cnt = __shfl_sync(0xffffffffu, cnt, 0);
+      val = __shfl_sync(0xffffffffu, val, 0);
+      // this window lies to the left of everything accumulated so far
+      acc_val = acc_cnt ? acc_val : val + acc_val;
+      acc_cnt = cnt + acc_cnt;
+      found = pm != 0;
     }
-    const unsigned pm = __ballot_sync(0xffffffffu, st == kStatePrefix);
-    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
-    if (lane > first) { cnt = 0; val = V(0); }
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
-      const V ov = __shfl_down_sync(0xffffffffu, val, off);
-      if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val)
-        val = cnt ? val : ov + val;
-        cnt = oc + cnt;
-      }
-    }
-    cnt = __shfl_sync(0xffffffffu, cnt, 0);
-    val = __shfl_sync(0xffffffffu, val, 0);
-    // this window lies to the left of everything accumulated so far
-    acc_val = acc_cnt ? acc_val : val + acc_val;
-    acc_cnt = cnt + acc_cnt;
-    if (pm) break;
-    base -= 32;
+    if (found) break;
+    base -= 64;
   }
   if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
   out_cnt = acc_cnt;
@@ -115,7 +131,7 @@ __device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* stat
 }
 
 template <typename K, typename V, bool ALIGNED>
-__global__ void __launch_bounds__(kRbkThreads)
+__global__ void __launch_bounds__(kRbkThreads, 2)
 reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __restrict__ keys_out,
                      V* __restrict__ vals_out, unsigned long long* __restrict__ num_runs, uint64_t n,
                      unsigned num_tiles, TempHeader* hdr, TileWords<4>* tiles) {

@@ -14,9 +14,12 @@
 namespace tb200 {
 namespace {
 
-constexpr int kScanThreads = 256;
+// 512 threads x 8 vectors = 64 KiB per tile. Large tiles keep the number of tiles
+// per microsecond (about 50 at full HBM speed) well below what the look-back chain
+// can resolve: a warp inspects 64 predecessors per L2 round trip.
+constexpr int kScanThreads = 512;
 constexpr int kScanWarps = kScanThreads / kWarp;
-constexpr int kScanVecs = 4;  // 16-byte vectors per thread
+constexpr int kScanVecs = 8;  // 16-byte vectors per thread
 
 template <typename T>
 struct alignas(16) Vec16 {
@@ -44,8 +47,9 @@ struct Words {
   }
 };
 
-// Warp 0 walks back over predecessor descriptors, 32 at a time, until it meets
-// one that carries a full prefix. Returns the sum of everything before `tile`.
+// Warp 0 walks back over predecessor descriptors, 64 at a time (two per lane,
+// both loads in flight together), until it meets one that carries a full prefix.
+// Returns the sum of everything before `tile`.
 template <typename T>
 __device__ T lookback_sum(const TileWords<Words<T>::W>* tiles, unsigned tile, int* status) {
   constexpr int W = Words<T>::W;
@@ -54,42 +58,58 @@ __device__ T lookback_sum(const TileWords<Words<T>::W>* tiles, unsigned tile, in
   long long base = (long long)tile - 1;
   bool timed_out = false;
   while (true) {
-    const long long idx = base - lane;
-    unsigned st = kStatePrefix;
-    T val = T(0);
-    if (idx >= 0) {
-      unsigned payload[W];
-      unsigned polls = 0;
-      while ((st = peek<W>(&tiles[idx], payload)) == kStateEmpty) {
-        backoff(++polls);
-        if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
-          timed_out = true;
-          st = kStatePrefix;
-          break;
-        }
-      }
-      val = timed_out ? T(0) : Words<T>::unpack(payload);
-    }
-    const unsigned pm = __ballot_sync(0xffffffffu, st == kStatePrefix);
-    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
-    if (lane > first) val = T(0);
-    // far predecessors (high lanes) are summed before near ones
+    // slot s = 0 is the nearer half of the window (tiles base-lane), s = 1 the farther one
+    unsigned st[2] = {kStatePrefix, kStatePrefix};
+    T val[2] = {T(0), T(0)};
+    unsigned payload[2][W];
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      T o = __shfl_down_sync(0xffffffffu, val, off);
-      if (lane + off < 32) val = o + val;
+    for (int s = 0; s < 2; ++s) {
+      const long long idx = base - 32 * s - lane;
+      if (idx >= 0) st[s] = peek<W>(&tiles[idx], payload[s]);
     }
-    val = __shfl_sync(0xffffffffu, val, 0);
-    acc = val + acc;
-    if (pm) break;
-    base -= 32;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const long long idx = base - 32 * s - lane;
+      if (idx >= 0) {
+        unsigned polls = 0;
+        while (st[s] == kStateEmpty) {
+          backoff(++polls);
+          if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+            timed_out = true;
+            st[s] = kStatePrefix;
+            break;
+          }
+          st[s] = peek<W>(&tiles[idx], payload[s]);
+        }
+        val[s] = timed_out ? T(0) : Words<T>::unpack(payload[s]);
+      }
+    }
+    bool found = false;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (found) break;
+      const unsigned pm = __ballot_sync(0xffffffffu, st[s] == kStatePrefix);
+      const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+      T v = lane > first ? T(0) : val[s];
+      // far predecessors (high lanes) are summed before near ones
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        T o = __shfl_down_sync(0xffffffffu, v, off);
+        if (lane + off < 32) v = o + v;
+      }
+      v = __shfl_sync(0xffffffffu, v, 0);
+      acc = v + acc;
+      found = pm != 0;
+    }
+    if (found) break;
+    base -= 64;
   }
   if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
   return acc;
 }
 
 template <typename T, bool EXCLUSIVE, bool ALIGNED>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kScanThreads, 2)
 scan_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr,
             TileWords<Words<T>::W>* tiles) {
   constexpr int W = Words<T>::W;
