@@ -56,12 +56,12 @@ void trace_mark(cudaStream_t stream);
 
 __device__ __forceinline__ unsigned lane_id() {
   unsigned r;
-  asm volatile("mov.u32 %0, %%laneid;" : "=r"(r));
+  asm("mov.u32 %0, %%laneid;" : "=r"(r));
   return r;
 }
 __device__ __forceinline__ unsigned lanemask_lt() {
   unsigned r;
-  asm volatile("mov.u32 %0, %%lanemask_lt;" : "=r"(r));
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(r));
   return r;
 }
 

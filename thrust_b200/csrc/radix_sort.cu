@@ -70,9 +70,17 @@ __device__ __forceinline__ UK decode_key(UK y, const Encoding& e) {
   return y ^ (UK)(((UK)~sra & (UK)e.fmask) | (UK)e.cmask);
 }
 
+// Digit of an encoded key. 64-bit keys: the 32-bit window that starts at bit `shift` is
+// taken with one funnel shift (or from the high word alone), never a 64-bit shift.
 template <typename UK>
 __device__ __forceinline__ unsigned digit_of(UK k, int shift, unsigned mask) {
-  return (unsigned)(k >> shift) & mask;
+  if constexpr (sizeof(UK) == 8) {
+    const unsigned lo = (unsigned)k, hi = (unsigned)(k >> 32);
+    const unsigned w = shift < 32 ? __funnelshift_r(lo, hi, shift) : hi >> (shift - 32);
+    return w & mask;
+  } else {
+    return ((unsigned)k >> shift) & mask;
+  }
 }
 
 template <int BYTES> struct ValueOf;
@@ -250,22 +258,33 @@ struct PassShape {
   static constexpr size_t kSmem = align_up(kKeysBytes, 16) + kValsBytes + kWhistBytes;
 };
 
+// Persistent CTAs: the grid holds as many CTAs as fit on the GPU at once and every
+// CTA loops over tiles taken from an atomic ticket counter. The ticket of the NEXT
+// tile is taken one iteration ahead and its keys are loaded into the key registers
+// as soon as the current tile's keys have been moved to shared memory, so the load
+// latency hides behind the look-back and the scatter of the current tile.
 template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 onesweep_kernel(const PassParams prm) {
   using Shape = PassShape<UK, VB, THREADS, ITEMS>;
   using V = typename Shape::V;
+  // 32-bit output indices whenever n fits (the narrow descriptor is used for n <= 2^30)
+  using IdxT = typename std::conditional<sizeof(DescT) == 4, unsigned, unsigned long long>::type;
   constexpr int WARPS = Shape::kWarps;
   constexpr int TILE = Shape::kTile;
   constexpr int DSH = DescBits<DescT>::kShift;
+  static_assert(THREADS >= kRadix && THREADS % kRadix == 0, "one or more threads per digit");
+  constexpr int GROUPS = THREADS / kRadix;          // thread groups that share the per-digit loops
+  constexpr int WARPS_PER_GROUP = WARPS / GROUPS;
 
   extern __shared__ __align__(16) unsigned char smem[];
   UK* s_keys = reinterpret_cast<UK*>(smem);
   V* s_vals = reinterpret_cast<V*>(smem + align_up(Shape::kKeysBytes, 16));
   unsigned* s_whist = reinterpret_cast<unsigned*>(smem + align_up(Shape::kKeysBytes, 16) + Shape::kValsBytes);
-  __shared__ unsigned long long s_gbase[kRadix];
+  __shared__ IdxT s_gbase[kRadix];
+  __shared__ unsigned s_part[GROUPS][kRadix];  // per-group digit totals
   __shared__ unsigned s_scan[kRadix / kWarp];
-  __shared__ unsigned s_tile;
+  __shared__ unsigned s_next;
 
   SortCtl* ctl = prm.ctl;
   const int pass = prm.pass;
@@ -285,172 +304,211 @@ onesweep_kernel(const PassParams prm) {
   const unsigned st_agg = (st_empty + 1u) & 3u;
   const unsigned st_prefix = (st_empty + 2u) & 3u;
 
-  if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->tickets[pass], 1u);
-  for (int i = threadIdx.x; i < WARPS * kRadix; i += THREADS) s_whist[i] = 0;
-  __syncthreads();
-  const unsigned tile = s_tile;
   const unsigned warp = threadIdx.x / kWarp;
   const unsigned lane = lane_id();
-  const uint64_t tile_base = (uint64_t)tile * TILE;
-  const uint64_t remaining = prm.n - tile_base;
-  const unsigned tile_valid = remaining < (uint64_t)TILE ? (unsigned)remaining : (unsigned)TILE;
   const unsigned warp_off = warp * Shape::kWarpItems;
   const int shift = prm.shift;
   const unsigned mask = prm.mask;
+  const unsigned num_tiles = prm.num_tiles;
+  unsigned* whist = s_whist + warp * kRadix;
 
-  // ---- load (warp-striped: round j of lane l is element j*32+l of the warp's slice)
+  // warp-striped load: round j of lane l is element j*32+l of the warp's slice
   UK key[ITEMS];
+  auto load_keys = [&](unsigned t) {
+    const uint64_t base = (uint64_t)t * TILE;
+    const uint64_t remaining = prm.n - base;
+    const UK* p = src_keys + base + warp_off + lane;
+    if (remaining >= (uint64_t)TILE) {  // full tile: no bounds checks, constant offsets
 #pragma unroll
-  for (int j = 0; j < ITEMS; ++j) {
-    const unsigned local = warp_off + j * kWarp + lane;
-    UK k = (UK)~(UK)0;  // padding sorts to the end of the tile
-    if (local < tile_valid) {
-      k = src_keys[tile_base + local];
-      if (first_exec) k = encode_key(k, prm.enc);
+      for (int j = 0; j < ITEMS; ++j) key[j] = p[j * kWarp];
+    } else {
+      const unsigned valid = (unsigned)remaining;
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j) {
+        const unsigned local = warp_off + j * kWarp + lane;
+        key[j] = local < valid ? p[j * kWarp] : (UK)0;
+      }
     }
-    key[j] = k;
-  }
+    if (first_exec) {
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j) key[j] = encode_key(key[j], prm.enc);
+    }
+    if (remaining < (uint64_t)TILE) {  // padding sorts to the end of the tile
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j)
+        if (warp_off + j * kWarp + lane >= (unsigned)remaining) key[j] = (UK)~(UK)0;
+    }
+  };
 
-#ifdef TB200_EARLY_VALUES
-  V val[VB ? ITEMS : 1];
-  if constexpr (VB != 0) {
+  if (threadIdx.x == 0) s_next = atomicAdd(&ctl->tickets[pass], 1u);
+  __syncthreads();
+  unsigned tile = s_next;
+  if (tile >= num_tiles) return;
+  load_keys(tile);
+  __syncthreads();  // everyone has read s_next before it is overwritten
+
+  while (true) {
+    const uint64_t tile_base = (uint64_t)tile * TILE;
+    const uint64_t remaining = prm.n - tile_base;
+    const unsigned tile_valid = remaining < (uint64_t)TILE ? (unsigned)remaining : (unsigned)TILE;
+
+    if (threadIdx.x == 0) s_next = atomicAdd(&ctl->tickets[pass], 1u);  // consumed after the ranking barrier
+    for (int i = threadIdx.x; i < WARPS * kRadix / 4; i += THREADS)
+      reinterpret_cast<uint4*>(s_whist)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+
+    // ---- rank inside the warp. All lanes read the warp's running count of their
+    // digit, then the lowest lane of every group of equal digits advances it. The
+    // shared-memory accesses of one warp execute in program order, so round j+1 reads
+    // what round j wrote; the only register dependency inside a round is
+    // load -> add -> store.
+    unsigned short rank[ITEMS];
+    const unsigned lt_mask = lanemask_lt();
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned local = warp_off + j * kWarp + lane;
-      if (local < tile_valid) val[j] = src_vals[tile_base + local];
+      const unsigned d = digit_of(key[j], shift, mask);
+      const unsigned peers = match_digit(d);
+      const unsigned ahead = __popc(peers & lt_mask);
+      const unsigned old = whist[d];
+      if (ahead == 0) whist[d] = old + __popc(peers);
+      __syncwarp();
+      rank[j] = (unsigned short)(old + ahead);
     }
-  }
-#endif
+    __syncthreads();
+    const unsigned next = s_next;
 
-  // ---- rank inside the warp. All lanes read the warp's running count of their digit,
-  // then the lowest lane of every group of equal digits advances it. Shared-memory
-  // accesses of one warp execute in program order, so round j+1 reads what round j
-  // wrote; the only register dependency inside a round is load -> add -> store.
-  unsigned* whist = s_whist + warp * kRadix;
-  unsigned short rank[ITEMS];
-#pragma unroll
-  for (int j = 0; j < ITEMS; ++j) {
-    const unsigned d = digit_of(key[j], shift, mask);
-    const unsigned peers = match_digit(d);
-    const unsigned before = __popc(peers & lanemask_lt());
-    const unsigned old = whist[d];
-    __syncwarp();
-    if (before == 0) whist[d] = old + __popc(peers);
-    __syncwarp();
-    rank[j] = (unsigned short)(old + before);
-  }
-  __syncthreads();
-
-  // ---- per-digit tile totals and warp offsets (thread d owns digit d). The tile's
-  // counts are published BEFORE any local reordering so that successor tiles can
-  // use them while this CTA is still busy.
-  unsigned count = 0;
-  if (threadIdx.x < kRadix) {
-    const unsigned d = threadIdx.x;
+    // ---- per-digit tile totals and warp offsets: thread (g, d) walks the warps of its
+    // group; group totals are combined through shared memory. The tile's counts are
+    // published BEFORE any local reordering so that successor tiles can use them
+    // while this CTA is still busy.
+    const unsigned d_own = threadIdx.x % kRadix;
+    const unsigned grp = threadIdx.x / kRadix;
+    unsigned part = 0;
 #pragma unroll 4
-    for (int w = 0; w < WARPS; ++w) {
-      const unsigned c = s_whist[w * kRadix + d];
-      s_whist[w * kRadix + d] = count;
+    for (int w = 0; w < WARPS_PER_GROUP; ++w) {
+      unsigned* cell = &s_whist[(grp * WARPS_PER_GROUP + w) * kRadix + d_own];
+      const unsigned c = *cell;
+      *cell = part;
+      part += c;
+    }
+    s_part[grp][d_own] = part;
+    __syncthreads();
+    unsigned count = 0, grp_off = 0;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      const unsigned c = s_part[g][d_own];
+      if (g < (int)grp) grp_off += c;
       count += c;
     }
-    if (d == mask) count -= (unsigned)TILE - tile_valid;  // padding carries the largest digit
-    DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
-    if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
-    else           st_desc<DescT>(mine, ((DescT)st_agg << DSH) | count);
-  }
-  // exclusive scan of the 256 tile totals -> first slot of each digit in the sorted tile
-  unsigned incl = count;
-  if (threadIdx.x < kRadix) {
+    if (d_own == mask) count -= (unsigned)TILE - tile_valid;  // padding carries the largest digit
+    if (grp == 0) {
+      DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d_own;
+      if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
+      else           st_desc<DescT>(mine, ((DescT)st_agg << DSH) | count);
+    }
+    // exclusive scan of the 256 tile totals -> first slot of each digit in the sorted tile
+    unsigned incl = count;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const unsigned t = __shfl_up_sync(0xffffffffu, incl, off);
       if (lane >= off) incl += t;
     }
-    if (lane == 31) s_scan[warp] = incl;
-  }
-  __syncthreads();
-  unsigned digit_start = 0;
-  if (threadIdx.x < kRadix) {
-    const unsigned d = threadIdx.x;
-    digit_start = incl - count;
-    for (unsigned w = 0; w < warp; ++w) digit_start += s_scan[w];
+    if (grp == 0 && lane == 31) s_scan[warp] = incl;
+    __syncthreads();
+    unsigned digit_start = incl - count;
+    for (unsigned w = 0; w < (warp % (kRadix / kWarp)); ++w) digit_start += s_scan[w];
+    {
+      const unsigned add = digit_start + grp_off;
 #pragma unroll 4
-    for (int w = 0; w < WARPS; ++w) s_whist[w * kRadix + d] += digit_start;
-  }
-  __syncthreads();
+      for (int w = 0; w < WARPS_PER_GROUP; ++w) s_whist[(grp * WARPS_PER_GROUP + w) * kRadix + d_own] += add;
+    }
+    __syncthreads();
 
-  // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
-#pragma unroll
-  for (int j = 0; j < ITEMS; ++j) {
-    const unsigned d = digit_of(key[j], shift, mask);
-    const unsigned q = whist[d] + rank[j];
-    rank[j] = (unsigned short)q;
-    s_keys[q] = key[j];
-  }
-  if constexpr (VB != 0) {
+    // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned local = warp_off + j * kWarp + lane;
-#ifdef TB200_EARLY_VALUES
-      if (local < tile_valid) s_vals[rank[j]] = val[j];
-#else
-      if (local < tile_valid) s_vals[rank[j]] = src_vals[tile_base + local];
-#endif
+      const unsigned d = digit_of(key[j], shift, mask);
+      const unsigned q = whist[d] + rank[j];
+      rank[j] = (unsigned short)q;
+      s_keys[q] = key[j];
     }
-  }
-
-  // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
-  // fetches kWindow descriptors at once and consumes them nearest first.
-  if (threadIdx.x < kRadix) {
-    const unsigned d = threadIdx.x;
-    unsigned long long excl = 0;
-    if (tile != 0) {
-      constexpr int kWindow = 4;
-      const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
-      const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
-      long long t = (long long)tile - 1;
-      bool timed_out = false, done = false;
-      while (!done && !timed_out) {
-        DescT v[kWindow];
+    // the key registers are free: fetch the next tile's keys now
+    if (next < num_tiles) load_keys(next);
+    if constexpr (VB != 0) {
+      const V* pv = src_vals + tile_base + warp_off + lane;
+      if (tile_valid == (unsigned)TILE) {
+        V val[ITEMS];
 #pragma unroll
-        for (int i = 0; i < kWindow; ++i)
-          v[i] = t - i >= 0 ? ld_desc<DescT>(chain + (size_t)(t - i) * kRadix) : below_first;
+        for (int j = 0; j < ITEMS; ++j) val[j] = pv[j * kWarp];
 #pragma unroll
-        for (int i = 0; i < kWindow; ++i) {
-          if (done || timed_out) break;
-          unsigned polls = 0;
-          while ((unsigned)(v[i] >> DSH) == st_empty) {
-            backoff(++polls);
-            if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
-              timed_out = true;
-              break;
-            }
-            v[i] = ld_desc<DescT>(chain + (size_t)(t - i) * kRadix);
-          }
-          if (timed_out) break;
-          excl += (unsigned long long)(v[i] & DescBits<DescT>::kValueMask);
-          done = (unsigned)(v[i] >> DSH) == st_prefix;
-        }
-        t -= kWindow;
+        for (int j = 0; j < ITEMS; ++j) s_vals[rank[j]] = val[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+          if (warp_off + j * kWarp + lane < tile_valid) s_vals[rank[j]] = pv[j * kWarp];
       }
-      if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
-      DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
-      st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + count) & DescBits<DescT>::kValueMask));
     }
-    s_gbase[d] = ctl->offs[pass][d] + excl - digit_start;
-  }
-  __syncthreads();
 
-  // ---- scatter: every digit leaves as one contiguous run
+    // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
+    // fetches kWindow descriptors at once and consumes them nearest first.
+    if (grp == 0) {
+      const unsigned d = d_own;
+      unsigned long long excl = 0;
+      if (tile != 0) {
+        constexpr int kWindow = 4;
+        const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
+        const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
+        long long t = (long long)tile - 1;
+        bool timed_out = false, done = false;
+        while (!done && !timed_out) {
+          DescT v[kWindow];
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const unsigned pos = threadIdx.x + i * THREADS;
-    if (pos < tile_valid) {
+          for (int i = 0; i < kWindow; ++i)
+            v[i] = t - i >= 0 ? ld_desc<DescT>(chain + (size_t)(t - i) * kRadix) : below_first;
+#pragma unroll
+          for (int i = 0; i < kWindow; ++i) {
+            if (done || timed_out) break;
+            unsigned polls = 0;
+            while ((unsigned)(v[i] >> DSH) == st_empty) {
+              backoff(++polls);
+              if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
+                timed_out = true;
+                break;
+              }
+              v[i] = ld_desc<DescT>(chain + (size_t)(t - i) * kRadix);
+            }
+            if (timed_out) break;
+            excl += (unsigned long long)(v[i] & DescBits<DescT>::kValueMask);
+            done = (unsigned)(v[i] >> DSH) == st_prefix;
+          }
+          t -= kWindow;
+        }
+        if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
+        DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
+        st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + count) & DescBits<DescT>::kValueMask));
+      }
+      s_gbase[d] = (IdxT)(ctl->offs[pass][d] + excl - digit_start);
+    }
+    __syncthreads();
+
+    // ---- scatter: every digit leaves as one contiguous run
+    auto emit = [&](unsigned pos) {
       const UK k = s_keys[pos];
-      const unsigned long long g = s_gbase[digit_of(k, shift, mask)] + pos;
+      const IdxT g = s_gbase[digit_of(k, shift, mask)] + pos;
       dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
       if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
+    };
+    if (tile_valid == (unsigned)TILE) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) emit(threadIdx.x + i * THREADS);
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i)
+        if (threadIdx.x + i * THREADS < tile_valid) emit(threadIdx.x + i * THREADS);
     }
+    if (next >= num_tiles) break;
+    tile = next;
+    __syncthreads();  // shared buffers are reused by the next tile
   }
 }
 
@@ -574,12 +632,17 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.desc = base + lay.desc_off;
   auto launch = [&](auto kernel) -> int {
     TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
+    int per_sm = 0;
+    TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, T::kThreads, Shape::kSmem));
+    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const uint64_t resident = (uint64_t)per_sm * sms;
+    const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
     for (int p = 0; p < num_passes; ++p) {
       prm.pass = p;
       prm.shift = begin_bit + 8 * p;
       const int bits = end_bit - prm.shift < 8 ? end_bit - prm.shift : 8;
       prm.mask = (1u << bits) - 1u;
-      kernel<<<(unsigned)tiles, T::kThreads, Shape::kSmem, stream>>>(prm);
+      kernel<<<grid, T::kThreads, Shape::kSmem, stream>>>(prm);
       trace_mark(stream);
       TB200_CUDA_TRY(cudaGetLastError());
     }
