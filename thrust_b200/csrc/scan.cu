@@ -11,6 +11,8 @@
 // sequential sum only by re-association.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace tb200 {
 namespace {
 
@@ -290,4 +292,55 @@ extern "C" int tb200_scan(void* d_temp, size_t* temp_bytes, const void* d_in, vo
     default:
       return TB200_ERR_UNSUPPORTED;
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// tb200_scan_static: the same scan, with its scratch in a fixed device array
+// ---------------------------------------------------------------------------------------
+namespace tb200 {
+namespace {
+
+// Look-back descriptors of tb200_scan_static. Lives in every GPU that loads this library,
+// from load until the process exits. 1 MiB + header: up to 131072 tiles of a 4-byte type
+// (n <= 2^31 elements) or 65536 tiles of an 8-byte type (n <= 2^29 elements).
+constexpr size_t kStaticScanBytes = kHeaderBytes + (1u << 20);
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scan_mutex;
+void* g_static_scan_ptr[kMaxDevices] = {};
+
+// In host code `g_static_scan_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address is looked up once per device, with that device current.
+int static_scan_scratch(void** out) {
+  int dev = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return TB200_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_scan_mutex);
+  if (g_static_scan_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    TB200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scan_scratch));
+    g_static_scan_ptr[dev] = p;
+  }
+  *out = g_static_scan_ptr[dev];
+  return TB200_OK;
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_scan_static(const void* d_in, void* d_out, uint64_t n, int dtype, int exclusive,
+                                 const void* h_init, tb200_stream_t stream) {
+  using namespace tb200;
+  size_t need = 0;
+  int rc = tb200_scan(nullptr, &need, nullptr, nullptr, n, dtype, exclusive, h_init, stream);
+  if (rc) return rc;
+  if (need > kStaticScanBytes) return TB200_ERR_OVERFLOW;  // n beyond the fixed scratch: use tb200_scan
+  void* scratch = nullptr;
+  rc = static_scan_scratch(&scratch);
+  if (rc) return rc;
+  size_t have = kStaticScanBytes;
+  // tb200_scan clears the part of the scratch it uses (header and descriptors) on `stream`
+  // before the kernel, so what the previous call left behind is never read.
+  return tb200_scan(scratch, &have, d_in, d_out, n, dtype, exclusive, h_init, stream);
 }
