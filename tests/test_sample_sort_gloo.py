@@ -1,0 +1,114 @@
+"""Host-side logic of the sharded sample sort over gloo, world size 2 and 3, on CPU.
+
+The per-shard compute is injected (a numpy `ops` object backed by the CPU oracle), so these
+tests exercise exactly the orchestration the GPU path runs: sampling, splitter choice, the
+count exchange, all-to-all-v sizes, source-rank order of the received runs, the capacity
+check — and compare the concatenated result with a single-process stable sort.
+"""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+class OracleOps:
+    """CPU stand-in for DeviceOps: same methods, numpy + the oracle's radix sort."""
+
+    def __init__(self):
+        import oracle
+        self.chk = oracle.port()
+
+    def sort_pairs(self, keys, vals, n):
+        k = keys[:n].numpy().view(np.uint64)
+        v = vals[:n].numpy().view(np.uint32)
+        self.chk.sort_by_key_inplace(k, v)
+
+    def sort_keys(self, keys):
+        self.chk.sort_inplace(keys.numpy().view(np.uint64))
+
+    def segment_counts(self, sorted_keys, n, splitters):
+        k = sorted_keys[:n].numpy().view(np.uint64)
+        ub = np.searchsorted(k, splitters.numpy().view(np.uint64), side="right")
+        return torch.from_numpy(np.diff(np.concatenate([[0], ub])).astype(np.int64))
+
+    def status(self):
+        return 0
+
+    def release(self):
+        pass
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, n, key_bits, slack, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from thrust_b200.sample_sort import ShardedSorter
+    rng = np.random.default_rng(1234 + rank)
+    keys = rng.integers(0, 1 << key_bits, size=n, dtype=np.uint64) << np.uint64(64 - key_bits)  # spans the sign bit
+    vals = (np.arange(n, dtype=np.uint64) + rank * n).astype(np.uint32)
+    np.save(f"{out_dir}/in_k{rank}.npy", keys)
+    np.save(f"{out_dir}/in_v{rank}.npy", vals)
+    sorter = ShardedSorter(n, torch.device("cpu"), world, rank, ops=OracleOps(), slack=slack)
+    k = torch.from_numpy(keys.view(np.int64).copy())
+    v = torch.from_numpy(vals.view(np.int32).copy())
+    try:
+        ok, ov, m = sorter.sort(k, v)
+        np.save(f"{out_dir}/out_k{rank}.npy", ok[:m].numpy().view(np.uint64))
+        np.save(f"{out_dir}/out_v{rank}.npy", ov[:m].numpy().view(np.uint32))
+        send, recv = sorter.last_counts
+        assert sum(send) == n and sum(recv) == m
+    except OverflowError:
+        Path(f"{out_dir}/overflow{rank}").touch()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _run(world, n, key_bits, slack, tmp_path):
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, n, key_bits, slack, str(tmp_path)), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world,n,key_bits", [(2, 5000, 64), (3, 4099, 64), (2, 3000, 6)])
+def test_sharded_sort_matches_single_process_stable_sort(tmp_path, world, n, key_bits):
+    import oracle
+    oracle.build(ref=False)
+    _run(world, n, key_bits, 1.0 if key_bits < 16 else 1.0 / 8, tmp_path)
+    in_k = np.concatenate([np.load(tmp_path / f"in_k{r}.npy") for r in range(world)])
+    in_v = np.concatenate([np.load(tmp_path / f"in_v{r}.npy") for r in range(world)])
+    out_k = np.concatenate([np.load(tmp_path / f"out_k{r}.npy") for r in range(world)])
+    out_v = np.concatenate([np.load(tmp_path / f"out_v{r}.npy") for r in range(world)])
+    want_k, want_v = oracle.port().sort_by_key(in_k, in_v)
+    assert out_k.tobytes() == want_k.tobytes()
+    assert out_v.tobytes() == want_v.tobytes()  # stability across ranks: lower source rank first
+
+
+def test_receive_overflow_is_an_error_not_a_crash(tmp_path):
+    # all keys equal: everything goes to one rank, which cannot hold it with 1/64 slack
+    _run(2, 4000, 1, 1.0 / 64, tmp_path)
+    assert any((tmp_path / f"overflow{r}").exists() for r in range(2))
+
+
+def test_sample_positions_and_splitters():
+    from thrust_b200.sample_sort import pick_splitters, sample_positions
+    p = sample_positions(1 << 20, 1024)
+    assert p.numel() == 1024 and p[0] == 512 and p[-1] == (1 << 20) - 512 and bool((p[1:] > p[:-1]).all())
+    assert sample_positions(10, 1024).tolist() == list(range(10))
+    assert sample_positions(0, 1024).numel() == 0
+    s = pick_splitters(torch.arange(4096), 4)
+    assert s.tolist() == [1024, 2048, 3072]
+    assert pick_splitters(torch.arange(8), 1).numel() == 0

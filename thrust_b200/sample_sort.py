@@ -10,7 +10,7 @@ The reference has no multi-GPU code at all; this is the sharded form of its
   4. destination d owns keys in (splitter[d-1], splitter[d]]: the send segments are
      contiguous ranges of the sorted shard, found with one upper-bound search per
      splitter (tb200_histogram_sorted) — no data movement
-  5. all-to-all of the G x G count matrix, then all-to-all-v of keys and of values
+  5. all-gather of the G x G count matrix, then all-to-all-v of keys and of values
      over NCCL; received runs are stored in source-rank order
   6. one more local sort of the received pairs. Rank r holds global indices
      [r*n, (r+1)*n), so a stable sort of runs concatenated in source-rank order
@@ -142,15 +142,18 @@ class ShardedSorter:
         # 4. contiguous send segments of the sorted shard
         head = self.ops.segment_counts(keys, n, splitters)
         send = torch.cat([head, (n - head.sum()).reshape(1)])
-        # 5. counts, then payload
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=self.group)
-        both = torch.stack([send, recv]).cpu()
-        send_l, recv_l = both[0].tolist(), both[1].tolist()
+        # 5. the whole G x G count matrix goes to every rank (row r = what rank r sends), so all
+        # ranks take the same decision about receive overflow; then the payload
+        matrix = torch.empty(G * G, dtype=torch.int64, device=self.device)
+        dist.all_gather_into_tensor(matrix, send.contiguous(), group=self.group)
+        mat = matrix.cpu().view(G, G)
+        send_l = mat[self.rank].tolist()
+        recv_l = mat[:, self.rank].tolist()
         m = int(sum(recv_l))
         self.last_counts = (send_l, recv_l)
-        if m > self.capacity:
-            raise OverflowError(f"rank {self.rank}: {m} incoming pairs exceed the receive capacity {self.capacity}")
+        worst = int(mat.sum(dim=0).max())
+        if worst > self.capacity:
+            raise OverflowError(f"{worst} incoming pairs on one rank exceed the receive capacity {self.capacity}")
         dist.all_to_all_single(self.recv_k[:m], keys[:n], recv_l, send_l, group=self.group)
         dist.all_to_all_single(self.recv_v[:m], vals[:n], recv_l, send_l, group=self.group)
         # 6. stable sort of the runs (already in source-rank order)
