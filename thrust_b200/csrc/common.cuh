@@ -89,7 +89,13 @@ __device__ __forceinline__ int ld_relaxed_s32(const int* p) {
 }
 
 __device__ __forceinline__ void backoff(unsigned polls) {
-  if (polls > 16) __nanosleep(polls > 256 ? 256 : 64);
+#if defined(TB200_EXPERIMENT_SLEEP_NS)
+  __nanosleep(TB200_EXPERIMENT_SLEEP_NS);
+#elif !defined(TB200_EXPERIMENT_NO_BACKOFF)
+  // a short sleep from the first retry on: tight polling of the few descriptor lines that
+  // every look-back reads delays the very stores it is waiting for
+  __nanosleep(polls > 256 ? 400 : 100);
+#endif
 }
 
 // Tile descriptors of the decoupled look-back chains. A descriptor is W 64-bit
@@ -133,6 +139,60 @@ __device__ __forceinline__ unsigned peek(const TileWords<W>* d, unsigned (&paylo
     same = same && ((unsigned)(v[i] >> 32) == st);
   }
   return same ? st : kStateEmpty;
+}
+
+// ---- bulk asynchronous copies (the TMA engine's untiled form) and their mbarriers -------
+// One elected thread issues a global -> shared copy of a whole tile; the data lands without
+// occupying registers or load-store slots and completion is signalled on an mbarrier.
+// Source, destination and size must be multiples of 16 bytes. Never used with multicast.
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Orders earlier generic-proxy accesses to shared memory before later async-proxy ones.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Barrier among the first `count` threads of the CTA (count a multiple of 32), id 1..15.
+__device__ __forceinline__ void named_barrier(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait for a bulk load. Returns false (after raising the status word) if the data
+// did not arrive within the limit; the caller carries on without waiting again.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsigned parity, int* status) {
+  for (unsigned spins = 0; spins < (1u << 20); ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 1023u) == 1023u && ld_relaxed_s32(status) != 0) return false;  // someone else gave up
+  }
+  atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+  return false;
 }
 
 #endif  // __CUDACC__

@@ -64,9 +64,10 @@ struct SegWords {
   }
 };
 
-// Look-back of warp 0 over (count, value) descriptors, 64 per round (two per lane,
-// loads in flight together). The operator is not commutative, so far predecessors
-// are combined on the left of near ones.
+// Look-back over (count, value) descriptors by one warp, 32 predecessors per round. The
+// operator is not commutative, so far predecessors are combined on the left of near ones.
+// (Wider windows were measured to be slower: every extra polled descriptor adds traffic
+// on the few cache lines all look-back warps read.)
 template <typename V>
 __device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* status,
                              unsigned long long& out_cnt, V& out_val) {
@@ -76,54 +77,42 @@ __device__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* stat
   long long base = (long long)tile - 1;
   bool timed_out = false;
   while (true) {
-    unsigned st[2] = {kStatePrefix, kStatePrefix};
-    unsigned payload[2][4];
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const long long idx = base - 32 * s - lane;
-      if (idx >= 0) st[s] = peek<4>(&tiles[idx], payload[s]);
-    }
-    bool found = false;
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      if (found) break;
-      const long long idx = base - 32 * s - lane;
-      unsigned long long cnt = 0;
-      V val = V(0);
-      if (idx >= 0) {
-        unsigned polls = 0;
-        while (st[s] == kStateEmpty) {
-          backoff(++polls);
-          if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
-            timed_out = true;
-            st[s] = kStatePrefix;
-            break;
-          }
-          st[s] = peek<4>(&tiles[idx], payload[s]);
-        }
-        if (!timed_out) SegWords<V>::unpack(payload[s], cnt, val);
-      }
-      const unsigned pm = __ballot_sync(0xffffffffu, st[s] == kStatePrefix);
-      const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
-      if (lane > first) { cnt = 0; val = V(0); }
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
-        const V ov = __shfl_down_sync(0xffffffffu, val, off);
-        if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val)
-          val = cnt ? val : ov + val;
-          cnt = oc + cnt;
+    const long long idx = base - lane;
+    unsigned st = kStatePrefix;
+    unsigned long long cnt = 0;
+    V val = V(0);
+    if (idx >= 0) {
+      unsigned payload[4];
+      unsigned polls = 0;
+      while ((st = peek<4>(&tiles[idx], payload)) == kStateEmpty) {
+        backoff(++polls);
+        if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+          timed_out = true;
+          st = kStatePrefix;
+          break;
         }
       }
-      cnt = __shfl_sync(0xffffffffu, cnt, 0);
-      val = __shfl_sync(0xffffffffu, val, 0);
-      // this window lies to the left of everything accumulated so far
-      acc_val = acc_cnt ? acc_val : val + acc_val;
-      acc_cnt = cnt + acc_cnt;
-      found = pm != 0;
+      if (!timed_out) SegWords<V>::unpack(payload, cnt, val);
     }
-    if (found) break;
-    base -= 64;
+    const unsigned pm = __ballot_sync(0xffffffffu, st == kStatePrefix);
+    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+    if (lane > first) { cnt = 0; val = V(0); }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
+      const V ov = __shfl_down_sync(0xffffffffu, val, off);
+      if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val)
+        val = cnt ? val : ov + val;
+        cnt = oc + cnt;
+      }
+    }
+    cnt = __shfl_sync(0xffffffffu, cnt, 0);
+    val = __shfl_sync(0xffffffffu, val, 0);
+    // this window lies to the left of everything accumulated so far
+    acc_val = acc_cnt ? acc_val : val + acc_val;
+    acc_cnt = cnt + acc_cnt;
+    if (pm) break;
+    base -= 32;
   }
   if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
   out_cnt = acc_cnt;
@@ -278,20 +267,306 @@ reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* 
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Streaming variant (16-byte aligned inputs): the structure of the streaming scan kernel.
+// Persistent CTAs, one per SM, 16 compute warps + two look-back warps; a ring of four slots,
+// each holding one tile of keys and one of values, filled by bulk asynchronous copies.
+// Thread t owns 3*E consecutive elements of the tile (48 bytes of the wider type: a
+// bank-conflict-free stride), so head flags need one shuffle and the tile-local
+// segmented scan one warp scan. Every value is then replaced in place by the sum of its
+// run so far (exclusive, tile-local) and the tile stays parked for two iterations while the
+// look-back warp resolves its prefix; the compute warps finally emit the parked tile's runs.
+// ---------------------------------------------------------------------------------------
+constexpr int kRsThreads = 512;
+constexpr int kRsWarps = kRsThreads / kWarp;
+constexpr int kRsLookWarps = 2;  // look-back warps; tile j of a CTA is resolved by warp j % 2
+constexpr int kRsCta = kRsThreads + kRsLookWarps * kWarp;
+constexpr int kRsPacks = 3;  // packs of E elements per thread
+constexpr int kRsPark = 2;
+constexpr int kRsStages = kRsPark + 2;
+constexpr unsigned kRsNoTile = 0xffffffffu;
+
+template <typename K, typename V>
+struct RsShape {
+  static constexpr int E = 16 / (sizeof(K) > sizeof(V) ? sizeof(K) : sizeof(V));
+  static constexpr int kItems = kRsPacks * E;
+  static constexpr int kTile = kRsThreads * kItems;
+  static constexpr int kKeyBytes = kTile * (int)sizeof(K);
+  static constexpr int kValBytes = kTile * (int)sizeof(V);
+  static constexpr int kSlotBytes = ((kKeyBytes + 127) / 128) * 128 + ((kValBytes + 127) / 128) * 128;
+  static constexpr int kValOffset = ((kKeyBytes + 127) / 128) * 128;
+  static constexpr int kSmem = kRsStages * kSlotBytes;
+};
+
+template <typename K, typename V>
+__global__ void __launch_bounds__(kRsCta, 1)
+rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __restrict__ keys_out,
+                  V* __restrict__ vals_out, unsigned long long* __restrict__ num_runs, uint64_t n,
+                  unsigned num_tiles, TempHeader* hdr, TileWords<4>* tiles) {
+  using Shape = RsShape<K, V>;
+  constexpr int E = Shape::E;
+  constexpr int P = kRsPacks;
+  constexpr int ITEMS = Shape::kItems;
+  constexpr int TILE = Shape::kTile;
+  constexpr int S = kRsStages;
+
+  extern __shared__ __align__(128) unsigned char ring[];
+  __shared__ __align__(8) unsigned long long s_full[S], s_handoff[S], s_resolved[S];
+  __shared__ unsigned s_tile[S], s_look_tile[S], s_look_cnt[S];
+  __shared__ V s_look_val[S];
+  __shared__ unsigned long long s_prefix_cnt[S];
+  __shared__ V s_prefix_val[S];
+  __shared__ unsigned short s_park_cnt[S][kRsThreads];
+  __shared__ unsigned short s_park_heads[S][kRsThreads];
+  __shared__ unsigned s_warp_cnt[kRsWarps];
+  __shared__ V s_warp_val[kRsWarps];
+
+  const unsigned warp = threadIdx.x / kWarp;
+  const unsigned lane = lane_id();
+  int* status = &hdr->status;
+  auto slot_keys = [&](int slot) { return reinterpret_cast<K*>(ring + (size_t)slot * Shape::kSlotBytes); };
+  auto slot_vals = [&](int slot) {
+    return reinterpret_cast<V*>(ring + (size_t)slot * Shape::kSlotBytes + Shape::kValOffset);
+  };
+
+  const unsigned first_dynamic = S * gridDim.x;
+  unsigned pending = 0;
+  auto start_load = [&](int slot, unsigned t) {
+    s_tile[slot] = t;
+    if (t < num_tiles && (uint64_t)(t + 1) * TILE <= n) {
+      fence_proxy_async_smem();  // the slot was last touched by ordinary loads and stores
+      mbar_expect_tx(&s_full[slot], Shape::kKeyBytes + Shape::kValBytes);
+      bulk_load(slot_keys(slot), keys + (uint64_t)t * TILE, Shape::kKeyBytes, &s_full[slot]);
+      bulk_load(slot_vals(slot), vals + (uint64_t)t * TILE, Shape::kValBytes, &s_full[slot]);
+    }
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_handoff[s], 1);
+      mbar_init(&s_resolved[s], 1);
+    }
+    mbar_init_fence();
+    for (int s = 0; s < S; ++s) start_load(s, s * gridDim.x + blockIdx.x);
+    pending = first_dynamic + atomicAdd(&hdr->ticket, 1u);
+  }
+  __syncthreads();
+
+  // ------------------------------------------------------------------ look-back warps
+  // One look-back takes longer than the compute warps need for a tile, so two warps take
+  // turns; each resolves its tiles independently of the other.
+  if (warp >= kRsWarps) {
+    for (unsigned j = warp - kRsWarps;; j += kRsLookWarps) {
+      const int slot = j % S;
+      if (!mbar_wait_bounded(&s_handoff[slot], (j / S) & 1u, status)) break;
+      const unsigned tile = s_look_tile[slot];
+      if (tile == kRsNoTile) break;
+      const unsigned tot_cnt = s_look_cnt[slot];
+      const V tot_val = s_look_val[slot];
+      unsigned long long pc = 0;
+      V pv = V(0);
+      if (tile != 0) lookback_seg<V>(tiles, tile, status, pc, pv);
+      if (lane == 0) {
+        const unsigned long long ic = pc + tot_cnt;
+        const V iv = tot_cnt ? tot_val : pv + tot_val;
+        unsigned payload[4];
+        SegWords<V>::pack(ic, iv, payload);
+        publish<4>(&tiles[tile], kStatePrefix, payload);
+        if (tile == num_tiles - 1) {  // close the last run and report the count
+          if (ic > 0) vals_out[ic - 1] = iv;
+          *num_runs = ic;
+        }
+        s_prefix_cnt[slot] = pc;
+        s_prefix_val[slot] = pv;
+        mbar_arrive(&s_resolved[slot]);
+      }
+      __syncwarp();
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ compute warps
+  // emits the runs that close inside the tile parked at iteration it_prev (each thread
+  // re-reads only what it parked itself)
+  auto finalize = [&](unsigned it_prev, bool refill) {
+    const int slot = it_prev % S;
+    mbar_wait_bounded(&s_resolved[slot], (it_prev / S) & 1u, status);
+    const unsigned heads = s_park_heads[slot][threadIdx.x];
+    if (heads) {
+      const unsigned long long pc = s_prefix_cnt[slot];
+      const V pv = s_prefix_val[slot];
+      const Pack<K, E>* pk = reinterpret_cast<const Pack<K, E>*>(slot_keys(slot)) + threadIdx.x * P;
+      const Pack<V, E>* pr = reinterpret_cast<const Pack<V, E>*>(slot_vals(slot)) + threadIdx.x * P;
+      unsigned cnt = s_park_cnt[slot][threadIdx.x];
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        if ((heads >> (p * E)) & ((1u << E) - 1u)) {
+          const Pack<K, E> kk = pk[p];
+          const Pack<V, E> rr = pr[p];
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            if (heads & (1u << (p * E + e))) {
+              const unsigned long long at = pc + cnt;
+              if (at > 0) vals_out[at - 1] = cnt ? rr.v[e] : pv + rr.v[e];
+              keys_out[at] = kk.v[e];
+              ++cnt;
+            }
+          }
+        }
+      }
+    }
+    if (refill) {
+      named_barrier(1, kRsThreads);  // the slot has been read by every compute thread
+      if (threadIdx.x == 0) {
+        start_load(slot, pending);
+        pending = first_dynamic + atomicAdd(&hdr->ticket, 1u);
+      }
+    }
+  };
+
+  unsigned it = 0;
+  for (;; ++it) {
+    const int slot = it % S;
+    const unsigned tile = s_tile[slot];
+    if (tile >= num_tiles) break;
+    const uint64_t tile_base = (uint64_t)tile * TILE;
+    const uint64_t my_base = tile_base + (uint64_t)threadIdx.x * ITEMS;
+    const bool full = tile_base + TILE <= n;
+    Pack<K, E>* mk = reinterpret_cast<Pack<K, E>*>(slot_keys(slot)) + threadIdx.x * P;
+    Pack<V, E>* mv = reinterpret_cast<Pack<V, E>*>(slot_vals(slot)) + threadIdx.x * P;
+
+    K k[ITEMS];
+    V v[ITEMS];
+    if (full) {
+      mbar_wait_bounded(&s_full[slot], (it / S) & 1u, status);
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        const Pack<K, E> kk = mk[p];
+        const Pack<V, E> vv = mv[p];
+#pragma unroll
+        for (int e = 0; e < E; ++e) { k[p * E + e] = kk.v[e]; v[p * E + e] = vv.v[e]; }
+      }
+    } else {
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        Pack<K, E> kk;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const uint64_t i = my_base + p * E + e;
+          k[p * E + e] = i < n ? keys[i] : K(0);
+          v[p * E + e] = i < n ? vals[i] : V(0);
+          kk.v[e] = k[p * E + e];
+        }
+        mk[p] = kk;  // the final pass reads keys from the slot
+      }
+    }
+    // key in front of this thread's run of elements
+    K prev = __shfl_up_sync(0xffffffffu, k[ITEMS - 1], 1);
+    if (lane == 0) prev = (my_base > 0 && my_base <= n) ? keys[my_base - 1] : K(0);
+
+    // head flags; full tiles need no bounds checks (only element 0 of the array is special)
+    unsigned heads = 0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) heads |= (unsigned)!(k[i] == (i == 0 ? prev : k[i - 1])) << i;
+      if (my_base == 0) heads |= 1u;
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) {
+        const uint64_t g = my_base + i;
+        const bool head = g < n && (g == 0 || !(k[i] == (i == 0 ? prev : k[i - 1])));
+        heads |= (unsigned)head << i;
+      }
+    }
+    // one pass of run sums inside the thread: incl[i] = sum of element i's run so far,
+    // counted from the thread's first element
+    V incl[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i)
+      incl[i] = (i == 0 || (heads & (1u << i))) ? v[i] : incl[i - 1] + v[i];
+    Seg<V> s{(unsigned)__popc(heads), incl[ITEMS - 1]};
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      Seg<V> o;
+      o.cnt = __shfl_up_sync(0xffffffffu, s.cnt, off);
+      o.val = __shfl_up_sync(0xffffffffu, s.val, off);
+      if (lane >= off) s = seg_combine(o, s);
+    }
+    Seg<V> lane_excl;
+    lane_excl.cnt = __shfl_up_sync(0xffffffffu, s.cnt, 1);
+    lane_excl.val = __shfl_up_sync(0xffffffffu, s.val, 1);
+    if (lane == 0) { lane_excl.cnt = 0; lane_excl.val = V(0); }
+    if (lane == 31) { s_warp_cnt[warp] = s.cnt; s_warp_val[warp] = s.val; }
+    named_barrier(1, kRsThreads);
+
+    Seg<V> warp_prefix{0u, V(0)}, tile_total{0u, V(0)};
+#pragma unroll
+    for (int w = 0; w < kRsWarps; ++w) {
+      const Seg<V> t{s_warp_cnt[w], s_warp_val[w]};
+      if (w < (int)warp) warp_prefix = seg_combine(warp_prefix, t);
+      tile_total = seg_combine(tile_total, t);
+    }
+    if (threadIdx.x == 0) {
+      if (tile != 0) {
+        unsigned payload[4];
+        SegWords<V>::pack(tile_total.cnt, tile_total.val, payload);
+        publish<4>(&tiles[tile], kStateAggregate, payload);
+      }
+      s_look_tile[slot] = tile;
+      s_look_cnt[slot] = tile_total.cnt;
+      s_look_val[slot] = tile_total.val;
+      mbar_arrive(&s_handoff[slot]);
+    }
+    // park: every value is replaced by the (tile-local, exclusive) sum of its run so far.
+    // Up to and including the thread's first head the open run began before this thread.
+    {
+      const Seg<V> local = seg_combine(warp_prefix, lane_excl);
+      s_park_heads[slot][threadIdx.x] = (unsigned short)heads;
+      s_park_cnt[slot][threadIdx.x] = (unsigned short)local.cnt;
+      const int first_head = heads ? __ffs(heads) - 1 : ITEMS;
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        Pack<V, E> rr;
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int i = p * E + e;
+          const V own = i == 0 ? V(0) : incl[i - 1];
+          rr.v[e] = i <= first_head ? local.val + own : own;
+        }
+        mv[p] = rr;
+      }
+    }
+    if (it >= (unsigned)kRsPark) finalize(it - kRsPark, true);
+    else named_barrier(1, kRsThreads);  // s_warp_* are rewritten by the next tile
+  }
+#pragma unroll
+  for (int p = kRsPark; p >= 1; --p)
+    if (it >= (unsigned)p) finalize(it - p, false);
+  if (threadIdx.x == 0) {  // release the look-back warps (the next kRsLookWarps hand-offs)
+    for (unsigned j = it; j < it + kRsLookWarps; ++j) {
+      const int slot = j % S;
+      s_look_tile[slot] = kRsNoTile;
+      mbar_arrive(&s_handoff[slot]);
+    }
+  }
+}
+
 template <typename K, typename V>
 int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vin, void* kout, void* vout,
                uint64_t* d_num_runs, uint64_t n, cudaStream_t stream) {
   constexpr int E = 16 / (sizeof(K) > sizeof(V) ? sizeof(K) : sizeof(V));
   constexpr uint64_t TILE = (uint64_t)kRbkThreads * kRbkChunks * E;
+  constexpr uint64_t STREAM_TILE = RsShape<K, V>::kTile;  // the smaller tile sizes the scratch
   const uint64_t tiles = (n + TILE - 1) / TILE;
-  const size_t need = kHeaderBytes + (size_t)tiles * sizeof(TileWords<4>);
+  const uint64_t stream_tiles = (n + STREAM_TILE - 1) / STREAM_TILE;
+  const size_t need = kHeaderBytes + (size_t)stream_tiles * sizeof(TileWords<4>);
   if (d_temp == nullptr) {
     *temp_bytes = need;
     return TB200_OK;
   }
   if (*temp_bytes < need) return TB200_ERR_TEMP_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(d_temp) % 256) return TB200_ERR_INVALID_ARGUMENT;
-  if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
+  if (stream_tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
   if (d_num_runs == nullptr || reinterpret_cast<uintptr_t>(d_num_runs) % 8) return TB200_ERR_INVALID_ARGUMENT;
   TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, need, stream));
   TB200_CUDA_TRY(cudaMemsetAsync(d_num_runs, 0, sizeof(uint64_t), stream));
@@ -301,8 +576,26 @@ int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
   auto* desc = reinterpret_cast<TileWords<4>*>(static_cast<char*>(d_temp) + kHeaderBytes);
   const bool aligned = reinterpret_cast<uintptr_t>(kin) % (sizeof(K) * E) == 0 &&
                        reinterpret_cast<uintptr_t>(vin) % (sizeof(V) * E) == 0;
-  const dim3 grid((unsigned)tiles), block(kRbkThreads);
   auto* nr = reinterpret_cast<unsigned long long*>(d_num_runs);
+  const bool aligned16 = (reinterpret_cast<uintptr_t>(kin) | reinterpret_cast<uintptr_t>(vin)) % 16 == 0;
+  if (aligned16 && stream_tiles >= 8) {
+    int dev = 0, sms = 0, per_sm = 0;
+    TB200_CUDA_TRY(cudaGetDevice(&dev));
+    TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    auto kernel = rbk_stream_kernel<K, V>;
+    constexpr int smem = RsShape<K, V>::kSmem;
+    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRsCta, smem));
+    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const uint64_t resident = (uint64_t)sms * per_sm;  // all CTAs resident: the first tiles are dealt statically
+    const unsigned sgrid = (unsigned)(stream_tiles < resident ? stream_tiles : resident);
+    kernel<<<sgrid, kRsCta, smem, stream>>>(static_cast<const K*>(kin), static_cast<const V*>(vin),
+                                            static_cast<K*>(kout), static_cast<V*>(vout), nr, n,
+                                            (unsigned)stream_tiles, hdr, desc);
+    trace_mark(stream);
+    return (int)cudaGetLastError();
+  }
+  const dim3 grid((unsigned)tiles), block(kRbkThreads);
   if (aligned)
     reduce_by_key_kernel<K, V, true><<<grid, block, 0, stream>>>(
         static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout), static_cast<V*>(vout), nr,
