@@ -169,7 +169,7 @@ def run_reference(args, rank: int):
 def workload_config(n_gpus: int):
     return {
         "workload": f"sharded stable sort_by_key, 2^{PER_GPU_LOG2} (uint64 key, uint32 value=global index) pairs per GPU, "
-                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: local sort, regular-sample splitters, NCCL all-to-all, final local sort'}",
+                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: regular-sample splitters, stable partition, exchange over NVLink (peer-load gather kernel, or NCCL all-to-all), one local onesweep sort'}",
         "pairs_per_gpu": 1 << PER_GPU_LOG2, "total_pairs": n_gpus << PER_GPU_LOG2,
         "l2_policy": "inputs (12 GiB per GPU) larger than L2; input restored by a device copy between steps",
     }
@@ -334,6 +334,7 @@ def main():
 
     step_ms, trace_ms = [], []
     ms_buf = (C.c_float * 64)()
+    kind_buf = (C.c_int * 64)()
     for i in range(args.warmup):
         k.copy_(k0); v.copy_(v0)
         sorter.sort(k, v)
@@ -349,11 +350,13 @@ def main():
             out_k, out_v, out_n = sorter.sort(k, v)
             b.record(stream)
             b.synchronize()
-            cnt = capi.lib.tb200_trace_end(ms_buf, 64)
+            cnt = capi.lib.tb200_trace_end(ms_buf, kind_buf, 64)
             step_ms.append(a.elapsed_time(b))
-            trace_ms.append([ms_buf[j] for j in range(max(cnt, 0))])
+            trace_ms.append([(kind_buf[j], ms_buf[j]) for j in range(max(min(cnt, 64), 0))])
         barrier()
     sorter.check_status()
+    phases = sorter.phase_times()
+    sorter_exchange = sorter.exchange
     ok = sorter.verify(out_k, out_v, out_n)
 
     t = torch.tensor(step_ms, dtype=torch.float64, device=dev)
@@ -364,13 +367,15 @@ def main():
     total_pairs = n * world
     value = total_pairs / (ms_per_step * 1e-3) / 1e9
 
-    # dominant kernel: one onesweep pass over the local shard. The first local sort of a
-    # step launches histogram, 8 passes, copy-back, so launches 1..8 are the passes.
-    pass_ms = [x for tr in trace_ms for x in tr[1:9]]
+    # dominant kernel: one onesweep radix pass (trace kind 2) over this rank's pairs. At N > 1 the
+    # passes run over the received pairs (about n of them), so n is used for every launch.
+    pass_ms = [ms for tr in trace_ms for kind, ms in tr if kind == 2]
     avg_pass = sum(pass_ms) / max(len(pass_ms), 1)
     pass_bytes = n * 2.0 * (8 + 4)
     achieved = pass_bytes / (avg_pass * 1e-3) / 1e9 if avg_pass > 0 else 0.0
     tpp = traffic_per_pair()
+    sort_ms = [sum(ms for kind, ms in tr if kind in (1, 2, 3)) for tr in trace_ms]
+    whole = (256.0 * n) / (sum(sort_ms) / max(len(sort_ms), 1) * 1e-3) / 1e9 if sort_ms and sort_ms[0] > 0 else None
     roofline = {
         "bound": "hbm", "kernel": "onesweep_kernel<u64 key, 4-byte value>", "achieved": achieved, "peak": peak,
         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
@@ -378,12 +383,10 @@ def main():
         "avg_launch_ms": avg_pass, "launches_timed": len(pass_ms),
         "whole_sort_3touch": {
             "bytes_per_pair": 256, "model": "8 passes x (2 reads + 1 write of an 8 B key, 1 read + 1 write of a 4 B value)",
-            "achieved": (256.0 * n) / (sum(sum(tr[:10]) for tr in trace_ms) / max(len(trace_ms), 1) * 1e-3) / 1e9
-            if trace_ms and trace_ms[0] else None,
+            "achieved": whole, "frac": None if whole is None else whole / peak,
+            "note": "local sort only (histogram + 8 passes + copy-back launches)",
         },
     }
-    if roofline["whole_sort_3touch"]["achieved"]:
-        roofline["whole_sort_3touch"]["frac"] = roofline["whole_sort_3touch"]["achieved"] / peak
     launches = sum(len(tr) for tr in trace_ms)
 
     del k0, v0, k, v, out_k, out_v
@@ -401,6 +404,9 @@ def main():
         "verified": bool(ok), "clocks": clocks.summary(), "roofline": roofline, "gpu_launches": launches,
         "e2e": e2e,
     }
+    if world > 1:
+        line["phases_ms_rank0_last_step"] = phases
+        line["config"]["exchange"] = sorter_exchange
     if rank == 0 and world == 1:
         if not args.no_cpu:
             line["cpu_baseline"], _ = cpu_sort_sample(25, 3, 1)

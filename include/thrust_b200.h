@@ -63,6 +63,32 @@ int tb200_radix_sort(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_val
                      int key_dtype, int val_bytes, int descending, int begin_bit, int end_bit,
                      tb200_stream_t stream);
 
+/* ---- stable multi-way partition -------------------------------------------------------
+ * Scatters n (key, value) pairs into num_splitters + 1 contiguous buckets of d_keys_out /
+ * d_vals_out, keeping input order inside a bucket: bucket b holds the keys in
+ * (splitter[b-1], splitter[b]] (unsigned comparison; splitters ascending, at most 255).
+ * d_counts (device, num_splitters + 1 x uint64) receives the bucket sizes. key_dtype U32 or
+ * U64, val_bytes 0, 4 or 8; outputs must not overlap inputs. One onesweep pass whose digit
+ * is the bucket id. It is the partition step of the sharded sample sort; the reference's
+ * closest algorithm is the two-way thrust::stable_partition (cuda/detail/partition.h:138),
+ * it has no multi-way form. */
+int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                    void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
+                    const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
+                    tb200_stream_t stream);
+
+/* ---- segment gather (exchange step of the sharded sort) ---------------------------------
+ * Concatenates num_segments (at most 16) source ranges into d_dst, in order: segment s is
+ * h_count[s] elements of elem_bytes (4, 8 or 16) starting h_src_offset[s] elements into
+ * h_src[s]. The three arrays are HOST arrays; the source pointers are device pointers and may
+ * be peer mappings of other GPUs' memory (the caller establishes the mapping and the
+ * ordering against the peers' writes). One kernel of plain loads and stores: each GPU pulls
+ * its runs over NVLink itself instead of calling a collective. No counterpart in the
+ * reference (it has no multi-GPU code). */
+int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
+                          const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
+                          tb200_stream_t stream);
+
 /* ---- scan ---------------------------------------------------------------------------
  * Prefix sum with plus over n elements of dtype in {I32,U32,I64,U64,F32,F64}; accumulator
  * type == element type. exclusive == 0: inclusive_scan. exclusive != 0: exclusive_scan
@@ -125,11 +151,12 @@ int tb200_temp_status(const void* d_temp, tb200_stream_t stream);
  * (thrust/system/cuda/detail/core/agent_launcher.h:501-560) without a sync per launch:
  * between tb200_trace_begin and tb200_trace_end every kernel this library launches from
  * the calling thread is followed by an event record on its stream. tb200_trace_end
- * synchronises, writes the device time of launch i (milliseconds) to ms[i] for
- * i < capacity and returns the number of launches (negative: -cudaError_t). Sort
- * launches are, in order: histogram, one per radix pass, copy-back. */
+ * synchronises, writes the device time of launch i (milliseconds) to ms[i] and what it was
+ * to kinds[i] (may be NULL) for i < capacity and returns the number of launches (negative:
+ * -cudaError_t). kinds: 1 sort histogram, 2 radix pass, 3 sort copy-back, 4 scan,
+ * 5 reduce_by_key, 6 histogram of sorted data, 7 partition histogram, 8 partition pass. */
 int tb200_trace_begin(tb200_stream_t stream);
-int tb200_trace_end(float* ms, int capacity);
+int tb200_trace_end(float* ms, int* kinds, int capacity);
 
 /* ---- workspace pool -----------------------------------------------------------------
  * The reference allocates and frees scratch with cudaMalloc/cudaFree inside every call

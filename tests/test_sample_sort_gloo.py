@@ -40,6 +40,15 @@ class OracleOps:
         ub = np.searchsorted(k, splitters.numpy().view(np.uint64), side="right")
         return torch.from_numpy(np.diff(np.concatenate([[0], ub])).astype(np.int64))
 
+    def partition(self, keys, vals, n, splitters, out_k, out_v):
+        k = keys[:n].numpy().view(np.uint64)
+        sp = splitters.numpy().view(np.uint64)
+        bucket = np.searchsorted(sp, k, side="left")  # number of splitters strictly below the key
+        order = np.argsort(bucket, kind="stable")
+        out_k[:n] = torch.from_numpy(k[order].view(np.int64))
+        out_v[:n] = torch.from_numpy(vals[:n].numpy()[order])
+        return torch.from_numpy(np.bincount(bucket, minlength=sp.size + 1).astype(np.int64))
+
     def status(self):
         return 0
 
@@ -53,7 +62,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, n, key_bits, slack, out_dir):
+def _worker(rank, world, port, n, key_bits, slack, out_dir, pipeline="partition_first"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -63,7 +72,7 @@ def _worker(rank, world, port, n, key_bits, slack, out_dir):
     vals = (np.arange(n, dtype=np.uint64) + rank * n).astype(np.uint32)
     np.save(f"{out_dir}/in_k{rank}.npy", keys)
     np.save(f"{out_dir}/in_v{rank}.npy", vals)
-    sorter = ShardedSorter(n, torch.device("cpu"), world, rank, ops=OracleOps(), slack=slack)
+    sorter = ShardedSorter(n, torch.device("cpu"), world, rank, ops=OracleOps(), slack=slack, pipeline=pipeline)
     k = torch.from_numpy(keys.view(np.int64).copy())
     v = torch.from_numpy(vals.view(np.int32).copy())
     try:
@@ -78,16 +87,18 @@ def _worker(rank, world, port, n, key_bits, slack, out_dir):
     dist.destroy_process_group()
 
 
-def _run(world, n, key_bits, slack, tmp_path):
+def _run(world, n, key_bits, slack, tmp_path, pipeline="partition_first"):
     port = _free_port()
-    mp.spawn(_worker, args=(world, port, n, key_bits, slack, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, n, key_bits, slack, str(tmp_path), pipeline), nprocs=world, join=True)
 
 
-@pytest.mark.parametrize("world,n,key_bits", [(2, 5000, 64), (3, 4099, 64), (2, 3000, 6)])
-def test_sharded_sort_matches_single_process_stable_sort(tmp_path, world, n, key_bits):
+@pytest.mark.parametrize("world,n,key_bits,pipeline", [(2, 5000, 64, "partition_first"), (3, 4099, 64, "partition_first"),
+                                                       (2, 3000, 6, "partition_first"), (2, 5000, 64, "sort_first"),
+                                                       (3, 3000, 6, "sort_first")])
+def test_sharded_sort_matches_single_process_stable_sort(tmp_path, world, n, key_bits, pipeline):
     import oracle
     oracle.build(ref=False)
-    _run(world, n, key_bits, 1.0 if key_bits < 16 else 1.0 / 8, tmp_path)
+    _run(world, n, key_bits, 1.0 if key_bits < 16 else 1.0 / 4, tmp_path, pipeline)
     in_k = np.concatenate([np.load(tmp_path / f"in_k{r}.npy") for r in range(world)])
     in_v = np.concatenate([np.load(tmp_path / f"in_v{r}.npy") for r in range(world)])
     out_k = np.concatenate([np.load(tmp_path / f"out_k{r}.npy") for r in range(world)])

@@ -198,3 +198,60 @@ def test_sort_rejects_bad_arguments(cuda_device):
     k = torch.zeros(1000, dtype=torch.int32, device="cuda:0")
     assert capi.lib.tb200_radix_sort(C.c_void_p(t.data_ptr()), C.byref(small), C.c_void_p(k.data_ptr()), None, 1000,
                                      capi.I32, 0, 0, 0, 32, None) == capi.ERR_TEMP_TOO_SMALL
+
+
+@pytest.mark.parametrize("kdtype,vdtype", [(np.uint64, np.uint32), (np.uint32, None), (np.uint64, np.uint64)])
+def test_partition_by_splitters_is_stable(cuda_device, kdtype, vdtype):
+    """tb200_partition against a numpy stable partition: bucket b = keys in (s[b-1], s[b]]."""
+    import ctypes as C
+    rng = np.random.default_rng(4242)
+    kcode = capi.U64 if kdtype == np.uint64 else capi.U32
+    for n, ns in [(0, 3), (1, 1), (5000, 0), (6144, 7), (100003, 7), (300007, 31), (70001, 255)]:
+        k = random_keys(rng, n, kdtype, bits=20 if ns < 100 else None)
+        sp = np.sort(random_keys(rng, ns, kdtype, bits=20 if ns < 100 else None))
+        v = None if vdtype is None else rng.integers(0, 1 << 31, size=n).astype(vdtype)
+        dk, dsp = to_device(k), to_device(sp) if ns else torch.empty(0, dtype=torch.int64, device="cuda:0")
+        ok = torch.empty_like(dk)
+        dv = to_device(v) if v is not None else None
+        ov = torch.empty_like(dv) if dv is not None else None
+        counts = torch.zeros(ns + 1, dtype=torch.int64, device="cuda:0")
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        vb = 0 if v is None else v.dtype.itemsize
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_partition(None, C.byref(need), None, None, None, None, n, kcode, vb, None, ns, None,
+                                            stream), "size")
+        temp = torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda:0")
+        capi.check(capi.lib.tb200_partition(
+            C.c_void_p(temp.data_ptr()), C.byref(need), C.c_void_p(dk.data_ptr()),
+            C.c_void_p(dv.data_ptr()) if dv is not None else None, C.c_void_p(ok.data_ptr()),
+            C.c_void_p(ov.data_ptr()) if ov is not None else None, n, kcode, vb,
+            C.c_void_p(dsp.data_ptr()) if ns else None, ns, C.c_void_p(counts.data_ptr()), stream), "tb200_partition")
+        capi.check(capi.lib.tb200_temp_status(C.c_void_p(temp.data_ptr()), stream), "status")
+        bucket = np.searchsorted(sp, k, side="left")
+        order = np.argsort(bucket, kind="stable")
+        assert counts.cpu().numpy().tolist() == np.bincount(bucket, minlength=ns + 1).tolist(), (n, ns)
+        assert to_host(ok, kdtype).tobytes() == k[order].tobytes(), (n, ns)
+        if v is not None:
+            assert to_host(ov, vdtype).tobytes() == v[order].tobytes(), (n, ns)
+
+
+@pytest.mark.parametrize("dtype", [np.uint64, np.uint32])
+def test_gather_segments_concatenates_ranges(cuda_device, dtype):
+    """tb200_gather_segments on local pointers: odd offsets and lengths, empty segments."""
+    import ctypes as C
+    rng = np.random.default_rng(77)
+    srcs = [rng.integers(0, 1 << 31, size=m).astype(dtype) for m in (100003, 5, 70001, 1 << 16)]
+    devs = [to_device(a, offset_elems=i % 2) for i, a in enumerate(srcs)]
+    offs = [3, 0, 12345, 1]
+    cnts = [99999, 0, 40001, (1 << 16) - 1]
+    want = np.concatenate([a[o:o + c] for a, o, c in zip(srcs, offs, cnts)])
+    dst = torch.zeros(want.size + 1, dtype=torch.int64 if dtype == np.uint64 else torch.int32, device="cuda:0")[1:]
+    g = len(srcs)
+    ptrs = (C.c_void_p * g)(*[d.data_ptr() for d in devs])
+    o = (C.c_uint64 * g)(*offs)
+    c = (C.c_uint64 * g)(*cnts)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, o, c, g, np.dtype(dtype).itemsize,
+                                              stream), "tb200_gather_segments")
+    torch.cuda.synchronize()
+    assert to_host(dst, dtype).tobytes() == want.tobytes()

@@ -42,7 +42,7 @@ int launch_hist(const void* d_sorted, uint64_t n, const void* d_bins, uint32_t n
   const unsigned grid = (num_bins + kHistThreads - 1) / kHistThreads;
   histogram_sorted_kernel<T><<<grid, kHistThreads, 0, stream>>>(static_cast<const T*>(d_sorted), n,
                                                                  static_cast<const T*>(d_bins), num_bins, d_counts);
-  trace_mark(stream);
+  trace_mark(stream, kTraceHistogramSorted);
   return (int)cudaGetLastError();
 }
 

@@ -206,6 +206,8 @@ struct PassParams {
   Encoding enc;
   SortCtl* ctl;
   void* desc;
+  const void* splitters;   // partition mode: ascending splitters (device), else unused
+  unsigned num_splitters;
 };
 
 template <typename DescT> struct DescBits;
@@ -263,7 +265,9 @@ struct PassShape {
 // tile is taken one iteration ahead and its keys are loaded into the key registers
 // as soon as the current tile's keys have been moved to shared memory, so the load
 // latency hides behind the look-back and the scatter of the current tile.
-template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT>
+// SPLIT = true turns the pass into a stable multi-way partition: the "digit" of a key is the
+// number of splitters strictly below it (bucket b holds keys in (s[b-1], s[b]]).
+template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT, bool SPLIT = false>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 onesweep_kernel(const PassParams prm) {
   using Shape = PassShape<UK, VB, THREADS, ITEMS>;
@@ -285,6 +289,7 @@ onesweep_kernel(const PassParams prm) {
   __shared__ unsigned s_part[GROUPS][kRadix];  // per-group digit totals
   __shared__ unsigned s_scan[kRadix / kWarp];
   __shared__ unsigned s_next;
+  __shared__ UK s_split[SPLIT ? kRadix : 1];
 
   SortCtl* ctl = prm.ctl;
   const int pass = prm.pass;
@@ -311,6 +316,19 @@ onesweep_kernel(const PassParams prm) {
   const unsigned mask = prm.mask;
   const unsigned num_tiles = prm.num_tiles;
   unsigned* whist = s_whist + warp * kRadix;
+  const unsigned num_split = SPLIT ? prm.num_splitters : 0u;
+  if constexpr (SPLIT) {
+    for (unsigned i = threadIdx.x; i < num_split; i += THREADS) s_split[i] = static_cast<const UK*>(prm.splitters)[i];
+  }
+  auto digit = [&](UK k) -> unsigned {
+    if constexpr (SPLIT) {
+      unsigned b = 0;
+      for (unsigned i = 0; i < num_split; ++i) b += s_split[i] < k;
+      return b;
+    } else {
+      return digit_of(k, shift, mask);
+    }
+  };
 
   // warp-striped load: round j of lane l is element j*32+l of the warp's slice
   UK key[ITEMS];
@@ -366,7 +384,7 @@ onesweep_kernel(const PassParams prm) {
     const unsigned lt_mask = lanemask_lt();
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned d = digit_of(key[j], shift, mask);
+      const unsigned d = digit(key[j]);
       const unsigned peers = match_digit(d);
       const unsigned ahead = __popc(peers & lt_mask);
       const unsigned old = whist[d];
@@ -400,7 +418,8 @@ onesweep_kernel(const PassParams prm) {
       if (g < (int)grp) grp_off += c;
       count += c;
     }
-    if (d_own == mask) count -= (unsigned)TILE - tile_valid;  // padding carries the largest digit
+    // padding (all-ones keys at the end of the tile) carries the largest digit in use
+    if (d_own == (SPLIT ? digit((UK)~(UK)0) : mask)) count -= (unsigned)TILE - tile_valid;
     if (grp == 0) {
       DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d_own;
       if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
@@ -427,7 +446,7 @@ onesweep_kernel(const PassParams prm) {
     // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned d = digit_of(key[j], shift, mask);
+      const unsigned d = digit(key[j]);
       const unsigned q = whist[d] + rank[j];
       rank[j] = (unsigned short)q;
       s_keys[q] = key[j];
@@ -494,7 +513,7 @@ onesweep_kernel(const PassParams prm) {
     // ---- scatter: every digit leaves as one contiguous run
     auto emit = [&](unsigned pos) {
       const UK k = s_keys[pos];
-      const IdxT g = s_gbase[digit_of(k, shift, mask)] + pos;
+      const IdxT g = s_gbase[digit(k)] + pos;
       dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
       if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
     };
@@ -616,7 +635,7 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
     const int aligned = reinterpret_cast<uintptr_t>(d_keys) % 16 == 0;
     histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n, begin_bit,
                                                             end_bit, num_passes, enc, ctl, aligned);
-    trace_mark(stream);
+    trace_mark(stream, kTraceSortHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
   }
 
@@ -630,6 +649,8 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.enc = enc;
   prm.ctl = ctl;
   prm.desc = base + lay.desc_off;
+  prm.splitters = nullptr;
+  prm.num_splitters = 0;
   auto launch = [&](auto kernel) -> int {
     TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
     int per_sm = 0;
@@ -643,7 +664,7 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
       const int bits = end_bit - prm.shift < 8 ? end_bit - prm.shift : 8;
       prm.mask = (1u << bits) - 1u;
       kernel<<<grid, T::kThreads, Shape::kSmem, stream>>>(prm);
-      trace_mark(stream);
+      trace_mark(stream, kTraceSortPass);
       TB200_CUDA_TRY(cudaGetLastError());
     }
     return TB200_OK;
@@ -655,8 +676,131 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   copy_back_kernel<<<sms * 4, 256, 0, stream>>>(
       static_cast<uint4*>(d_keys), reinterpret_cast<const uint4*>(base + lay.keys_off), n * sizeof(UK),
       static_cast<uint4*>(d_vals), reinterpret_cast<const uint4*>(base + lay.vals_off), n * (uint64_t)VB, ctl);
-  trace_mark(stream);
+  trace_mark(stream, kTraceSortCopyBack);
   return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------
+// stable multi-way partition by splitters (one onesweep pass with bucket ids as digits)
+// ---------------------------------------------------------------------------------
+template <typename UK>
+__global__ void __launch_bounds__(kHistThreads)
+bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __restrict__ splitters, unsigned num_split,
+                        SortCtl* ctl) {
+  __shared__ unsigned s_hist[kRadix];
+  __shared__ UK s_split[kRadix];
+  __shared__ unsigned s_last;
+  __shared__ unsigned long long s_warp_tot[8];
+  for (int i = threadIdx.x; i < kRadix; i += kHistThreads) s_hist[i] = 0;
+  for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) s_split[i] = splitters[i];
+  __syncthreads();
+  for (uint64_t i = (uint64_t)blockIdx.x * kHistThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kHistThreads) {
+    const UK k = keys[i];
+    unsigned b = 0;
+    for (unsigned j = 0; j < num_split; ++j) b += s_split[j] < k;
+    atomicAdd(&s_hist[b], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= (int)num_split; i += kHistThreads)
+    if (s_hist[i]) atomicAdd(&ctl->hist[0][i], (unsigned long long)s_hist[i]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&ctl->hist_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  unsigned long long c = 0;
+  if (threadIdx.x < kRadix) c = ld_relaxed_u64(&ctl->hist[0][threadIdx.x]);
+  unsigned long long s = c;
+  const unsigned lane = lane_id(), warp = threadIdx.x / kWarp;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, s, off);
+    if (lane >= off) s += t;
+  }
+  if (threadIdx.x < kRadix && lane == 31) s_warp_tot[warp] = s;
+  __syncthreads();
+  if (threadIdx.x < kRadix) {
+    unsigned long long base = 0;
+    for (unsigned w = 0; w < warp; ++w) base += s_warp_tot[w];
+    ctl->offs[0][threadIdx.x] = base + s - c;
+  }
+  if (threadIdx.x == 0) {  // one pass, never skipped, input in the caller's array, output in the other
+    ctl->skip[0] = 0;
+    ctl->exec_before[0] = 0;
+    ctl->total_exec = 1;
+    ctl->last_pass = 0;
+  }
+}
+
+template <typename UK, int VB>
+int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, void* d_keys_out,
+                   void* d_vals_out, uint64_t n, const void* d_splitters, unsigned num_splitters,
+                   uint64_t* d_counts, cudaStream_t stream) {
+  using T = Tuning<UK, VB>;
+  using Shape = PassShape<UK, VB, T::kThreads, T::kItems>;
+  constexpr uint64_t TILE = Shape::kTile;
+  const uint64_t tiles = (n + TILE - 1) / TILE;
+  const bool wide = n > (1ull << 30);
+  const Layout lay = make_layout(0, sizeof(UK), VB, tiles, wide ? 8 : 4);  // control block + descriptors only
+  if (d_temp == nullptr) {
+    *temp_bytes = lay.total;
+    return TB200_OK;
+  }
+  if (*temp_bytes < lay.total) return TB200_ERR_TEMP_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(d_temp) % 256) return TB200_ERR_INVALID_ARGUMENT;
+  if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
+  if (!d_counts || (num_splitters && !d_splitters)) return TB200_ERR_INVALID_ARGUMENT;
+  char* base = static_cast<char*>(d_temp);
+  auto* ctl = reinterpret_cast<SortCtl*>(base + lay.ctl_off);
+  TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
+  if (n == 0) {
+    TB200_CUDA_TRY(cudaMemsetAsync(d_counts, 0, (num_splitters + 1) * sizeof(uint64_t), stream));
+    return TB200_OK;
+  }
+  if (!d_keys || !d_keys_out || (VB && (!d_vals || !d_vals_out))) return TB200_ERR_INVALID_ARGUMENT;
+  int dev = 0, sms = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  {
+    const uint64_t want = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
+    const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
+    bucket_histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n,
+                                                                   static_cast<const UK*>(d_splitters), num_splitters, ctl);
+    trace_mark(stream, kTracePartitionHistogram);
+    TB200_CUDA_TRY(cudaGetLastError());
+  }
+  PassParams prm;
+  prm.keys_main = const_cast<void*>(d_keys);
+  prm.keys_alt = d_keys_out;
+  prm.vals_main = const_cast<void*>(d_vals);
+  prm.vals_alt = d_vals_out;
+  prm.n = n;
+  prm.num_tiles = (unsigned)tiles;
+  prm.enc = Encoding{0ull, 0ull, 0ull};
+  prm.ctl = ctl;
+  prm.desc = base + lay.desc_off;
+  prm.pass = 0;
+  prm.shift = 0;
+  prm.mask = num_splitters;
+  prm.splitters = d_splitters;
+  prm.num_splitters = num_splitters;
+  auto launch = [&](auto kernel) -> int {
+    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
+    int per_sm = 0;
+    TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, T::kThreads, Shape::kSmem));
+    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const uint64_t resident = (uint64_t)per_sm * sms;
+    const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
+    kernel<<<grid, T::kThreads, Shape::kSmem, stream>>>(prm);
+    trace_mark(stream, kTracePartitionPass);
+    return (int)cudaGetLastError();
+  };
+  const int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true>)
+                      : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true>);
+  if (rc) return rc;
+  return (int)cudaMemcpyAsync(d_counts, &ctl->hist[0][0], (num_splitters + 1) * sizeof(uint64_t),
+                              cudaMemcpyDeviceToDevice, stream);
 }
 
 template <typename UK>
@@ -696,4 +840,27 @@ extern "C" int tb200_radix_sort(void* d_temp, size_t* temp_bytes, void* d_keys, 
     case 4: return sort_vals<uint32_t>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
     default: return sort_vals<unsigned long long>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
   }
+}
+
+extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                               void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
+                               const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
+                               tb200_stream_t stream) {
+  using namespace tb200;
+  if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  if (num_splitters > 255) return TB200_ERR_INVALID_ARGUMENT;
+#define TB200_PART(UK, VB) \
+  return partition_impl<UK, VB>(d_temp, temp_bytes, d_keys, d_vals, d_keys_out, d_vals_out, n, d_splitters, \
+                                num_splitters, d_counts, stream)
+  if (key_dtype == TB200_U64) {
+    if (val_bytes == 0) TB200_PART(unsigned long long, 0);
+    if (val_bytes == 4) TB200_PART(unsigned long long, 4);
+    if (val_bytes == 8) TB200_PART(unsigned long long, 8);
+  } else if (key_dtype == TB200_U32) {
+    if (val_bytes == 0) TB200_PART(uint32_t, 0);
+    if (val_bytes == 4) TB200_PART(uint32_t, 4);
+    if (val_bytes == 8) TB200_PART(uint32_t, 8);
+  }
+#undef TB200_PART
+  return TB200_ERR_UNSUPPORTED;
 }

@@ -274,15 +274,20 @@ reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* 
 // Thread t owns 3*E consecutive elements of the tile (48 bytes of the wider type: a
 // bank-conflict-free stride), so head flags need one shuffle and the tile-local
 // segmented scan one warp scan. Every value is then replaced in place by the sum of its
-// run so far (exclusive, tile-local) and the tile stays parked for two iterations while the
+// run inside the thread and the tile stays parked for two iterations while the
 // look-back warp resolves its prefix; the compute warps finally emit the parked tile's runs.
 // ---------------------------------------------------------------------------------------
-constexpr int kRsThreads = 512;
+#ifndef TB200_RS_THREADS
+#define TB200_RS_THREADS 512
+#define TB200_RS_PACKS 3
+#define TB200_RS_PARK 2
+#endif
+constexpr int kRsThreads = TB200_RS_THREADS;
 constexpr int kRsWarps = kRsThreads / kWarp;
 constexpr int kRsLookWarps = 2;  // look-back warps; tile j of a CTA is resolved by warp j % 2
 constexpr int kRsCta = kRsThreads + kRsLookWarps * kWarp;
-constexpr int kRsPacks = 3;  // packs of E elements per thread
-constexpr int kRsPark = 2;
+constexpr int kRsPacks = TB200_RS_PACKS;  // packs of E elements per thread
+constexpr int kRsPark = TB200_RS_PARK;
 constexpr int kRsStages = kRsPark + 2;
 constexpr unsigned kRsNoTile = 0xffffffffu;
 
@@ -318,6 +323,7 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
   __shared__ V s_prefix_val[S];
   __shared__ unsigned short s_park_cnt[S][kRsThreads];
   __shared__ unsigned short s_park_heads[S][kRsThreads];
+  __shared__ V s_park_val[S][kRsThreads];
   __shared__ unsigned s_warp_cnt[kRsWarps];
   __shared__ V s_warp_val[kRsWarps];
 
@@ -365,7 +371,9 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
       const V tot_val = s_look_val[slot];
       unsigned long long pc = 0;
       V pv = V(0);
+#ifndef TB200_EXPERIMENT_NO_LOOKBACK
       if (tile != 0) lookback_seg<V>(tiles, tile, status, pc, pv);
+#endif
       if (lane == 0) {
         const unsigned long long ic = pc + tot_cnt;
         const V iv = tot_cnt ? tot_val : pv + tot_val;
@@ -391,28 +399,24 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
   auto finalize = [&](unsigned it_prev, bool refill) {
     const int slot = it_prev % S;
     mbar_wait_bounded(&s_resolved[slot], (it_prev / S) & 1u, status);
-    const unsigned heads = s_park_heads[slot][threadIdx.x];
+    unsigned heads = s_park_heads[slot][threadIdx.x];
     if (heads) {
       const unsigned long long pc = s_prefix_cnt[slot];
       const V pv = s_prefix_val[slot];
-      const Pack<K, E>* pk = reinterpret_cast<const Pack<K, E>*>(slot_keys(slot)) + threadIdx.x * P;
-      const Pack<V, E>* pr = reinterpret_cast<const Pack<V, E>*>(slot_vals(slot)) + threadIdx.x * P;
+      const K* pk = slot_keys(slot) + threadIdx.x * ITEMS;
+      const V* pr = slot_vals(slot) + threadIdx.x * ITEMS;  // parked: run sums inside the thread
       unsigned cnt = s_park_cnt[slot][threadIdx.x];
-#pragma unroll
-      for (int p = 0; p < P; ++p) {
-        if ((heads >> (p * E)) & ((1u << E) - 1u)) {
-          const Pack<K, E> kk = pk[p];
-          const Pack<V, E> rr = pr[p];
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            if (heads & (1u << (p * E + e))) {
-              const unsigned long long at = pc + cnt;
-              if (at > 0) vals_out[at - 1] = cnt ? rr.v[e] : pv + rr.v[e];
-              keys_out[at] = kk.v[e];
-              ++cnt;
-            }
-          }
-        }
+      // the run that closes at the thread's FIRST head began before the thread
+      V carried = s_park_val[slot][threadIdx.x];
+      while (heads) {  // one iteration per run that starts in this thread's elements
+        const int i = __ffs(heads) - 1;
+        heads &= heads - 1;
+        const unsigned long long at = pc + cnt;
+        const V r = carried + (i ? pr[i - 1] : V(0));
+        if (at > 0) vals_out[at - 1] = cnt ? r : pv + r;
+        keys_out[at] = pk[i];
+        carried = V(0);
+        ++cnt;
       }
     }
     if (refill) {
@@ -499,13 +503,22 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
     if (lane == 31) { s_warp_cnt[warp] = s.cnt; s_warp_val[warp] = s.val; }
     named_barrier(1, kRsThreads);
 
-    Seg<V> warp_prefix{0u, V(0)}, tile_total{0u, V(0)};
+    // scan of the warp totals: lane w holds warp w's total (kRsWarps <= 32)
+    Seg<V> wt{0u, V(0)};
+    if (lane < kRsWarps) { wt.cnt = s_warp_cnt[lane]; wt.val = s_warp_val[lane]; }
 #pragma unroll
-    for (int w = 0; w < kRsWarps; ++w) {
-      const Seg<V> t{s_warp_cnt[w], s_warp_val[w]};
-      if (w < (int)warp) warp_prefix = seg_combine(warp_prefix, t);
-      tile_total = seg_combine(tile_total, t);
+    for (int off = 1; off < kRsWarps; off <<= 1) {
+      Seg<V> o;
+      o.cnt = __shfl_up_sync(0xffffffffu, wt.cnt, off);
+      o.val = __shfl_up_sync(0xffffffffu, wt.val, off);
+      if (lane >= off) wt = seg_combine(o, wt);
     }
+    Seg<V> warp_prefix, tile_total;
+    warp_prefix.cnt = __shfl_sync(0xffffffffu, wt.cnt, warp == 0 ? 0 : warp - 1);
+    warp_prefix.val = __shfl_sync(0xffffffffu, wt.val, warp == 0 ? 0 : warp - 1);
+    if (warp == 0) { warp_prefix.cnt = 0; warp_prefix.val = V(0); }
+    tile_total.cnt = __shfl_sync(0xffffffffu, wt.cnt, kRsWarps - 1);
+    tile_total.val = __shfl_sync(0xffffffffu, wt.val, kRsWarps - 1);
     if (threadIdx.x == 0) {
       if (tile != 0) {
         unsigned payload[4];
@@ -517,22 +530,18 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
       s_look_val[slot] = tile_total.val;
       mbar_arrive(&s_handoff[slot]);
     }
-    // park: every value is replaced by the (tile-local, exclusive) sum of its run so far.
-    // Up to and including the thread's first head the open run began before this thread.
+    // park what the final pass needs: the run sums inside the thread (in place of the
+    // values), the thread's head mask, and the state of the scan in front of the thread
     {
       const Seg<V> local = seg_combine(warp_prefix, lane_excl);
       s_park_heads[slot][threadIdx.x] = (unsigned short)heads;
       s_park_cnt[slot][threadIdx.x] = (unsigned short)local.cnt;
-      const int first_head = heads ? __ffs(heads) - 1 : ITEMS;
+      s_park_val[slot][threadIdx.x] = local.val;
 #pragma unroll
       for (int p = 0; p < P; ++p) {
         Pack<V, E> rr;
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const int i = p * E + e;
-          const V own = i == 0 ? V(0) : incl[i - 1];
-          rr.v[e] = i <= first_head ? local.val + own : own;
-        }
+        for (int e = 0; e < E; ++e) rr.v[e] = incl[p * E + e];
         mv[p] = rr;
       }
     }
@@ -592,7 +601,7 @@ int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
     kernel<<<sgrid, kRsCta, smem, stream>>>(static_cast<const K*>(kin), static_cast<const V*>(vin),
                                             static_cast<K*>(kout), static_cast<V*>(vout), nr, n,
                                             (unsigned)stream_tiles, hdr, desc);
-    trace_mark(stream);
+    trace_mark(stream, kTraceReduceByKey);
     return (int)cudaGetLastError();
   }
   const dim3 grid((unsigned)tiles), block(kRbkThreads);
@@ -604,7 +613,7 @@ int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
     reduce_by_key_kernel<K, V, false><<<grid, block, 0, stream>>>(
         static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout), static_cast<V*>(vout), nr,
         n, (unsigned)tiles, hdr, desc);
-  trace_mark(stream);
+  trace_mark(stream, kTraceReduceByKey);
   return (int)cudaGetLastError();
 }
 

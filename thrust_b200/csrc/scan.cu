@@ -543,7 +543,7 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
     };
     const int rc = exclusive ? run(scan_stream_kernel<T, true>) : run(scan_stream_kernel<T, false>);
     if (rc) return rc;
-    trace_mark(stream);
+    trace_mark(stream, kTraceScan);
     return (int)cudaGetLastError();
   }
 #endif
@@ -555,7 +555,7 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
     if (aligned) scan_kernel<T, false, true><<<grid, block, 0, stream>>>(in, out, n, init, hdr, desc);
     else         scan_kernel<T, false, false><<<grid, block, 0, stream>>>(in, out, n, init, hdr, desc);
   }
-  trace_mark(stream);
+  trace_mark(stream, kTraceScan);
   return (int)cudaGetLastError();
 }
 

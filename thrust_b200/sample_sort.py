@@ -1,20 +1,27 @@
 """Sharded stable sort_by_key across the GPUs of one node: a sample sort.
 
 The reference has no multi-GPU code at all; this is the sharded form of its
-``stable_sort_by_key`` on (uint64 key, uint32 value) pairs, one process per GPU:
+``stable_sort_by_key`` on (uint64 key, uint32 value) pairs, one process per GPU.
+Two pipelines share the sampling, splitter and exchange code:
 
-  1. local onesweep sort of the shard                        (tb200_radix_sort)
-  2. regular sample: ``samples_per_rank`` keys at fixed ranks of the sorted shard
-  3. all-gather the samples; every rank sorts them identically and takes the keys
+``pipeline="partition_first"`` (default; one full local sort per step)
+  1. regular sample of the shard: ``samples_per_rank`` keys at evenly spaced positions
+  2. all-gather the samples; every rank sorts them identically and takes the keys
      at ranks samples_per_rank * r (r = 1..G-1) as splitters
-  4. destination d owns keys in (splitter[d-1], splitter[d]]: the send segments are
-     contiguous ranges of the sorted shard, found with one upper-bound search per
-     splitter (tb200_histogram_sorted) — no data movement
-  5. all-gather of the G x G count matrix, then all-to-all-v of keys and of values
+  3. stable partition of the shard into G buckets, destination d owning the keys in
+     (splitter[d-1], splitter[d]] (tb200_partition: one onesweep pass)
+  4. all-gather of the G x G count matrix, then all-to-all-v of keys and of values
      over NCCL; received runs are stored in source-rank order
-  6. one more local sort of the received pairs. Rank r holds global indices
-     [r*n, (r+1)*n), so a stable sort of runs concatenated in source-rank order
-     reproduces the single-process stable order.
+  5. local onesweep sort of the received pairs (tb200_radix_sort). Rank r holds
+     global indices [r*n, (r+1)*n), so a stable sort of runs concatenated in
+     source-rank order reproduces the single-process stable order.
+
+``pipeline="sort_first"``
+  local sort first; the sample is then taken at fixed ranks of the sorted shard
+  (a classical regular sample, receive imbalance bounded by n*G/samples), the send
+  segments are contiguous ranges found by upper-bound search (tb200_histogram_sorted)
+  with no data movement, and step 5 sorts runs that are already sorted. It costs a
+  second full local sort and exists for comparison.
 
 The collectives go through ``torch.distributed`` (NCCL on GPUs). The per-shard
 compute goes through an ``ops`` object; the default ``DeviceOps`` calls the CUDA
@@ -73,6 +80,30 @@ class DeviceOps:
                    "tb200_histogram_sorted")
         return counts.to(torch.int64) & 0xFFFFFFFF
 
+    def partition(self, keys: torch.Tensor, vals: torch.Tensor, n: int, splitters: torch.Tensor,
+                  out_k: torch.Tensor, out_v: torch.Tensor) -> torch.Tensor:
+        """Stable partition into len(splitters)+1 buckets; returns the bucket sizes (int64 tensor)."""
+        capi = self.capi
+        counts = torch.empty(splitters.numel() + 1, dtype=torch.int64, device=self.device)
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_partition(C.c_void_p(self.temp.data_ptr()), C.byref(have),
+                                            C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
+                                            C.c_void_p(out_k.data_ptr()), C.c_void_p(out_v.data_ptr()), n, capi.U64, 4,
+                                            C.c_void_p(splitters.data_ptr()), splitters.numel(),
+                                            C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
+        return counts
+
+    def gather(self, dst: torch.Tensor, src_ptrs, src_offsets, counts, elem_bytes: int) -> None:
+        """dst[:sum(counts)] = concatenation of counts[s] elements at src_ptrs[s] + src_offsets[s]
+        (device pointers, possibly peer mappings): tb200_gather_segments."""
+        capi = self.capi
+        g = len(counts)
+        ptrs = (C.c_void_p * g)(*src_ptrs)
+        offs = (C.c_uint64 * g)(*src_offsets)
+        cnts = (C.c_uint64 * g)(*counts)
+        capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, offs, cnts, g, elem_bytes,
+                                                  self._stream()), "tb200_gather_segments")
+
     def status(self) -> int:
         return int(self.capi.lib.tb200_temp_status(C.c_void_p(self.temp.data_ptr()), self._stream()))
 
@@ -101,24 +132,87 @@ class ShardedSorter:
     """Sorts one shard per rank; after ``sort`` rank r holds the r-th slice of the global order."""
 
     def __init__(self, n: int, device: torch.device, world_size: int = 1, rank: int = 0, seed: int = 0,
-                 ops=None, group=None, slack: float = 1.0 / 64):
+                 ops=None, group=None, slack: Optional[float] = None, pipeline: str = "partition_first",
+                 exchange: str = "auto"):
+        """exchange: "peer" — every GPU pulls its runs out of the other GPUs' partition buffers with
+        one kernel of peer loads over NVLink (buffers in torch symmetric memory, no multicast);
+        "nccl" — all-to-all-v through torch.distributed; "auto" — "peer" on CUDA with the
+        partition_first pipeline when the symmetric-memory rendezvous succeeds, else "nccl"."""
+        if pipeline not in ("partition_first", "sort_first"):
+            raise ValueError(pipeline)
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError(exchange)
         self.n, self.device, self.world, self.rank, self.seed = n, device, world_size, rank, seed
         self.group = group
+        self.pipeline = pipeline
+        if slack is None:
+            # sort_first: a regular sample of sorted shards bounds the imbalance by n*G/samples;
+            # partition_first: the sample is random with respect to key order, so the receive
+            # count fluctuates by a few percent (about 4 sigma for 8 ranks x 1024 samples)
+            slack = 1.0 / 64 if pipeline == "sort_first" else 0.2
         self.capacity = n if world_size == 1 else n + int(n * slack) + SAMPLES_PER_RANK
         if ops is None:
             if device.type != "cuda":
                 raise RuntimeError("thrust_b200 has no CPU path: ShardedSorter needs a CUDA device")
             ops = DeviceOps(device, self.capacity)
         self.ops = ops
-        self.recv_k = self.recv_v = None
+        self.recv_k = self.recv_v = self.part_k = self.part_v = None
+        self.exchange = "none"
         if world_size > 1:
             self.recv_k = torch.empty(self.capacity, dtype=torch.int64, device=device)
             self.recv_v = torch.empty(self.capacity, dtype=torch.int32, device=device)
+            self.exchange = "nccl"
+            self.peer_k = self.peer_v = None
+            if pipeline == "partition_first":
+                want_peer = exchange == "peer" or (exchange == "auto" and device.type == "cuda")
+                if want_peer:
+                    try:
+                        self._alloc_symmetric(n)
+                        self.exchange = "peer"
+                    except Exception as e:  # symmetric memory unavailable: use the collective
+                        if exchange == "peer":
+                            raise
+                        self.exchange_fallback_reason = repr(e)
+                if self.exchange == "nccl":
+                    self.part_k = torch.empty(n, dtype=torch.int64, device=device)
+                    self.part_v = torch.empty(n, dtype=torch.int32, device=device)
         self.last_counts = None
+        self._marks = []
+
+    def _alloc_symmetric(self, n: int) -> None:
+        """Partition buffers in symmetric memory; peer pointers of every rank's buffers."""
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+        import torch.distributed._symmetric_memory as symm
+        grp = self.group if self.group is not None else dist.group.WORLD
+        self.part_k = symm.empty(n, dtype=torch.int64, device=self.device)
+        self.part_v = symm.empty(n, dtype=torch.int32, device=self.device)
+        hk = symm.rendezvous(self.part_k, grp)
+        hv = symm.rendezvous(self.part_v, grp)
+        self.peer_k = [int(p) for p in hk.buffer_ptrs]
+        self.peer_v = [int(p) for p in hv.buffer_ptrs]
+        self._symm_handles = (hk, hv)
+        if len(self.peer_k) != self.world:
+            raise RuntimeError("symmetric memory rendezvous returned the wrong number of peers")
+
+    def _mark(self, name: str) -> None:
+        """Records a CUDA event at a phase boundary (device tensors only)."""
+        if self.device.type == "cuda":
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(torch.cuda.current_stream(self.device))
+            self._marks.append((name, e))
+
+    def phase_times(self) -> dict:
+        """Milliseconds between the phase boundaries of the last sort() (synchronises)."""
+        if len(self._marks) < 2:
+            return {}
+        self._marks[-1][1].synchronize()
+        return {self._marks[i + 1][0]: self._marks[i][1].elapsed_time(self._marks[i + 1][1])
+                for i in range(len(self._marks) - 1)}
 
     def release(self) -> None:
         self.ops.release()
-        self.recv_k = self.recv_v = None
+        self.recv_k = self.recv_v = self.part_k = self.part_v = None
 
     def check_status(self) -> None:
         st = self.ops.status()
@@ -129,19 +223,32 @@ class ShardedSorter:
         """keys: int64 tensor holding uint64 bit patterns, vals: int32 tensor holding uint32.
         Returns (keys, vals, count): this rank's slice of the globally sorted sequence."""
         n, G = self.n, self.world
-        self.ops.sort_pairs(keys, vals, n)
         if G == 1:
+            self.ops.sort_pairs(keys, vals, n)
             return keys, vals, n
-        # 2-3. regular sample -> splitters (identical on every rank)
+        sort_first = self.pipeline == "sort_first"
+        self._marks = []
+        self._mark("start")
+        if sort_first:
+            self.ops.sort_pairs(keys, vals, n)
+            self._mark("local_sort")
+        # regular sample -> splitters (identical on every rank)
         pos = sample_positions(n, SAMPLES_PER_RANK).to(self.device)
         mine = keys[pos].contiguous()
         gathered = torch.empty(G * mine.numel(), dtype=torch.int64, device=self.device)
         dist.all_gather_into_tensor(gathered, mine, group=self.group)
         self.ops.sort_keys(gathered)
         splitters = pick_splitters(gathered, G).contiguous()
-        # 4. contiguous send segments of the sorted shard
-        head = self.ops.segment_counts(keys, n, splitters)
-        send = torch.cat([head, (n - head.sum()).reshape(1)])
+        self._mark("sample_and_splitters")
+        if sort_first:
+            # contiguous send segments of the sorted shard
+            head = self.ops.segment_counts(keys, n, splitters)
+            send = torch.cat([head, (n - head.sum()).reshape(1)])
+            src_k, src_v = keys, vals
+        else:
+            send = self.ops.partition(keys, vals, n, splitters, self.part_k, self.part_v)
+            src_k, src_v = self.part_k, self.part_v
+        self._mark("segments" if sort_first else "partition")
         # 5. the whole G x G count matrix goes to every rank (row r = what rank r sends), so all
         # ranks take the same decision about receive overflow; then the payload
         matrix = torch.empty(G * G, dtype=torch.int64, device=self.device)
@@ -154,10 +261,23 @@ class ShardedSorter:
         worst = int(mat.sum(dim=0).max())
         if worst > self.capacity:
             raise OverflowError(f"{worst} incoming pairs on one rank exceed the receive capacity {self.capacity}")
-        dist.all_to_all_single(self.recv_k[:m], keys[:n], recv_l, send_l, group=self.group)
-        dist.all_to_all_single(self.recv_v[:m], vals[:n], recv_l, send_l, group=self.group)
-        # 6. stable sort of the runs (already in source-rank order)
+        self._mark("count_matrix")
+        if self.exchange == "peer" and not sort_first:
+            # Pull: rank r's bucket for me starts where the buckets of lower destinations end.
+            # The count matrix arrived through a collective that every rank entered after its
+            # partition kernel, so all partition buffers are complete.
+            src_off = [int(mat[r, :self.rank].sum()) for r in range(G)]
+            self.ops.gather(self.recv_k, self.peer_k, src_off, recv_l, 8)
+            self.ops.gather(self.recv_v, self.peer_v, src_off, recv_l, 4)
+            # nobody may overwrite its partition buffer (next call) before all pulls are done
+            dist.barrier(group=self.group)
+        else:
+            dist.all_to_all_single(self.recv_k[:m], src_k[:n], recv_l, send_l, group=self.group)
+            dist.all_to_all_single(self.recv_v[:m], src_v[:n], recv_l, send_l, group=self.group)
+        self._mark("exchange")
+        # stable sort of the runs (already in source-rank order)
         self.ops.sort_pairs(self.recv_k, self.recv_v, m)
+        self._mark("final_sort")
         return self.recv_k, self.recv_v, m
 
     # ---- reference-free verification (needs the CUDA library) ------------------------------
@@ -202,7 +322,7 @@ def bench_host_path(n: int, device: torch.device, world: int, rank: int, seed: i
         hk = torch.empty(n, dtype=torch.int64).pin_memory()
         hv = torch.empty(n, dtype=torch.int32).pin_memory()
         if world > 1:
-            cap = n + n // 64 + SAMPLES_PER_RANK
+            cap = n + n // 5 + SAMPLES_PER_RANK
             ok_, ov_ = torch.empty(cap, dtype=torch.int64).pin_memory(), torch.empty(cap, dtype=torch.int32).pin_memory()
     except RuntimeError:
         return None
