@@ -392,6 +392,20 @@ onesweep_kernel(const PassParams prm) {
       __syncwarp();
       rank[j] = (unsigned short)(old + ahead);
     }
+    // values of this tile: requested now, consumed after the per-digit phases below, so the
+    // global-load latency overlaps two barriers' worth of work
+    V val[VB ? ITEMS : 1];
+    if constexpr (VB != 0) {
+      const V* pv = src_vals + tile_base + warp_off + lane;
+      if (tile_valid == (unsigned)TILE) {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j) val[j] = pv[j * kWarp];
+      } else {
+#pragma unroll
+        for (int j = 0; j < ITEMS; ++j)
+          if (warp_off + j * kWarp + lane < tile_valid) val[j] = pv[j * kWarp];
+      }
+    }
     __syncthreads();
     const unsigned next = s_next;
 
@@ -454,18 +468,8 @@ onesweep_kernel(const PassParams prm) {
     // the key registers are free: fetch the next tile's keys now
     if (next < num_tiles) load_keys(next);
     if constexpr (VB != 0) {
-      const V* pv = src_vals + tile_base + warp_off + lane;
-      if (tile_valid == (unsigned)TILE) {
-        V val[ITEMS];
 #pragma unroll
-        for (int j = 0; j < ITEMS; ++j) val[j] = pv[j * kWarp];
-#pragma unroll
-        for (int j = 0; j < ITEMS; ++j) s_vals[rank[j]] = val[j];
-      } else {
-#pragma unroll
-        for (int j = 0; j < ITEMS; ++j)
-          if (warp_off + j * kWarp + lane < tile_valid) s_vals[rank[j]] = pv[j * kWarp];
-      }
+      for (int j = 0; j < ITEMS; ++j) s_vals[rank[j]] = val[j];  // padding slots lie beyond tile_valid
     }
 
     // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
