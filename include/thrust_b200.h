@@ -83,11 +83,13 @@ int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const 
  * h_src[s]. The three arrays are HOST arrays; the source pointers are device pointers and may
  * be peer mappings of other GPUs' memory (the caller establishes the mapping and the
  * ordering against the peers' writes). One kernel of plain loads and stores: each GPU pulls
- * its runs over NVLink itself instead of calling a collective. No counterpart in the
+ * its runs over NVLink itself instead of calling a collective. Its CTAs work on all segments
+ * at once, starting `rotate` segments in (pass the caller's rank), so that neither one
+ * source GPU nor one link is read by everyone at the same time. No counterpart in the
  * reference (it has no multi-GPU code). */
 int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
                           const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
-                          tb200_stream_t stream);
+                          uint32_t rotate, tb200_stream_t stream);
 
 /* ---- scan ---------------------------------------------------------------------------
  * Prefix sum with plus over n elements of dtype in {I32,U32,I64,U64,F32,F64}; accumulator

@@ -251,7 +251,7 @@ def test_gather_segments_concatenates_ranges(cuda_device, dtype):
     o = (C.c_uint64 * g)(*offs)
     c = (C.c_uint64 * g)(*cnts)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, o, c, g, np.dtype(dtype).itemsize,
+    capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, o, c, g, np.dtype(dtype).itemsize, 3,
                                               stream), "tb200_gather_segments")
     torch.cuda.synchronize()
     assert to_host(dst, dtype).tobytes() == want.tobytes()

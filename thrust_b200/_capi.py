@@ -36,7 +36,7 @@ def _load() -> C.CDLL:
         "tb200_error_string": ([i32], C.c_char_p),
         "tb200_radix_sort": ([vp, psz, vp, vp, u64, i32, i32, i32, i32, i32, vp], i32),
         "tb200_partition": ([vp, psz, vp, vp, vp, vp, u64, i32, i32, vp, u32, vp, vp], i32),
-        "tb200_gather_segments": ([vp, vp, vp, vp, u32, i32, vp], i32),
+        "tb200_gather_segments": ([vp, vp, vp, vp, u32, i32, u32, vp], i32),
         "tb200_scan": ([vp, psz, vp, vp, u64, i32, i32, vp, vp], i32),
         "tb200_scan_static": ([vp, vp, u64, i32, i32, vp, vp], i32),
         "tb200_reduce_by_key": ([vp, psz, vp, vp, vp, vp, vp, u64, i32, i32, vp], i32),

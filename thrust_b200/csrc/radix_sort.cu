@@ -322,9 +322,13 @@ onesweep_kernel(const PassParams prm) {
   }
   auto digit = [&](UK k) -> unsigned {
     if constexpr (SPLIT) {
-      unsigned b = 0;
-      for (unsigned i = 0; i < num_split; ++i) b += s_split[i] < k;
-      return b;
+      // number of splitters strictly below k: binary search over the ascending splitters
+      unsigned lo = 0, hi = num_split;
+      while (lo < hi) {
+        const unsigned mid = (lo + hi) >> 1;
+        if (s_split[mid] < k) lo = mid + 1; else hi = mid;
+      }
+      return lo;
     } else {
       return digit_of(k, shift, mask);
     }

@@ -256,6 +256,7 @@ struct GatherArgs {
   unsigned long long count[kMaxSegments];
   unsigned long long dst_off[kMaxSegments];
   int num_segments;
+  int rotate;
 };
 
 // Every CTA walks all segments with a grid-stride loop. The source side (possibly across
@@ -269,7 +270,11 @@ gather_segments_kernel(T* __restrict__ dst, const GatherArgs args) {
   constexpr int V = 16 / sizeof(T);  // elements per 16-byte load
   const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
   const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-  for (int s = 0; s < args.num_segments; ++s) {
+  // CTAs start on different segments (CTA b on segment (b + rotate) mod count) and then walk
+  // all of them cyclically, so at any moment the loads of one GPU are spread over all source
+  // GPUs, and with `rotate` = the caller's rank the pullers are spread over the sources too.
+  for (int k = 0; k < args.num_segments; ++k) {
+    const int s = (int)((blockIdx.x + (unsigned)args.rotate + (unsigned)k) % (unsigned)args.num_segments);
     const T* __restrict__ src = static_cast<const T*>(args.src[s]);
     T* __restrict__ out = dst + args.dst_off[s];
     const unsigned long long n = args.count[s];
@@ -315,13 +320,14 @@ gather_segments_kernel(T* __restrict__ dst, const GatherArgs args) {
 
 extern "C" int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
                                      const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
-                                     tb200_stream_t stream) {
+                                     uint32_t rotate, tb200_stream_t stream) {
   using namespace tb200;
   if (num_segments > (uint32_t)kMaxSegments) return TB200_ERR_UNSUPPORTED;
   if (num_segments && (!d_dst || !h_src || !h_src_offset || !h_count)) return TB200_ERR_INVALID_ARGUMENT;
   if (elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return TB200_ERR_UNSUPPORTED;
   GatherArgs a{};
   a.num_segments = (int)num_segments;
+  a.rotate = (int)(num_segments ? rotate % num_segments : 0);
   unsigned long long off = 0;
   for (uint32_t s = 0; s < num_segments; ++s) {
     a.src[s] = static_cast<const char*>(h_src[s]) + h_src_offset[s] * (uint64_t)elem_bytes;

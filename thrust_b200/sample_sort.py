@@ -93,7 +93,7 @@ class DeviceOps:
                                             C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
         return counts
 
-    def gather(self, dst: torch.Tensor, src_ptrs, src_offsets, counts, elem_bytes: int) -> None:
+    def gather(self, dst: torch.Tensor, src_ptrs, src_offsets, counts, elem_bytes: int, rotate: int = 0) -> None:
         """dst[:sum(counts)] = concatenation of counts[s] elements at src_ptrs[s] + src_offsets[s]
         (device pointers, possibly peer mappings): tb200_gather_segments."""
         capi = self.capi
@@ -101,7 +101,7 @@ class DeviceOps:
         ptrs = (C.c_void_p * g)(*src_ptrs)
         offs = (C.c_uint64 * g)(*src_offsets)
         cnts = (C.c_uint64 * g)(*counts)
-        capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, offs, cnts, g, elem_bytes,
+        capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, offs, cnts, g, elem_bytes, rotate,
                                                   self._stream()), "tb200_gather_segments")
 
     def status(self) -> int:
@@ -267,8 +267,8 @@ class ShardedSorter:
             # The count matrix arrived through a collective that every rank entered after its
             # partition kernel, so all partition buffers are complete.
             src_off = [int(mat[r, :self.rank].sum()) for r in range(G)]
-            self.ops.gather(self.recv_k, self.peer_k, src_off, recv_l, 8)
-            self.ops.gather(self.recv_v, self.peer_v, src_off, recv_l, 4)
+            self.ops.gather(self.recv_k, self.peer_k, src_off, recv_l, 8, self.rank)
+            self.ops.gather(self.recv_v, self.peer_v, src_off, recv_l, 4, self.rank)
             # nobody may overwrite its partition buffer (next call) before all pulls are done
             dist.barrier(group=self.group)
         else:
