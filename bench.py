@@ -369,12 +369,16 @@ def main():
 
     # dominant kernel: one onesweep radix pass (trace kind 2) over this rank's pairs. At N > 1 the
     # passes run over the received pairs (about n of them), so n is used for every launch.
-    pass_ms = [ms for tr in trace_ms for kind, ms in tr if kind == 2]
+    # (the last 8 radix passes of a step: at N > 1 the splitter sample is sorted first, with tiny passes)
+    pass_ms = [ms for tr in trace_ms for ms in [m for kind, m in tr if kind == 2][-8:]]
     avg_pass = sum(pass_ms) / max(len(pass_ms), 1)
     pass_bytes = n * 2.0 * (8 + 4)
     achieved = pass_bytes / (avg_pass * 1e-3) / 1e9 if avg_pass > 0 else 0.0
     tpp = traffic_per_pair()
-    sort_ms = [sum(ms for kind, ms in tr if kind in (1, 2, 3)) for tr in trace_ms]
+    def last_sort(tr):  # launches of the last local sort of a step: histogram, passes, copy-back
+        idx = [i for i, (kind, _) in enumerate(tr) if kind == 1]
+        return tr[idx[-1]:] if idx else []
+    sort_ms = [sum(ms for kind, ms in last_sort(tr) if kind in (1, 2, 3)) for tr in trace_ms]
     whole = (256.0 * n) / (sum(sort_ms) / max(len(sort_ms), 1) * 1e-3) / 1e9 if sort_ms and sort_ms[0] > 0 else None
     roofline = {
         "bound": "hbm", "kernel": "onesweep_kernel<u64 key, 4-byte value>", "achieved": achieved, "peak": peak,

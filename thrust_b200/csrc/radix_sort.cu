@@ -247,6 +247,16 @@ __device__ __forceinline__ unsigned match_digit(unsigned d) {
   return peers;
 #endif
 }
+// Same, for digits known to fit in `bits` bits (bucket ids of a partition): fewer ballots.
+__device__ __forceinline__ unsigned match_digit_bits(unsigned d, int bits) {
+  unsigned peers = 0xffffffffu;
+  for (int b = 0; b < bits; ++b) {
+    const unsigned m = __ballot_sync(0xffffffffu, (d >> b) & 1u);
+    const unsigned t = 0u - ((d >> b) & 1u);
+    peers &= ~(m ^ t);
+  }
+  return peers;
+}
 
 template <typename UK, int VB, int THREADS, int ITEMS>
 struct PassShape {
@@ -317,6 +327,7 @@ onesweep_kernel(const PassParams prm) {
   const unsigned num_tiles = prm.num_tiles;
   unsigned* whist = s_whist + warp * kRadix;
   const unsigned num_split = SPLIT ? prm.num_splitters : 0u;
+  const int split_bits = 32 - __clz(num_split | 1u);  // bucket ids are 0..num_split
   if constexpr (SPLIT) {
     for (unsigned i = threadIdx.x; i < num_split; i += THREADS) s_split[i] = static_cast<const UK*>(prm.splitters)[i];
   }
@@ -389,7 +400,7 @@ onesweep_kernel(const PassParams prm) {
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
       const unsigned d = digit(key[j]);
-      const unsigned peers = match_digit(d);
+      const unsigned peers = SPLIT ? match_digit_bits(d, split_bits) : match_digit(d);
       const unsigned ahead = __popc(peers & lt_mask);
       const unsigned old = whist[d];
       if (ahead == 0) whist[d] = old + __popc(peers);
