@@ -373,6 +373,8 @@ onesweep_kernel(const PassParams prm) {
     }
   };
 
+  // global offset of this thread's digit in this pass: read once, used for every tile
+  const unsigned long long pass_offset = ctl->offs[pass][threadIdx.x % kRadix];
   if (threadIdx.x == 0) s_next = atomicAdd(&ctl->tickets[pass], 1u);
   __syncthreads();
   unsigned tile = s_next;
@@ -493,7 +495,10 @@ onesweep_kernel(const PassParams prm) {
       const unsigned d = d_own;
       unsigned long long excl = 0;
       if (tile != 0) {
-        constexpr int kWindow = 4;
+#ifndef TB200_SORT_WINDOW
+#define TB200_SORT_WINDOW 4
+#endif
+        constexpr int kWindow = TB200_SORT_WINDOW;
         const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
         const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
         long long t = (long long)tile - 1;
@@ -525,7 +530,7 @@ onesweep_kernel(const PassParams prm) {
         DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
         st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + count) & DescBits<DescT>::kValueMask));
       }
-      s_gbase[d] = (IdxT)(ctl->offs[pass][d] + excl - digit_start);
+      s_gbase[d] = (IdxT)(pass_offset + excl - digit_start);
     }
     __syncthreads();
 
