@@ -86,10 +86,21 @@ int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const 
  * its runs over NVLink itself instead of calling a collective. Its CTAs work on all segments
  * at once, starting `rotate` segments in (pass the caller's rank), so that neither one
  * source GPU nor one link is read by everyone at the same time. No counterpart in the
- * reference (it has no multi-GPU code). */
+ * reference (it has no multi-GPU code).
+ * d_sort_temp (may be NULL; 8-byte elements only): scratch of a uint64 sort prepared with
+ * tb200_radix_sort_begin — the kernel then also counts the digits of every key it moves, so
+ * that tb200_radix_sort_finish can skip the sort's own histogram pass over the data. */
 int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
                           const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
-                          uint32_t rotate, tb200_stream_t stream);
+                          uint32_t rotate, void* d_sort_temp, tb200_stream_t stream);
+
+/* tb200_radix_sort in two halves for whole uint64 keys (ascending): _begin clears the scratch,
+ * the caller accumulates the histograms of the n keys through tb200_gather_segments(...,
+ * d_sort_temp, ...), _finish runs the passes. Same scratch size and result as tb200_radix_sort. */
+int tb200_radix_sort_begin(void* d_temp, size_t* temp_bytes, uint64_t n, int key_dtype, int val_bytes,
+                           tb200_stream_t stream);
+int tb200_radix_sort_finish(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n,
+                            int key_dtype, int val_bytes, tb200_stream_t stream);
 
 /* ---- scan ---------------------------------------------------------------------------
  * Prefix sum with plus over n elements of dtype in {I32,U32,I64,U64,F32,F64}; accumulator

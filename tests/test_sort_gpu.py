@@ -252,6 +252,37 @@ def test_gather_segments_concatenates_ranges(cuda_device, dtype):
     c = (C.c_uint64 * g)(*cnts)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, o, c, g, np.dtype(dtype).itemsize, 3,
-                                              stream), "tb200_gather_segments")
+                                              None, stream), "tb200_gather_segments")
     torch.cuda.synchronize()
     assert to_host(dst, dtype).tobytes() == want.tobytes()
+
+
+def test_gather_that_counts_digits_then_sort_finish(cuda_device):
+    """tb200_radix_sort_begin + gather with digit counting + tb200_radix_sort_finish == tb200_radix_sort."""
+    import ctypes as C
+    rng = np.random.default_rng(78)
+    parts_k = [random_keys(rng, m, np.uint64) for m in (70001, 3, 123457)]
+    parts_v = [rng.integers(0, 1 << 32, size=a.size, dtype=np.uint32) for a in parts_k]
+    dk = [to_device(a, offset_elems=1) for a in parts_k]
+    dv = [to_device(a, offset_elems=3) for a in parts_v]
+    n = sum(a.size for a in parts_k)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    need = C.c_size_t(0)
+    capi.check(capi.lib.tb200_radix_sort(None, C.byref(need), None, None, n, capi.U64, 4, 0, 0, 64, stream), "size")
+    temp = torch.empty(need.value, dtype=torch.uint8, device="cuda:0")
+    out_k = torch.empty(n, dtype=torch.int64, device="cuda:0")
+    out_v = torch.empty(n, dtype=torch.int32, device="cuda:0")
+    g = 3
+    zeros = (C.c_uint64 * g)(0, 0, 0)
+    cnts = (C.c_uint64 * g)(*[a.size for a in parts_k])
+    capi.check(capi.lib.tb200_radix_sort_begin(C.c_void_p(temp.data_ptr()), C.byref(need), n, capi.U64, 4, stream), "begin")
+    capi.check(capi.lib.tb200_gather_segments(C.c_void_p(out_k.data_ptr()), (C.c_void_p * g)(*[d.data_ptr() for d in dk]),
+                                              zeros, cnts, g, 8, 1, C.c_void_p(temp.data_ptr()), stream), "gather keys")
+    capi.check(capi.lib.tb200_gather_segments(C.c_void_p(out_v.data_ptr()), (C.c_void_p * g)(*[d.data_ptr() for d in dv]),
+                                              zeros, cnts, g, 4, 1, None, stream), "gather values")
+    capi.check(capi.lib.tb200_radix_sort_finish(C.c_void_p(temp.data_ptr()), C.byref(need), C.c_void_p(out_k.data_ptr()),
+                                                C.c_void_p(out_v.data_ptr()), n, capi.U64, 4, stream), "finish")
+    capi.check(capi.lib.tb200_temp_status(C.c_void_p(temp.data_ptr()), stream), "status")
+    wk, wv = oracle.port().sort_by_key(np.concatenate(parts_k), np.concatenate(parts_v))
+    assert to_host(out_k, np.uint64).tobytes() == wk.tobytes()
+    assert to_host(out_v, np.uint32).tobytes() == wv.tobytes()

@@ -102,6 +102,42 @@ struct alignas(16) KeyVec {
   UK v[16 / sizeof(UK)];
 };
 
+// One CTA of kHistThreads threads: exclusive offsets per pass, skip flags, ping-pong bookkeeping.
+__device__ __forceinline__ void finalize_histograms(SortCtl* ctl, int num_passes, uint64_t n,
+                                                    unsigned long long* s_warp_tot) {
+  unsigned exec = 0, last = 0;
+  for (int p = 0; p < num_passes; ++p) {
+    unsigned long long c = 0;
+    if (threadIdx.x < kRadix) c = ld_relaxed_u64(&ctl->hist[p][threadIdx.x]);
+    const int all_here = __syncthreads_or(threadIdx.x < kRadix && c == n);
+    // block-exclusive scan over the 256 digits (threads 0..255 = 8 warps)
+    unsigned long long s = c;
+    const unsigned lane = lane_id(), warp = threadIdx.x / kWarp;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long t = __shfl_up_sync(0xffffffffu, s, off);
+      if (lane >= off) s += t;
+    }
+    if (threadIdx.x < kRadix && lane == 31) s_warp_tot[warp] = s;
+    __syncthreads();
+    if (threadIdx.x < kRadix) {
+      unsigned long long base = 0;
+      for (unsigned w = 0; w < warp; ++w) base += s_warp_tot[w];
+      ctl->offs[p][threadIdx.x] = base + s - c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ctl->skip[p] = all_here ? 1u : 0u;
+      ctl->exec_before[p] = exec;
+    }
+    if (!all_here) { last = p; ++exec; }
+  }
+  if (threadIdx.x == 0) {
+    ctl->total_exec = exec;
+    ctl->last_pass = last;
+  }
+}
+
 template <typename UK>
 __global__ void __launch_bounds__(kHistThreads)
 histogram_kernel(const UK* __restrict__ keys, uint64_t n, int begin_bit, int end_bit, int num_passes,
@@ -156,38 +192,15 @@ histogram_kernel(const UK* __restrict__ keys, uint64_t n, int begin_bit, int end
   if (!s_last) return;
   __threadfence();
 
-  // last CTA: exclusive offsets per pass, skip flags, ping-pong bookkeeping
-  unsigned exec = 0, last = 0;
-  for (int p = 0; p < num_passes; ++p) {
-    unsigned long long c = 0;
-    if (threadIdx.x < kRadix) c = ld_relaxed_u64(&ctl->hist[p][threadIdx.x]);
-    const int all_here = __syncthreads_or(threadIdx.x < kRadix && c == n);
-    // block-exclusive scan over the 256 digits (threads 0..255 = 8 warps)
-    unsigned long long s = c;
-    const unsigned lane = lane_id(), warp = threadIdx.x / kWarp;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const unsigned long long t = __shfl_up_sync(0xffffffffu, s, off);
-      if (lane >= off) s += t;
-    }
-    if (threadIdx.x < kRadix && lane == 31) s_warp_tot[warp] = s;
-    __syncthreads();
-    if (threadIdx.x < kRadix) {
-      unsigned long long base = 0;
-      for (unsigned w = 0; w < warp; ++w) base += s_warp_tot[w];
-      ctl->offs[p][threadIdx.x] = base + s - c;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      ctl->skip[p] = all_here ? 1u : 0u;
-      ctl->exec_before[p] = exec;
-    }
-    if (!all_here) { last = p; ++exec; }
-  }
-  if (threadIdx.x == 0) {
-    ctl->total_exec = exec;
-    ctl->last_pass = last;
-  }
+  finalize_histograms(ctl, num_passes, n, s_warp_tot);
+}
+
+// Finalisation alone, for histograms that another kernel accumulated (the gather of the
+// sharded sort counts the digits of the keys it moves).
+__global__ void __launch_bounds__(kHistThreads)
+histogram_finalize_kernel(SortCtl* ctl, int num_passes, uint64_t n) {
+  __shared__ unsigned long long s_warp_tot[8];
+  finalize_histograms(ctl, num_passes, n, s_warp_tot);
 }
 
 // ---------------------------------------------------------------------------------
@@ -587,6 +600,10 @@ copy_back_kernel(uint4* __restrict__ keys_main, const uint4* __restrict__ keys_a
 // ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
+// tb200_radix_sort runs both phases; the sharded sort splits them around its gather kernel,
+// which accumulates the digit histograms itself.
+enum { kPhaseAll = 0, kPhaseBegin = 1, kPhaseFinish = 2 };
+
 template <typename UK, int VB>
 struct Tuning {
   // threads x items per thread of one onesweep tile, and CTAs the register budget must allow per SM
@@ -618,7 +635,7 @@ inline Layout make_layout(uint64_t n, int key_bytes, int val_bytes, uint64_t til
 
 template <typename UK, int VB>
 int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n, int kind,
-              int descending, int begin_bit, int end_bit, cudaStream_t stream) {
+              int descending, int begin_bit, int end_bit, cudaStream_t stream, int phase = kPhaseAll) {
   using T = Tuning<UK, VB>;
   using Shape = PassShape<UK, VB, T::kThreads, T::kItems>;
   constexpr uint64_t TILE = Shape::kTile;
@@ -635,11 +652,12 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   char* base = static_cast<char*>(d_temp);
   auto* ctl = reinterpret_cast<SortCtl*>(base + lay.ctl_off);
   if (n <= 1 || begin_bit >= end_bit) {
-    TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, sizeof(int), stream));
+    if (phase != kPhaseFinish) TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, sizeof(int), stream));
     return TB200_OK;
   }
+  if (phase != kPhaseFinish) TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
+  if (phase == kPhaseBegin) return TB200_OK;
   if (d_keys == nullptr || (VB && d_vals == nullptr)) return TB200_ERR_INVALID_ARGUMENT;
-  TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
 
   Encoding enc;
   const unsigned long long sign = 1ull << (8 * sizeof(UK) - 1);
@@ -652,7 +670,11 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   TB200_CUDA_TRY(cudaGetDevice(&dev));
   TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-  {
+  if (phase == kPhaseFinish) {
+    histogram_finalize_kernel<<<1, kHistThreads, 0, stream>>>(ctl, num_passes, n);
+    trace_mark(stream, kTraceSortHistogram);
+    TB200_CUDA_TRY(cudaGetLastError());
+  } else {
     const uint64_t chunk = (uint64_t)kHistThreads * (16 / sizeof(UK)) * kHistUnroll;
     const uint64_t want = (n + chunk - 1) / chunk;
     const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
@@ -829,14 +851,14 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
 
 template <typename UK>
 int sort_vals(int val_bytes, void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n, int kind,
-              int descending, int begin_bit, int end_bit, cudaStream_t stream) {
+              int descending, int begin_bit, int end_bit, cudaStream_t stream, int phase = kPhaseAll) {
   switch (val_bytes) {
-    case 0: return sort_impl<UK, 0>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
-    case 1: return sort_impl<UK, 1>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
-    case 2: return sort_impl<UK, 2>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
-    case 4: return sort_impl<UK, 4>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
-    case 8: return sort_impl<UK, 8>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
-    case 16: return sort_impl<UK, 16>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream);
+    case 0: return sort_impl<UK, 0>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
+    case 1: return sort_impl<UK, 1>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
+    case 2: return sort_impl<UK, 2>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
+    case 4: return sort_impl<UK, 4>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
+    case 8: return sort_impl<UK, 8>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
+    case 16: return sort_impl<UK, 16>(d_temp, temp_bytes, d_keys, d_vals, n, kind, descending, begin_bit, end_bit, stream, phase);
     default: return TB200_ERR_UNSUPPORTED;
   }
 }
@@ -887,4 +909,159 @@ extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_k
   }
 #undef TB200_PART
   return TB200_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------
+// Exchange step of the sharded sort, fused with the first step of the sort that follows it:
+// one kernel pulls this GPU's runs out of the peers' buffers (plain loads over NVLink) and,
+// for the keys, counts the digits of all eight passes on the way.
+// ---------------------------------------------------------------------------------------
+namespace tb200 {
+namespace {
+
+constexpr int kMaxSegments = 16;
+
+struct GatherArgs {
+  const void* src[kMaxSegments];     // may point into another GPU's memory (peer mapping)
+  unsigned long long count[kMaxSegments];
+  unsigned long long dst_off[kMaxSegments];
+  int num_segments;
+  int rotate;
+};
+
+// Every CTA walks all segments with a grid-stride loop. The source side (possibly across
+// NVLink) is read with 16-byte loads, eight in flight per thread, after peeling the few
+// elements in front of the first 16-byte boundary of the source; the destination is local
+// and is written element by element (its alignment is independent of the source's).
+// CTAs start on different segments (CTA b on segment (b + rotate) mod count) and then walk
+// all of them cyclically, so at any moment the loads of one GPU are spread over all source
+// GPUs, and with `rotate` = the caller's rank the pullers are spread over the sources too.
+// HIST (64-bit keys only): the digits of every moved key are counted for all eight radix
+// passes in shared memory and added to the sort's control block at the end.
+template <typename T, bool HIST>
+__global__ void __launch_bounds__(512)
+gather_segments_kernel(T* __restrict__ dst, const GatherArgs args, SortCtl* ctl) {
+  constexpr int U = 8;
+  constexpr int V = 16 / sizeof(T);  // elements per 16-byte load
+  __shared__ unsigned s_hist[HIST ? 8 : 1][HIST ? kRadix : 1];
+  if constexpr (HIST) {
+    for (int i = threadIdx.x; i < 8 * kRadix; i += blockDim.x) (&s_hist[0][0])[i] = 0;
+    __syncthreads();
+  }
+  auto count = [&](T e) {
+    if constexpr (HIST) {
+      const unsigned long long k = (unsigned long long)e;
+#pragma unroll
+      for (int p = 0; p < 8; ++p) atomicAdd(&s_hist[p][(unsigned)(k >> (8 * p)) & 0xffu], 1u);
+    }
+  };
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int k = 0; k < args.num_segments; ++k) {
+    const int s = (int)((blockIdx.x + (unsigned)args.rotate + (unsigned)k) % (unsigned)args.num_segments);
+    const T* __restrict__ src = static_cast<const T*>(args.src[s]);
+    T* __restrict__ out = dst + args.dst_off[s];
+    const unsigned long long n = args.count[s];
+    if constexpr (V == 1) {
+      unsigned long long i = tid;
+      for (; i + (U - 1) * stride < n; i += U * stride) {
+        T v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < U; ++u) out[i + u * stride] = v[u];
+      }
+      for (; i < n; i += stride) out[i] = src[i];
+    } else {
+      unsigned long long head = ((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15) / sizeof(T);
+      if (head > n) head = n;
+      if (tid < head) { const T e = src[tid]; out[tid] = e; count(e); }
+      const uint4* __restrict__ vsrc = reinterpret_cast<const uint4*>(src + head);
+      T* __restrict__ vout = out + head;
+      const unsigned long long nvec = (n - head) / V;
+      unsigned long long i = tid;
+      auto emit = [&](unsigned long long at, const uint4& q) {
+        const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+        for (int j = 0; j < V; ++j) { vout[at * V + j] = e[j]; count(e[j]); }
+      };
+      for (; i + (U - 1) * stride < nvec; i += U * stride) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = vsrc[i + u * stride];
+#pragma unroll
+        for (int u = 0; u < U; ++u) emit(i + u * stride, v[u]);
+      }
+      for (; i < nvec; i += stride) emit(i, vsrc[i]);
+      const unsigned long long done = head + nvec * V;
+      if (tid < n - done) { const T e = src[done + tid]; out[done + tid] = e; count(e); }
+    }
+  }
+  if constexpr (HIST) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 8 * kRadix; i += blockDim.x) {
+      const unsigned c = (&s_hist[0][0])[i];
+      if (c) atomicAdd(&ctl->hist[0][0] + i, (unsigned long long)c);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
+                                     const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
+                                     uint32_t rotate, void* d_sort_temp, tb200_stream_t stream) {
+  using namespace tb200;
+  if (num_segments > (uint32_t)kMaxSegments) return TB200_ERR_UNSUPPORTED;
+  if (num_segments && (!d_dst || !h_src || !h_src_offset || !h_count)) return TB200_ERR_INVALID_ARGUMENT;
+  if (elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return TB200_ERR_UNSUPPORTED;
+  if (d_sort_temp && elem_bytes != 8) return TB200_ERR_UNSUPPORTED;
+  GatherArgs a{};
+  a.num_segments = (int)num_segments;
+  a.rotate = (int)(num_segments ? rotate % num_segments : 0);
+  unsigned long long off = 0;
+  for (uint32_t s = 0; s < num_segments; ++s) {
+    a.src[s] = static_cast<const char*>(h_src[s]) + h_src_offset[s] * (uint64_t)elem_bytes;
+    a.count[s] = h_count[s];
+    a.dst_off[s] = off;
+    off += h_count[s];
+  }
+  if (off == 0) return TB200_OK;
+  int dev = 0, sms = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const unsigned grid = (unsigned)sms * 4;
+  auto* ctl = static_cast<SortCtl*>(d_sort_temp);
+  switch (elem_bytes) {
+    case 4:
+      gather_segments_kernel<uint32_t, false><<<grid, 512, 0, stream>>>(static_cast<uint32_t*>(d_dst), a, nullptr);
+      break;
+    case 8:
+      if (ctl) gather_segments_kernel<unsigned long long, true><<<grid, 512, 0, stream>>>(static_cast<unsigned long long*>(d_dst), a, ctl);
+      else     gather_segments_kernel<unsigned long long, false><<<grid, 512, 0, stream>>>(static_cast<unsigned long long*>(d_dst), a, nullptr);
+      break;
+    default:
+      gather_segments_kernel<uint4, false><<<grid, 512, 0, stream>>>(static_cast<uint4*>(d_dst), a, nullptr);
+      break;
+  }
+  trace_mark(stream, kTraceOther);
+  return (int)cudaGetLastError();
+}
+
+// The two halves of tb200_radix_sort for uint64 keys sorted whole, around a gather that counts.
+extern "C" int tb200_radix_sort_begin(void* d_temp, size_t* temp_bytes, uint64_t n, int key_dtype, int val_bytes,
+                                      tb200_stream_t stream) {
+  using namespace tb200;
+  if (temp_bytes == nullptr || d_temp == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  if (key_dtype != TB200_U64) return TB200_ERR_UNSUPPORTED;
+  return sort_vals<unsigned long long>(val_bytes, d_temp, temp_bytes, nullptr, nullptr, n, 0, 0, 0, 64, stream, kPhaseBegin);
+}
+
+extern "C" int tb200_radix_sort_finish(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint64_t n,
+                                       int key_dtype, int val_bytes, tb200_stream_t stream) {
+  using namespace tb200;
+  if (temp_bytes == nullptr || d_temp == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  if (key_dtype != TB200_U64) return TB200_ERR_UNSUPPORTED;
+  return sort_vals<unsigned long long>(val_bytes, d_temp, temp_bytes, d_keys, d_vals, n, 0, 0, 0, 64, stream, kPhaseFinish);
 }

@@ -242,109 +242,3 @@ extern "C" int tb200_reduce_by_key_host(const void* h_keys_in, const void* h_val
   *h_num_runs = runs;
   return tb200_temp_status(d_temp, stream);
 }
-
-// ---------------------------------------------------------------------------------------
-// Segment gather: the exchange step of the sharded sort as ONE kernel of peer loads.
-// ---------------------------------------------------------------------------------------
-namespace tb200 {
-namespace {
-
-constexpr int kMaxSegments = 16;
-
-struct GatherArgs {
-  const void* src[kMaxSegments];     // may point into another GPU's memory (peer mapping)
-  unsigned long long count[kMaxSegments];
-  unsigned long long dst_off[kMaxSegments];
-  int num_segments;
-  int rotate;
-};
-
-// Every CTA walks all segments with a grid-stride loop. The source side (possibly across
-// NVLink) is read with 16-byte loads, eight in flight per thread, after peeling the few
-// elements in front of the first 16-byte boundary of the source; the destination is local
-// and is written element by element (its alignment is independent of the source's).
-template <typename T>
-__global__ void __launch_bounds__(512)
-gather_segments_kernel(T* __restrict__ dst, const GatherArgs args) {
-  constexpr int U = 8;
-  constexpr int V = 16 / sizeof(T);  // elements per 16-byte load
-  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
-  const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
-  // CTAs start on different segments (CTA b on segment (b + rotate) mod count) and then walk
-  // all of them cyclically, so at any moment the loads of one GPU are spread over all source
-  // GPUs, and with `rotate` = the caller's rank the pullers are spread over the sources too.
-  for (int k = 0; k < args.num_segments; ++k) {
-    const int s = (int)((blockIdx.x + (unsigned)args.rotate + (unsigned)k) % (unsigned)args.num_segments);
-    const T* __restrict__ src = static_cast<const T*>(args.src[s]);
-    T* __restrict__ out = dst + args.dst_off[s];
-    const unsigned long long n = args.count[s];
-    if constexpr (V == 1) {
-      unsigned long long i = tid;
-      for (; i + (U - 1) * stride < n; i += U * stride) {
-        T v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = src[i + u * stride];
-#pragma unroll
-        for (int u = 0; u < U; ++u) out[i + u * stride] = v[u];
-      }
-      for (; i < n; i += stride) out[i] = src[i];
-    } else {
-      unsigned long long head = ((16 - (reinterpret_cast<uintptr_t>(src) & 15)) & 15) / sizeof(T);
-      if (head > n) head = n;
-      if (tid < head) out[tid] = src[tid];
-      const uint4* __restrict__ vsrc = reinterpret_cast<const uint4*>(src + head);
-      T* __restrict__ vout = out + head;
-      const unsigned long long nvec = (n - head) / V;
-      unsigned long long i = tid;
-      auto emit = [&](unsigned long long at, const uint4& q) {
-        const T* e = reinterpret_cast<const T*>(&q);
-#pragma unroll
-        for (int j = 0; j < V; ++j) vout[at * V + j] = e[j];
-      };
-      for (; i + (U - 1) * stride < nvec; i += U * stride) {
-        uint4 v[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = vsrc[i + u * stride];
-#pragma unroll
-        for (int u = 0; u < U; ++u) emit(i + u * stride, v[u]);
-      }
-      for (; i < nvec; i += stride) emit(i, vsrc[i]);
-      const unsigned long long done = head + nvec * V;
-      if (tid < n - done) out[done + tid] = src[done + tid];
-    }
-  }
-}
-
-}  // namespace
-}  // namespace tb200
-
-extern "C" int tb200_gather_segments(void* d_dst, const void* const* h_src, const uint64_t* h_src_offset,
-                                     const uint64_t* h_count, uint32_t num_segments, int elem_bytes,
-                                     uint32_t rotate, tb200_stream_t stream) {
-  using namespace tb200;
-  if (num_segments > (uint32_t)kMaxSegments) return TB200_ERR_UNSUPPORTED;
-  if (num_segments && (!d_dst || !h_src || !h_src_offset || !h_count)) return TB200_ERR_INVALID_ARGUMENT;
-  if (elem_bytes != 4 && elem_bytes != 8 && elem_bytes != 16) return TB200_ERR_UNSUPPORTED;
-  GatherArgs a{};
-  a.num_segments = (int)num_segments;
-  a.rotate = (int)(num_segments ? rotate % num_segments : 0);
-  unsigned long long off = 0;
-  for (uint32_t s = 0; s < num_segments; ++s) {
-    a.src[s] = static_cast<const char*>(h_src[s]) + h_src_offset[s] * (uint64_t)elem_bytes;
-    a.count[s] = h_count[s];
-    a.dst_off[s] = off;
-    off += h_count[s];
-  }
-  if (off == 0) return TB200_OK;
-  int dev = 0, sms = 0;
-  TB200_CUDA_TRY(cudaGetDevice(&dev));
-  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const unsigned grid = (unsigned)sms * 4;
-  switch (elem_bytes) {
-    case 4: gather_segments_kernel<uint32_t><<<grid, 512, 0, stream>>>(static_cast<uint32_t*>(d_dst), a); break;
-    case 8: gather_segments_kernel<unsigned long long><<<grid, 512, 0, stream>>>(static_cast<unsigned long long*>(d_dst), a); break;
-    default: gather_segments_kernel<uint4><<<grid, 512, 0, stream>>>(static_cast<uint4*>(d_dst), a); break;
-  }
-  trace_mark(stream, kTraceOther);
-  return (int)cudaGetLastError();
-}

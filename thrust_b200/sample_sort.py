@@ -93,7 +93,22 @@ class DeviceOps:
                                             C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
         return counts
 
-    def gather(self, dst: torch.Tensor, src_ptrs, src_offsets, counts, elem_bytes: int, rotate: int = 0) -> None:
+    def sort_begin(self, n: int) -> None:
+        """First half of sort_pairs: clears the scratch; the key gather then counts the digits."""
+        capi = self.capi
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_radix_sort_begin(C.c_void_p(self.temp.data_ptr()), C.byref(have), n, capi.U64, 4,
+                                                   self._stream()), "tb200_radix_sort_begin")
+
+    def sort_finish(self, keys: torch.Tensor, vals: torch.Tensor, n: int) -> None:
+        capi = self.capi
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_radix_sort_finish(C.c_void_p(self.temp.data_ptr()), C.byref(have),
+                                                    C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), n,
+                                                    capi.U64, 4, self._stream()), "tb200_radix_sort_finish")
+
+    def gather(self, dst: torch.Tensor, src_ptrs, src_offsets, counts, elem_bytes: int, rotate: int = 0,
+               count_digits: bool = False) -> None:
         """dst[:sum(counts)] = concatenation of counts[s] elements at src_ptrs[s] + src_offsets[s]
         (device pointers, possibly peer mappings): tb200_gather_segments."""
         capi = self.capi
@@ -101,8 +116,9 @@ class DeviceOps:
         ptrs = (C.c_void_p * g)(*src_ptrs)
         offs = (C.c_uint64 * g)(*src_offsets)
         cnts = (C.c_uint64 * g)(*counts)
+        hist = C.c_void_p(self.temp.data_ptr()) if count_digits else None
         capi.check(capi.lib.tb200_gather_segments(C.c_void_p(dst.data_ptr()), ptrs, offs, cnts, g, elem_bytes, rotate,
-                                                  self._stream()), "tb200_gather_segments")
+                                                  hist, self._stream()), "tb200_gather_segments")
 
     def status(self) -> int:
         return int(self.capi.lib.tb200_temp_status(C.c_void_p(self.temp.data_ptr()), self._stream()))
@@ -267,10 +283,16 @@ class ShardedSorter:
             # The count matrix arrived through a collective that every rank entered after its
             # partition kernel, so all partition buffers are complete.
             src_off = [int(mat[r, :self.rank].sum()) for r in range(G)]
-            self.ops.gather(self.recv_k, self.peer_k, src_off, recv_l, 8, self.rank)
+            # The key gather also counts the digits of all eight passes of the sort that follows.
+            self.ops.sort_begin(m)
+            self.ops.gather(self.recv_k, self.peer_k, src_off, recv_l, 8, self.rank, count_digits=True)
             self.ops.gather(self.recv_v, self.peer_v, src_off, recv_l, 4, self.rank)
             # nobody may overwrite its partition buffer (next call) before all pulls are done
             dist.barrier(group=self.group)
+            self._mark("exchange")
+            self.ops.sort_finish(self.recv_k, self.recv_v, m)
+            self._mark("final_sort")
+            return self.recv_k, self.recv_v, m
         else:
             dist.all_to_all_single(self.recv_k[:m], src_k[:n], recv_l, send_l, group=self.group)
             dist.all_to_all_single(self.recv_v[:m], src_v[:n], recv_l, send_l, group=self.group)
