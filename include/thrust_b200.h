@@ -159,6 +159,12 @@ int tb200_histogram_sorted(const void* d_sorted, uint64_t n, int dtype, const vo
  * (thrust/system/cuda/detail/util.h:113-140, 251-299). */
 int tb200_temp_status(const void* d_temp, tb200_stream_t stream);
 
+/* Self-test of the bounded-wait convention every kernel here follows: launches one warp that
+ * polls a flag nothing ever sets, for at most limit_polls polls (1 .. 2^20), and returns the
+ * device status it reports — TB200_ERR_WAIT_TIMEOUT — after which the context is still
+ * usable. (The reference's device code prints and traps on errors, util.h:202-205.) */
+int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream);
+
 /* ---- launch tracing -------------------------------------------------------------------
  * Plays the role of the reference's THRUST_DEBUG_SYNC launch log
  * (thrust/system/cuda/detail/core/agent_launcher.h:501-560) without a sync per launch:

@@ -66,3 +66,23 @@ def test_host_generators_are_counter_based():
     assert not np.isnan(k).any()
     r = g.host(g.ZIPF_RANK_U32, 1 << 16, 5, cdf=g.zipf_cdf())
     assert r.max() < (1 << 16) and (r == 0).mean() > 0.1
+
+
+def test_argument_validation_precedes_any_device_work():
+    """Host-side fault injection: bad scratch is refused before anything touches a GPU."""
+    from thrust_b200 import _capi as capi
+    need = C.c_size_t(0)
+    assert capi.lib.tb200_scan(None, C.byref(need), None, None, 1 << 16, capi.I64, 0, None, None) == 0
+    fake = C.c_void_p(0x7f0000000100 + 8)  # never dereferenced: not 256-byte aligned
+    assert capi.lib.tb200_scan(fake, C.byref(need), fake, fake, 1 << 16, capi.I64, 0, None, None) == capi.ERR_INVALID_ARGUMENT
+    small = C.c_size_t(16)
+    fake = C.c_void_p(0x7f0000000100)
+    assert capi.lib.tb200_scan(fake, C.byref(small), fake, fake, 1 << 16, capi.I64, 0, None, None) == capi.ERR_TEMP_TOO_SMALL
+    assert capi.lib.tb200_reduce_by_key(fake, C.byref(small), fake, fake, fake, fake, fake, 1 << 16, capi.I32, capi.F32,
+                                        None) == capi.ERR_TEMP_TOO_SMALL
+    assert capi.lib.tb200_partition(None, C.byref(need), None, None, None, None, 10, capi.U64, 4, None, 300, None,
+                                    None) == capi.ERR_INVALID_ARGUMENT
+    assert capi.lib.tb200_partition(None, C.byref(need), None, None, None, None, 10, capi.F32, 4, None, 3, None,
+                                    None) == capi.ERR_UNSUPPORTED
+    assert capi.lib.tb200_gather_segments(None, None, None, None, 17, 8, 0, None, None) == capi.ERR_UNSUPPORTED
+    assert capi.lib.tb200_scan_static(None, None, 1 << 40, capi.F32, 0, None, None) == capi.ERR_OVERFLOW

@@ -242,3 +242,37 @@ extern "C" int tb200_reduce_by_key_host(const void* h_keys_in, const void* h_val
   *h_num_runs = runs;
   return tb200_temp_status(d_temp, stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded-wait convention: a kernel polls a flag that nothing sets, with
+// the same loop shape the look-back chains use, gives up after `limit_polls` polls and
+// reports TB200_ERR_WAIT_TIMEOUT through a status word — the context stays usable.
+// ---------------------------------------------------------------------------------------
+namespace tb200 {
+namespace {
+__global__ void selftest_wait_kernel(const unsigned* flag, unsigned limit_polls, int* status) {
+  unsigned polls = 0;
+  while (ld_relaxed_u32(flag) == 0u) {
+    backoff(++polls);
+    if (polls >= limit_polls) {
+      atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+      break;
+    }
+  }
+}
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream) {
+  using namespace tb200;
+  if (limit_polls == 0 || limit_polls > (1u << 20)) return TB200_ERR_INVALID_ARGUMENT;
+  void* ws = nullptr;
+  int rc = tb200_workspace_acquire(512, stream, &ws);
+  if (rc) return rc;
+  TB200_CUDA_TRY(cudaMemsetAsync(ws, 0, 512, stream));
+  int* status = static_cast<int*>(ws);
+  const unsigned* flag = reinterpret_cast<const unsigned*>(static_cast<char*>(ws) + 256);
+  selftest_wait_kernel<<<1, 32, 0, stream>>>(flag, limit_polls, status);
+  TB200_CUDA_TRY(cudaGetLastError());
+  return tb200_temp_status(ws, stream);
+}
