@@ -21,7 +21,7 @@ pytestmark = pytest.mark.gpu
 ALL_TYPES = [np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32, np.int64, np.uint64,
              np.float32, np.float64, np.bool_]
 SIZES = [0, 1, 2, 3, 31, 32, 33, 255, 1000, 3071, 3072, 3073, 4095, 4096, 4097, 6143, 6144, 6145,
-         10027, 65537, 300007]
+         8191, 8192, 8193, 10027, 10239, 10240, 10241, 65537, 300007]  # incl. tile sizes +-1
 
 
 @pytest.mark.parametrize("dtype", ALL_TYPES)
@@ -39,7 +39,7 @@ def test_sort_keys_all_sizes(cuda_device, dtype):
 @pytest.mark.parametrize("dtype", ALL_TYPES)
 def test_stable_sort_by_key_independent_values(cuda_device, dtype):
     chk = oracle.port()
-    for n in [0, 1, 2, 33, 1000, 6145, 65537, 300007]:
+    for n in [0, 1, 2, 33, 1000, 6145, 8193, 10241, 65537, 300007]:
         rng = np.random.default_rng(2000 + n)
         k = random_keys(rng, n, dtype)
         v = rng.integers(0, 1 << 32, size=n, dtype=np.uint32)
