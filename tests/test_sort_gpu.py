@@ -286,3 +286,36 @@ def test_gather_that_counts_digits_then_sort_finish(cuda_device):
     wk, wv = oracle.port().sort_by_key(np.concatenate(parts_k), np.concatenate(parts_v))
     assert to_host(out_k, np.uint64).tobytes() == wk.tobytes()
     assert to_host(out_v, np.uint32).tobytes() == wv.tobytes()
+
+
+def test_sort_more_than_2_pow_30_keys(cuda_device):
+    """n > 2^30 switches the look-back descriptors and output indices to 64 bits."""
+    from thrust_b200 import datagen as g
+    n = (1 << 30) + 12345
+    k = g.device(g.BITS_U32, n, 99, dev=cuda_device)  # int32 tensor holding uint32 bit patterns
+    before_sum = int(k.view(torch.int32).sum(dtype=torch.int64))
+    before_xor = 0
+    for s in range(0, n, 1 << 28):  # xor checksum in chunks (bitwise ops keep int32)
+        c = k[s:s + (1 << 28)]
+        while c.numel() > 1:
+            h = c.numel() // 2
+            c = torch.cat([c[:h] ^ c[h:2 * h], c[2 * h:]])
+        before_xor ^= int(c.item())
+    tb.sort(k, key_dtype=capi.U32)
+    u = k.view(torch.int32)
+    # unsigned order: compare after flipping the sign bit, chunk by chunk
+    ok = True
+    for s in range(0, n - 1, 1 << 28):
+        e = min(n, s + (1 << 28) + 1)
+        f = u[s:e] ^ (-2147483648)
+        ok = ok and bool((f[1:] >= f[:-1]).all())
+    assert ok
+    assert int(u.sum(dtype=torch.int64)) == before_sum
+    after_xor = 0
+    for s in range(0, n, 1 << 28):
+        c = k[s:s + (1 << 28)]
+        while c.numel() > 1:
+            h = c.numel() // 2
+            c = torch.cat([c[:h] ^ c[h:2 * h], c[2 * h:]])
+        after_xor ^= int(c.item())
+    assert after_xor == before_xor

@@ -395,6 +395,81 @@ onesweep_kernel(const PassParams prm) {
   load_keys(tile);
   __syncthreads();  // everyone has read s_next before it is overwritten
 
+  // The sorted keys and values of a tile stay parked in shared memory while the CTA ranks the
+  // NEXT tile (ranking needs only registers and the per-warp counters). The parked tile's
+  // look-back and scatter run after that ranking: by then the predecessor tiles it waits for
+  // have had a whole ranking phase to publish their counts, so the in-order dependency of
+  // the chained scan costs almost no idle time.
+  bool parked = false;
+  unsigned p_tile = 0, p_valid = 0, p_count = 0, p_digit_start = 0;
+  const unsigned d_own = threadIdx.x % kRadix;
+  const unsigned grp = threadIdx.x / kRadix;
+  auto flush_parked = [&]() {
+      // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
+      // fetches kWindow descriptors at once and consumes them nearest first.
+      if (grp == 0) {
+        const unsigned d = d_own;
+        unsigned long long excl = 0;
+  #ifdef TB200_EXPERIMENT_NO_LOOKBACK  // timing experiments only: results are wrong
+        if (false) {
+  #else
+        if (p_tile != 0) {
+  #endif
+  #ifndef TB200_SORT_WINDOW
+  #define TB200_SORT_WINDOW 4
+  #endif
+          constexpr int kWindow = TB200_SORT_WINDOW;
+          const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
+          const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
+          long long t = (long long)p_tile - 1;
+          bool timed_out = false, done = false;
+          while (!done && !timed_out) {
+            DescT v[kWindow];
+  #pragma unroll
+            for (int i = 0; i < kWindow; ++i)
+              v[i] = t - i >= 0 ? ld_desc<DescT>(chain + (size_t)(t - i) * kRadix) : below_first;
+  #pragma unroll
+            for (int i = 0; i < kWindow; ++i) {
+              if (done || timed_out) break;
+              unsigned polls = 0;
+              while ((unsigned)(v[i] >> DSH) == st_empty) {
+                backoff(++polls);
+                if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
+                  timed_out = true;
+                  break;
+                }
+                v[i] = ld_desc<DescT>(chain + (size_t)(t - i) * kRadix);
+              }
+              if (timed_out) break;
+              excl += (unsigned long long)(v[i] & DescBits<DescT>::kValueMask);
+              done = (unsigned)(v[i] >> DSH) == st_prefix;
+            }
+            t -= kWindow;
+          }
+          if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
+          DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)p_tile * kRadix + d;
+          st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + p_count) & DescBits<DescT>::kValueMask));
+        }
+        s_gbase[d] = (IdxT)(pass_offset + excl - p_digit_start);
+      }
+      __syncthreads();
+      // ---- scatter: every digit leaves as one contiguous run
+      auto emit = [&](unsigned pos) {
+        const UK k = s_keys[pos];
+        const IdxT g = s_gbase[digit(k)] + pos;
+        dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
+        if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
+      };
+      if (p_valid == (unsigned)TILE) {
+  #pragma unroll
+        for (int i = 0; i < ITEMS; ++i) emit(threadIdx.x + i * THREADS);
+      } else {
+  #pragma unroll
+        for (int i = 0; i < ITEMS; ++i)
+          if (threadIdx.x + i * THREADS < p_valid) emit(threadIdx.x + i * THREADS);
+      }
+  };
+
   while (true) {
     const uint64_t tile_base = (uint64_t)tile * TILE;
     const uint64_t remaining = prm.n - tile_base;
@@ -443,8 +518,6 @@ onesweep_kernel(const PassParams prm) {
     // group; group totals are combined through shared memory. The tile's counts are
     // published BEFORE any local reordering so that successor tiles can use them
     // while this CTA is still busy.
-    const unsigned d_own = threadIdx.x % kRadix;
-    const unsigned grp = threadIdx.x / kRadix;
     unsigned part = 0;
 #pragma unroll 4
     for (int w = 0; w < WARPS_PER_GROUP; ++w) {
@@ -485,7 +558,11 @@ onesweep_kernel(const PassParams prm) {
 #pragma unroll 4
       for (int w = 0; w < WARPS_PER_GROUP; ++w) s_whist[(grp * WARPS_PER_GROUP + w) * kRadix + d_own] += add;
     }
-    __syncthreads();
+
+#ifndef TB200_SORT_FLUSH_IMMEDIATELY
+    if (parked) flush_parked();  // tile i-1 leaves while tile i's counts are already published
+#endif
+    __syncthreads();  // counters hold slot offsets; the shared tile buffers are free
 
     // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
 #pragma unroll
@@ -502,73 +579,23 @@ onesweep_kernel(const PassParams prm) {
       for (int j = 0; j < ITEMS; ++j) s_vals[rank[j]] = val[j];  // padding slots lie beyond tile_valid
     }
 
-    // ---- look-back: global prefix of every digit over the predecessor tiles. A thread
-    // fetches kWindow descriptors at once and consumes them nearest first.
-    if (grp == 0) {
-      const unsigned d = d_own;
-      unsigned long long excl = 0;
-#ifdef TB200_EXPERIMENT_NO_LOOKBACK  // timing experiments only: results are wrong
-      if (false) {
-#else
-      if (tile != 0) {
-#endif
-#ifndef TB200_SORT_WINDOW
-#define TB200_SORT_WINDOW 4
-#endif
-        constexpr int kWindow = TB200_SORT_WINDOW;
-        const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
-        const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
-        long long t = (long long)tile - 1;
-        bool timed_out = false, done = false;
-        while (!done && !timed_out) {
-          DescT v[kWindow];
-#pragma unroll
-          for (int i = 0; i < kWindow; ++i)
-            v[i] = t - i >= 0 ? ld_desc<DescT>(chain + (size_t)(t - i) * kRadix) : below_first;
-#pragma unroll
-          for (int i = 0; i < kWindow; ++i) {
-            if (done || timed_out) break;
-            unsigned polls = 0;
-            while ((unsigned)(v[i] >> DSH) == st_empty) {
-              backoff(++polls);
-              if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(&ctl->status) != 0)) {
-                timed_out = true;
-                break;
-              }
-              v[i] = ld_desc<DescT>(chain + (size_t)(t - i) * kRadix);
-            }
-            if (timed_out) break;
-            excl += (unsigned long long)(v[i] & DescBits<DescT>::kValueMask);
-            done = (unsigned)(v[i] >> DSH) == st_prefix;
-          }
-          t -= kWindow;
-        }
-        if (timed_out) atomicExch(&ctl->status, (int)TB200_ERR_WAIT_TIMEOUT);
-        DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d;
-        st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + count) & DescBits<DescT>::kValueMask));
-      }
-      s_gbase[d] = (IdxT)(pass_offset + excl - digit_start);
-    }
+    parked = true;
+    p_tile = tile;
+    p_valid = tile_valid;
+    p_count = count;
+    p_digit_start = digit_start;
+#ifdef TB200_SORT_FLUSH_IMMEDIATELY
     __syncthreads();
-
-    // ---- scatter: every digit leaves as one contiguous run
-    auto emit = [&](unsigned pos) {
-      const UK k = s_keys[pos];
-      const IdxT g = s_gbase[digit(k)] + pos;
-      dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
-      if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
-    };
-    if (tile_valid == (unsigned)TILE) {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) emit(threadIdx.x + i * THREADS);
-    } else {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i)
-        if (threadIdx.x + i * THREADS < tile_valid) emit(threadIdx.x + i * THREADS);
-    }
+    flush_parked();
+    parked = false;
+#endif
     if (next >= num_tiles) break;
     tile = next;
-    __syncthreads();  // shared buffers are reused by the next tile
+    __syncthreads();  // counters are cleared and the tile buffers read by the next iteration
+  }
+  if (parked) {
+    __syncthreads();
+    flush_parked();
   }
 }
 
