@@ -282,13 +282,20 @@ reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* 
 #define TB200_RS_PACKS 3
 #define TB200_RS_PARK 2
 #endif
+#ifndef TB200_RS_LOADING
+#define TB200_RS_LOADING 1
+#endif
 constexpr int kRsThreads = TB200_RS_THREADS;
 constexpr int kRsWarps = kRsThreads / kWarp;
-constexpr int kRsLookWarps = 2;  // look-back warps; tile j of a CTA is resolved by warp j % 2
+#ifndef TB200_RS_LOOK_WARPS
+#define TB200_RS_LOOK_WARPS 1
+#endif
+constexpr int kRsLookWarps = TB200_RS_LOOK_WARPS;  // look-back warps; tile j of a CTA is resolved by warp j % count
 constexpr int kRsCta = kRsThreads + kRsLookWarps * kWarp;
 constexpr int kRsPacks = TB200_RS_PACKS;  // packs of E elements per thread
 constexpr int kRsPark = TB200_RS_PARK;
-constexpr int kRsStages = kRsPark + 2;
+constexpr int kRsLoading = TB200_RS_LOADING;  // tiles in flight from HBM beside the one being scanned
+constexpr int kRsStages = kRsPark + 1 + kRsLoading;
 constexpr unsigned kRsNoTile = 0xffffffffu;
 
 template <typename K, typename V>
@@ -400,6 +407,9 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
     const int slot = it_prev % S;
     mbar_wait_bounded(&s_resolved[slot], (it_prev / S) & 1u, status);
     unsigned heads = s_park_heads[slot][threadIdx.x];
+#ifdef TB200_EXPERIMENT_NO_FINALIZE
+    heads = 0;
+#endif
     if (heads) {
       const unsigned long long pc = s_prefix_cnt[slot];
       const V pv = s_prefix_val[slot];
@@ -532,6 +542,7 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
     }
     // park what the final pass needs: the run sums inside the thread (in place of the
     // values), the thread's head mask, and the state of the scan in front of the thread
+#ifndef TB200_EXPERIMENT_NO_PARK
     {
       const Seg<V> local = seg_combine(warp_prefix, lane_excl);
       s_park_heads[slot][threadIdx.x] = (unsigned short)heads;
@@ -545,6 +556,7 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
         mv[p] = rr;
       }
     }
+#endif
     if (it >= (unsigned)kRsPark) finalize(it - kRsPark, true);
     else named_barrier(1, kRsThreads);  // s_warp_* are rewritten by the next tile
   }
