@@ -29,7 +29,7 @@
 #include <type_traits>
 
 #ifndef TB200_MATCH_MODE
-#define TB200_MATCH_MODE 1  // 0: match.any instruction (slow on sm_100), 1: eight ballots
+#define TB200_MATCH_MODE 2  // 0: match.any instruction (slow on sm_100), 1: eight ballots in C++, 2: in PTX
 #endif
 
 namespace tb200 {
@@ -244,11 +244,38 @@ __device__ __forceinline__ void st_desc(DescT* p, DescT v) {
   else st_relaxed_u64(p, v);
 }
 
+template <int B>
+__device__ __forceinline__ void match_bit(unsigned& peers, unsigned d) {
+#ifdef TB200_MATCH_ASM_PLAIN
+  asm(
+#else
+  asm volatile(
+#endif
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b32 t, m, nm;\n"
+      "and.b32 t, %1, %2;\n"
+      "setp.ne.u32 p, t, 0;\n"
+      "vote.sync.ballot.b32 m, p, 0xffffffff;\n"
+      "not.b32 nm, m;\n"
+      "@p and.b32 %0, %0, m;\n"
+      "@!p and.b32 %0, %0, nm;\n"
+      "}\n"
+      : "+r"(peers)
+      : "r"(d), "n"(1 << B));
+}
+
 // Lanes of the warp that hold the same 8-bit digit. One ballot per bit; a lane keeps
 // the voters that agree with its own bit: peers &= ~(ballot ^ sign_extend(bit)).
 __device__ __forceinline__ unsigned match_digit(unsigned d) {
 #if TB200_MATCH_MODE == 0
   return __match_any_sync(0xffffffffu, d);
+#elif TB200_MATCH_MODE == 2
+  // four instructions per bit: test, vote, and one predicated AND for either polarity
+  unsigned peers = 0xffffffffu;
+  match_bit<0>(peers, d); match_bit<1>(peers, d); match_bit<2>(peers, d); match_bit<3>(peers, d);
+  match_bit<4>(peers, d); match_bit<5>(peers, d); match_bit<6>(peers, d); match_bit<7>(peers, d);
+  return peers;
 #else
   unsigned peers = 0xffffffffu;
 #pragma unroll
@@ -263,10 +290,16 @@ __device__ __forceinline__ unsigned match_digit(unsigned d) {
 // Same, for digits known to fit in `bits` bits (bucket ids of a partition): fewer ballots.
 __device__ __forceinline__ unsigned match_digit_bits(unsigned d, int bits) {
   unsigned peers = 0xffffffffu;
-  for (int b = 0; b < bits; ++b) {
-    const unsigned m = __ballot_sync(0xffffffffu, (d >> b) & 1u);
-    const unsigned t = 0u - ((d >> b) & 1u);
-    peers &= ~(m ^ t);
+  switch (bits) {  // bits is the same for the whole grid
+    case 8: match_bit<7>(peers, d); [[fallthrough]];
+    case 7: match_bit<6>(peers, d); [[fallthrough]];
+    case 6: match_bit<5>(peers, d); [[fallthrough]];
+    case 5: match_bit<4>(peers, d); [[fallthrough]];
+    case 4: match_bit<3>(peers, d); [[fallthrough]];
+    case 3: match_bit<2>(peers, d); [[fallthrough]];
+    case 2: match_bit<1>(peers, d); [[fallthrough]];
+    case 1: match_bit<0>(peers, d); [[fallthrough]];
+    default: break;
   }
   return peers;
 }
