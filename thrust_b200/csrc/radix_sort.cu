@@ -195,6 +195,124 @@ histogram_kernel(const UK* __restrict__ keys, uint64_t n, int begin_bit, int end
   finalize_histograms(ctl, num_passes, n, s_warp_tot);
 }
 
+// Whole-key variant of histogram_kernel (begin_bit = 0, end_bit = key width: what every sort of
+// the Thrust front end asks for). Every digit is a byte of the key at a compile-time position,
+// and the counters are laid out [pass][digit pair][lane]: each lane of a warp owns a bank, so the
+// one shared-memory atomic per key and pass meets no bank conflict (a single shared copy costs a
+// random-digit warp about 3.2 conflict cycles per atomic), and the address needs three
+// instructions. Two digits share a 32-bit word as 16-bit halves (16 KiB per pass); the CTA folds
+// the words into per-thread 64-bit totals before any half can reach 65536.
+constexpr int kByteHistThreads = 1024;
+
+// One count: byte (PASS & 3) of `w` is the digit of pass PASS; lane_base is the shared-memory
+// address of the calling lane's column of counters.
+template <int PASS>
+__device__ __forceinline__ void count_byte(unsigned w, unsigned lane_base) {
+  constexpr int b = 8 * (PASS & 3);
+  unsigned off;  // byte offset of the word of digit pair (d >> 1): ((w >> b) & 0xfe) << 6
+  if constexpr (b == 0) off = (w << 6) & 0x3f80u;
+  else off = (w >> (b - 6)) & 0x3f80u;
+  const unsigned inc = (w & (1u << b)) ? 0x10000u : 1u;
+  asm volatile("red.shared.add.u32 [%0 + %2], %1;" ::"r"(lane_base + off), "r"(inc), "n"(PASS * 16384) : "memory");
+}
+
+template <typename UK>
+__global__ void __launch_bounds__(kByteHistThreads, 1)
+histogram_bytes_kernel(const UK* __restrict__ keys, uint64_t n, Encoding enc, SortCtl* ctl, int aligned) {
+  constexpr int P = sizeof(UK);
+  constexpr int VEC = 16 / sizeof(UK);
+  constexpr int T = kByteHistThreads;
+  constexpr unsigned kHalfMax = 65535u;
+  constexpr int kEntries = P * (kRadix / 2);  // thread e owns digits 2e' and 2e'+1 of one pass
+  extern __shared__ __align__(16) unsigned s_cnt[];  // [P][128][32]
+  __shared__ unsigned s_last;
+  __shared__ unsigned long long s_warp_tot[8];
+
+  const unsigned lane = lane_id();
+  for (int i = threadIdx.x; i < kEntries * kWarp; i += T) s_cnt[i] = 0;
+  __syncthreads();
+  const unsigned lane_base = (unsigned)__cvta_generic_to_shared(s_cnt) + lane * 4u;
+
+  unsigned long long tot_lo = 0, tot_hi = 0;
+  unsigned pending = 0;  // upper bound of any 16-bit half since the last fold
+
+  auto count = [&](UK raw) {
+    const UK k = encode_key(raw, enc);
+    const unsigned lo = (unsigned)k;
+    count_byte<0>(lo, lane_base);
+    if constexpr (sizeof(UK) >= 2) count_byte<1>(lo, lane_base);
+    if constexpr (sizeof(UK) >= 4) {
+      count_byte<2>(lo, lane_base);
+      count_byte<3>(lo, lane_base);
+    }
+    if constexpr (sizeof(UK) == 8) {
+      const unsigned hi = (unsigned)((unsigned long long)k >> 32);
+      count_byte<4>(hi, lane_base);
+      count_byte<5>(hi, lane_base);
+      count_byte<6>(hi, lane_base);
+      count_byte<7>(hi, lane_base);
+    }
+  };
+  auto fold = [&]() {
+    __syncthreads();
+    if ((int)threadIdx.x < kEntries) {
+      unsigned* row = s_cnt + ((unsigned)threadIdx.x << 5);
+      unsigned lo = 0, hi = 0;
+#pragma unroll 8
+      for (unsigned j = 0; j < kWarp; ++j) {
+        const unsigned idx = (j + lane) & 31u;  // rotated: one bank per lane
+        const unsigned w = row[idx];
+        row[idx] = 0;
+        lo += w & 0xffffu;
+        hi += w >> 16;
+      }
+      tot_lo += lo;
+      tot_hi += hi;
+    }
+    __syncthreads();
+    pending = 0;
+  };
+
+  constexpr uint64_t CHUNK = (uint64_t)T * VEC * kHistUnroll;
+  constexpr unsigned kPerChunk = (T / kWarp) * VEC * kHistUnroll;  // adds one lane's counters can see
+  const uint64_t full_chunks = aligned ? n / CHUNK : 0;
+  for (uint64_t c = blockIdx.x; c < full_chunks; c += gridDim.x) {
+    if (pending + kPerChunk > kHalfMax) fold();
+    pending += kPerChunk;
+    const KeyVec<UK>* src = reinterpret_cast<const KeyVec<UK>*>(keys + c * CHUNK);
+    KeyVec<UK> v[kHistUnroll];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u) v[u] = src[u * T + threadIdx.x];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) count(v[u].v[j]);
+  }
+  // remainder (and everything, when the pointer is not 16-byte aligned); every thread of the
+  // CTA makes the same number of trips because fold() synchronises
+  for (uint64_t base = full_chunks * CHUNK + (uint64_t)blockIdx.x * T; base < n; base += (uint64_t)gridDim.x * T) {
+    if (pending + T / kWarp > kHalfMax) fold();
+    pending += T / kWarp;
+    const uint64_t i = base + threadIdx.x;
+    if (i < n) count(keys[i]);
+  }
+  fold();
+
+  if ((int)threadIdx.x < kEntries) {
+    unsigned long long* h = &ctl->hist[0][0] + 2 * threadIdx.x;
+    if (tot_lo) atomicAdd(h, tot_lo);
+    if (tot_hi) atomicAdd(h + 1, tot_hi);
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&ctl->hist_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  finalize_histograms(ctl, P, n, s_warp_tot);
+}
+
 // Finalisation alone, for histograms that another kernel accumulated (the gather of the
 // sharded sort counts the digits of the keys it moves).
 __global__ void __launch_bounds__(kHistThreads)
@@ -743,12 +861,26 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
     trace_mark(stream, kTraceSortHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
   } else {
-    const uint64_t chunk = (uint64_t)kHistThreads * (16 / sizeof(UK)) * kHistUnroll;
-    const uint64_t want = (n + chunk - 1) / chunk;
-    const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
     const int aligned = reinterpret_cast<uintptr_t>(d_keys) % 16 == 0;
-    histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n, begin_bit,
-                                                            end_bit, num_passes, enc, ctl, aligned);
+    if (begin_bit == 0 && end_bit == 8 * (int)sizeof(UK)) {
+      constexpr int kSmem = (int)sizeof(UK) * (kRadix / 2) * kWarp * (int)sizeof(unsigned);
+      const uint64_t chunk = (uint64_t)kByteHistThreads * (16 / sizeof(UK)) * kHistUnroll;
+      const uint64_t want = (n + chunk - 1) / chunk;
+      auto kernel = histogram_bytes_kernel<UK>;
+      TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+      int per_sm = 0;
+      TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kByteHistThreads, kSmem));
+      if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+      const uint64_t resident = (uint64_t)per_sm * sms;
+      const unsigned grid = (unsigned)(want < resident ? (want ? want : 1) : resident);
+      kernel<<<grid, kByteHistThreads, kSmem, stream>>>(static_cast<const UK*>(d_keys), n, enc, ctl, aligned);
+    } else {
+      const uint64_t chunk = (uint64_t)kHistThreads * (16 / sizeof(UK)) * kHistUnroll;
+      const uint64_t want = (n + chunk - 1) / chunk;
+      const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
+      histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n, begin_bit,
+                                                              end_bit, num_passes, enc, ctl, aligned);
+    }
     trace_mark(stream, kTraceSortHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
   }
