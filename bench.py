@@ -169,7 +169,7 @@ def run_reference(args, rank: int):
 def workload_config(n_gpus: int):
     return {
         "workload": f"sharded stable sort_by_key, 2^{PER_GPU_LOG2} (uint64 key, uint32 value=global index) pairs per GPU, "
-                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: regular-sample splitters, stable partition, exchange over NVLink (peer-load gather kernel, or NCCL all-to-all), one local onesweep sort'}",
+                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: regular-sample splitters, stable partition, partition stored straight into the destination GPUs' receive buffers over NVLink (or peer-load gather / NCCL all-to-all), one local onesweep sort'}",
         "pairs_per_gpu": 1 << PER_GPU_LOG2, "total_pairs": n_gpus << PER_GPU_LOG2,
         "l2_policy": "inputs (12 GiB per GPU) larger than L2; input restored by a device copy between steps",
     }
@@ -295,6 +295,8 @@ def main():
     ap.add_argument("--log2-per-gpu", type=int, default=PER_GPU_LOG2, help="for quick checks only")
     ap.add_argument("--no-others", action="store_true", help="skip the side configurations at --gpus 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer", "nccl"],
+                    help="exchange step of the sharded sort at --gpus > 1 (default: push over NVLink)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -322,7 +324,7 @@ def main():
     n = 1 << args.log2_per_gpu
     stream = torch.cuda.current_stream(dev)
 
-    sorter = ss.ShardedSorter(n, dev, world_size=world, rank=rank, seed=SEED)
+    sorter = ss.ShardedSorter(n, dev, world_size=world, rank=rank, seed=SEED, exchange=args.exchange)
     k0, v0 = g.pairs_u64_u32(n, SEED, rank * n, dev)
     k, v = torch.empty_like(k0), torch.empty_like(v0)
 

@@ -77,6 +77,22 @@ int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const 
                     const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
                     tb200_stream_t stream);
 
+/* The two halves of tb200_partition, for callers that place the buckets themselves.
+ * tb200_partition_count writes the bucket sizes to d_counts (it reads the keys once);
+ * tb200_partition_scatter, called once afterwards with the same scratch, keys and splitters,
+ * moves bucket b to h_bucket_keys[b] / h_bucket_vals[b]: HOST arrays of num_splitters + 1
+ * device pointers to each bucket's first element. The buckets may lie in different
+ * allocations, including memory of another GPU mapped into this process (the partition then
+ * stores straight across NVLink: the push form of the sharded sort's exchange, where bucket
+ * b is rank b's share and its pointer is rank b's receive buffer plus what lower ranks send
+ * there). Plain stores only; no counterpart in the reference. */
+int tb200_partition_count(void* d_temp, size_t* temp_bytes, const void* d_keys, uint64_t n, int key_dtype,
+                          int val_bytes, const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
+                          tb200_stream_t stream);
+int tb200_partition_scatter(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, uint64_t n,
+                            int key_dtype, int val_bytes, const void* d_splitters, uint32_t num_splitters,
+                            void* const* h_bucket_keys, void* const* h_bucket_vals, tb200_stream_t stream);
+
 /* ---- segment gather (exchange step of the sharded sort) ---------------------------------
  * Concatenates num_segments (at most 16) source ranges into d_dst, in order: segment s is
  * h_count[s] elements of elem_bytes (4, 8 or 16) starting h_src_offset[s] elements into

@@ -123,3 +123,31 @@ def test_sample_positions_and_splitters():
     s = pick_splitters(torch.arange(4096), 4)
     assert s.tolist() == [1024, 2048, 3072]
     assert pick_splitters(torch.arange(8), 1).numel() == 0
+
+
+def test_push_offsets_keep_source_rank_order():
+    """The push form of the exchange emulated in one process with numpy: every rank scatters its
+    buckets into the destinations' receive buffers at push_offsets; the receive buffers must then
+    hold the runs in source-rank order, which makes the final stable sort the global stable sort."""
+    from thrust_b200.sample_sort import push_offsets
+    rng = np.random.default_rng(5)
+    world, n = 4, 3001
+    shards = [rng.integers(0, 1 << 16, size=n, dtype=np.uint64) for _ in range(world)]
+    splitters = np.array([1 << 14, 1 << 15, 3 << 14], dtype=np.uint64)
+    buckets = [np.searchsorted(splitters, s, side="left") for s in shards]
+    matrix = [[int((b == d).sum()) for d in range(world)] for b in buckets]
+    recv = [np.zeros(sum(matrix[r][d] for r in range(world)), dtype=np.uint64) for d in range(world)]
+    src = [np.zeros(recv[d].size, dtype=np.int64) for d in range(world)]
+    for r in range(world):
+        off = push_offsets(matrix, r)
+        assert off == [sum(matrix[q][d] for q in range(r)) for d in range(world)]
+        for d in range(world):
+            run = shards[r][buckets[r] == d]
+            recv[d][off[d]:off[d] + run.size] = run
+            src[d][off[d]:off[d] + run.size] = r
+    whole = np.concatenate(shards)
+    order = np.argsort(whole, kind="stable")
+    got = np.concatenate([np.sort(recv[d], kind="stable") for d in range(world)])
+    assert got.tobytes() == whole[order].tobytes()
+    for d in range(world):
+        assert (np.diff(src[d]) >= 0).all()  # runs of rank 0, then rank 1, ...

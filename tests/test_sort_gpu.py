@@ -235,6 +235,54 @@ def test_partition_by_splitters_is_stable(cuda_device, kdtype, vdtype):
             assert to_host(ov, vdtype).tobytes() == v[order].tobytes(), (n, ns)
 
 
+@pytest.mark.parametrize("kdtype,vdtype", [(np.uint64, np.uint32), (np.uint32, None)])
+def test_partition_count_then_scatter_into_separate_buffers(cuda_device, kdtype, vdtype):
+    """tb200_partition_count + tb200_partition_scatter: every bucket goes to its own allocation,
+    at an odd element offset, and holds its keys in input order (the push form of the exchange)."""
+    import ctypes as C
+    rng = np.random.default_rng(9001)
+    kcode = capi.U64 if kdtype == np.uint64 else capi.U32
+    ktorch = torch.int64 if kdtype == np.uint64 else torch.int32
+    for n, ns in [(0, 3), (1, 1), (6144, 0), (100003, 7), (250007, 3), (70001, 15)]:
+        k = random_keys(rng, n, kdtype, bits=24)
+        sp = np.sort(random_keys(rng, ns, kdtype, bits=24))
+        v = None if vdtype is None else rng.integers(0, 1 << 31, size=n).astype(vdtype)
+        dk = to_device(k)
+        dsp = to_device(sp) if ns else torch.empty(0, dtype=ktorch, device="cuda:0")
+        dv = to_device(v) if v is not None else None
+        counts = torch.zeros(ns + 1, dtype=torch.int64, device="cuda:0")
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        vb = 0 if v is None else v.dtype.itemsize
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_partition_count(None, C.byref(need), None, n, kcode, vb, None, ns, None, stream), "size")
+        temp = torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda:0")
+        capi.check(capi.lib.tb200_partition_count(
+            C.c_void_p(temp.data_ptr()), C.byref(need), C.c_void_p(dk.data_ptr()), n, kcode, vb,
+            C.c_void_p(dsp.data_ptr()) if ns else None, ns, C.c_void_p(counts.data_ptr()), stream), "count")
+        bucket = np.searchsorted(sp, k, side="left")
+        want_counts = np.bincount(bucket, minlength=ns + 1).tolist()
+        got = counts.cpu().numpy().tolist()
+        assert got == want_counts, (n, ns)
+        pad = 3  # buckets start three elements into their buffers
+        out_k = [torch.full((c + pad + 1,), -1, dtype=ktorch, device="cuda:0") for c in got]
+        out_v = [torch.full((c + pad + 1,), -1, dtype=torch.int32, device="cuda:0") for c in got]
+        pk = (C.c_void_p * (ns + 1))(*[t.data_ptr() + pad * t.element_size() for t in out_k])
+        pv = (C.c_void_p * (ns + 1))(*[t.data_ptr() + pad * 4 for t in out_v])
+        capi.check(capi.lib.tb200_partition_scatter(
+            C.c_void_p(temp.data_ptr()), C.byref(need), C.c_void_p(dk.data_ptr()),
+            C.c_void_p(dv.data_ptr()) if dv is not None else None, n, kcode, vb,
+            C.c_void_p(dsp.data_ptr()) if ns else None, ns, pk, pv if vb else None, stream), "scatter")
+        capi.check(capi.lib.tb200_temp_status(C.c_void_p(temp.data_ptr()), stream), "status")
+        for b in range(ns + 1):
+            sel = bucket == b
+            hk = to_host(out_k[b], kdtype)
+            assert hk[pad:pad + got[b]].tobytes() == k[sel].tobytes(), (n, ns, b)
+            assert (hk[:pad] == np.iinfo(kdtype).max).all() and hk[-1] == np.iinfo(kdtype).max, (n, ns, b)
+            if v is not None:
+                hv = to_host(out_v[b], vdtype)
+                assert hv[pad:pad + got[b]].tobytes() == v[sel].tobytes(), (n, ns, b)
+
+
 @pytest.mark.parametrize("dtype", [np.uint64, np.uint32])
 def test_gather_segments_concatenates_ranges(cuda_device, dtype):
     """tb200_gather_segments on local pointers: odd offsets and lengths, empty segments."""

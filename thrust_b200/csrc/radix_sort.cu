@@ -339,6 +339,11 @@ struct PassParams {
   void* desc;
   const void* splitters;   // partition mode: ascending splitters (device), else unused
   unsigned num_splitters;
+  // partition mode: device tables of num_splitters + 1 pointers, the first element of every
+  // bucket's output (keys, values); the buckets may live in different allocations, another
+  // GPU's memory included. Null: bucket b starts at element offs[0][b] of the alternate arrays.
+  void* const* bucket_keys;
+  void* const* bucket_vals;
 };
 
 template <typename DescT> struct DescBits;
@@ -464,6 +469,8 @@ onesweep_kernel(const PassParams prm) {
   __shared__ unsigned s_scan[kRadix / kWarp];
   __shared__ unsigned s_next;
   __shared__ UK s_split[SPLIT ? kRadix : 1];
+  __shared__ UK* s_bucket_keys[SPLIT ? kRadix : 1];
+  __shared__ V* s_bucket_vals[SPLIT ? kRadix : 1];
 
   SortCtl* ctl = prm.ctl;
   const int pass = prm.pass;
@@ -538,7 +545,21 @@ onesweep_kernel(const PassParams prm) {
   };
 
   // global offset of this thread's digit in this pass: read once, used for every tile
-  const unsigned long long pass_offset = ctl->offs[pass][threadIdx.x % kRadix];
+  unsigned long long pass_offset = ctl->offs[pass][threadIdx.x % kRadix];
+  if constexpr (SPLIT) {  // buckets are addressed through their own base pointers
+    if (threadIdx.x < kRadix) {
+      const unsigned b = threadIdx.x;
+      UK* bk = dst_keys + pass_offset;
+      V* bv = VB ? dst_vals + pass_offset : nullptr;
+      if (prm.bucket_keys != nullptr && b <= num_split) {
+        bk = static_cast<UK*>(prm.bucket_keys[b]);
+        if (VB) bv = static_cast<V*>(prm.bucket_vals[b]);
+      }
+      s_bucket_keys[b] = bk;
+      s_bucket_vals[b] = bv;
+    }
+    pass_offset = 0;
+  }
   if (threadIdx.x == 0) s_next = atomicAdd(&ctl->tickets[pass], 1u);
   __syncthreads();
   unsigned tile = s_next;
@@ -607,9 +628,16 @@ onesweep_kernel(const PassParams prm) {
       // ---- scatter: every digit leaves as one contiguous run
       auto emit = [&](unsigned pos) {
         const UK k = s_keys[pos];
-        const IdxT g = s_gbase[digit(k)] + pos;
-        dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
-        if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
+        if constexpr (SPLIT) {
+          const unsigned b = digit(k);
+          const IdxT g = s_gbase[b] + pos;  // index inside bucket b (the sum never wraps)
+          s_bucket_keys[b][g] = k;
+          if constexpr (VB != 0) s_bucket_vals[b][g] = s_vals[pos];
+        } else {
+          const IdxT g = s_gbase[digit(k)] + pos;
+          dst_keys[g] = last_exec ? decode_key(k, prm.enc) : k;
+          if constexpr (VB != 0) dst_vals[g] = s_vals[pos];
+        }
       };
       if (p_valid == (unsigned)TILE) {
   #pragma unroll
@@ -897,6 +925,8 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.desc = base + lay.desc_off;
   prm.splitters = nullptr;
   prm.num_splitters = 0;
+  prm.bucket_keys = nullptr;
+  prm.bucket_vals = nullptr;
   auto launch = [&](auto kernel) -> int {
     TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
     int per_sm = 0;
@@ -940,11 +970,38 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
   for (int i = threadIdx.x; i < kRadix; i += kHistThreads) s_hist[i] = 0;
   for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) s_split[i] = splitters[i];
   __syncthreads();
-  for (uint64_t i = (uint64_t)blockIdx.x * kHistThreads + threadIdx.x; i < n; i += (uint64_t)gridDim.x * kHistThreads) {
-    const UK k = keys[i];
-    unsigned b = 0;
-    for (unsigned j = 0; j < num_split; ++j) b += s_split[j] < k;
-    atomicAdd(&s_hist[b], 1u);
+  // Whole warps walk the keys together: equal buckets inside a warp are found with one ballot
+  // per bucket-id bit and counted by one lane, so a handful of buckets does not serialise the
+  // shared-memory atomics.
+  const int split_bits = 32 - __clz(num_split | 1u);
+  const unsigned lt_mask = lanemask_lt();
+  auto count = [&](UK k, bool valid) {
+    unsigned lo = 0, hi = num_split;  // number of splitters strictly below k
+    while (lo < hi) {
+      const unsigned mid = (lo + hi) >> 1;
+      if (s_split[mid] < k) lo = mid + 1; else hi = mid;
+    }
+    unsigned peers = match_digit_bits(lo, split_bits) & __ballot_sync(0xffffffffu, valid);
+    if (valid && (peers & lt_mask) == 0) atomicAdd(&s_hist[lo], (unsigned)__popc(peers));
+  };
+  constexpr int VEC = 16 / sizeof(UK);
+  constexpr uint64_t CHUNK = (uint64_t)kHistThreads * VEC * kHistUnroll;
+  const uint64_t full_chunks = reinterpret_cast<uintptr_t>(keys) % 16 == 0 ? n / CHUNK : 0;
+  for (uint64_t c = blockIdx.x; c < full_chunks; c += gridDim.x) {
+    const KeyVec<UK>* src = reinterpret_cast<const KeyVec<UK>*>(keys + c * CHUNK);
+    KeyVec<UK> v[kHistUnroll];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u) v[u] = src[u * kHistThreads + threadIdx.x];
+#pragma unroll
+    for (int u = 0; u < kHistUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) count(v[u].v[j], true);
+  }
+  for (uint64_t base = full_chunks * CHUNK + (uint64_t)blockIdx.x * kHistThreads; base < n;
+       base += (uint64_t)gridDim.x * kHistThreads) {
+    const uint64_t i = base + threadIdx.x;
+    const bool valid = i < n;
+    count(valid ? keys[i] : UK(0), valid);
   }
   __syncthreads();
   for (int i = threadIdx.x; i <= (int)num_split; i += kHistThreads)
@@ -979,10 +1036,15 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
   }
 }
 
+// phase kPhaseAll: count and scatter into d_keys_out / d_vals_out; kPhaseBegin: count only (the
+// bucket sizes reach d_counts); kPhaseFinish: scatter only, bucket b to h_bucket_keys[b] /
+// h_bucket_vals[b] (host arrays of num_splitters + 1 device pointers) after a kPhaseBegin call
+// on the same scratch and input.
 template <typename UK, int VB>
 int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, void* d_keys_out,
                    void* d_vals_out, uint64_t n, const void* d_splitters, unsigned num_splitters,
-                   uint64_t* d_counts, cudaStream_t stream) {
+                   uint64_t* d_counts, cudaStream_t stream, int phase = kPhaseAll,
+                   void* const* h_bucket_keys = nullptr, void* const* h_bucket_vals = nullptr) {
   using T = Tuning<UK, VB>;
   using Shape = PassShape<UK, VB, T::kThreads, T::kItems>;
   constexpr uint64_t TILE = Shape::kTile;
@@ -996,25 +1058,49 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   if (*temp_bytes < lay.total) return TB200_ERR_TEMP_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(d_temp) % 256) return TB200_ERR_INVALID_ARGUMENT;
   if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
-  if (!d_counts || (num_splitters && !d_splitters)) return TB200_ERR_INVALID_ARGUMENT;
+  if ((phase != kPhaseFinish && !d_counts) || (num_splitters && !d_splitters)) return TB200_ERR_INVALID_ARGUMENT;
+  if (phase == kPhaseFinish && (!h_bucket_keys || (VB && !h_bucket_vals))) return TB200_ERR_INVALID_ARGUMENT;
   char* base = static_cast<char*>(d_temp);
   auto* ctl = reinterpret_cast<SortCtl*>(base + lay.ctl_off);
-  TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
-  if (n == 0) {
-    TB200_CUDA_TRY(cudaMemsetAsync(d_counts, 0, (num_splitters + 1) * sizeof(uint64_t), stream));
-    return TB200_OK;
+  if (phase != kPhaseFinish) {
+    TB200_CUDA_TRY(cudaMemsetAsync(d_temp, 0, lay.clear_bytes, stream));
+    if (n == 0) {
+      TB200_CUDA_TRY(cudaMemsetAsync(d_counts, 0, (num_splitters + 1) * sizeof(uint64_t), stream));
+      return TB200_OK;
+    }
   }
-  if (!d_keys || !d_keys_out || (VB && (!d_vals || !d_vals_out))) return TB200_ERR_INVALID_ARGUMENT;
+  if (n == 0) return TB200_OK;
+  if (!d_keys) return TB200_ERR_INVALID_ARGUMENT;
+  if (phase != kPhaseBegin && VB && !d_vals) return TB200_ERR_INVALID_ARGUMENT;
+  if (phase == kPhaseAll && (!d_keys_out || (VB && !d_vals_out))) return TB200_ERR_INVALID_ARGUMENT;
   int dev = 0, sms = 0;
   TB200_CUDA_TRY(cudaGetDevice(&dev));
   TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  {
+  if (phase != kPhaseFinish) {
     const uint64_t want = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
     const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
     bucket_histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n,
                                                                    static_cast<const UK*>(d_splitters), num_splitters, ctl);
     trace_mark(stream, kTracePartitionHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
+    TB200_CUDA_TRY(cudaMemcpyAsync(d_counts, &ctl->hist[0][0], (num_splitters + 1) * sizeof(uint64_t),
+                                   cudaMemcpyDeviceToDevice, stream));
+    if (phase == kPhaseBegin) return TB200_OK;
+  }
+  // the bucket pointer tables travel in two rows of the control block that a one-pass
+  // partition never touches
+  void* const* d_bucket_keys = nullptr;
+  void* const* d_bucket_vals = nullptr;
+  if (phase == kPhaseFinish) {
+    static_assert(sizeof(void*) == sizeof(unsigned long long), "pointer tables reuse 64-bit rows");
+    TB200_CUDA_TRY(cudaMemcpyAsync(&ctl->offs[1][0], h_bucket_keys, (num_splitters + 1) * sizeof(void*),
+                                   cudaMemcpyHostToDevice, stream));
+    d_bucket_keys = reinterpret_cast<void* const*>(&ctl->offs[1][0]);
+    if (VB) {
+      TB200_CUDA_TRY(cudaMemcpyAsync(&ctl->offs[2][0], h_bucket_vals, (num_splitters + 1) * sizeof(void*),
+                                     cudaMemcpyHostToDevice, stream));
+      d_bucket_vals = reinterpret_cast<void* const*>(&ctl->offs[2][0]);
+    }
   }
   PassParams prm;
   prm.keys_main = const_cast<void*>(d_keys);
@@ -1031,6 +1117,8 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   prm.mask = num_splitters;
   prm.splitters = d_splitters;
   prm.num_splitters = num_splitters;
+  prm.bucket_keys = d_bucket_keys;
+  prm.bucket_vals = d_bucket_vals;
   auto launch = [&](auto kernel) -> int {
     TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
     int per_sm = 0;
@@ -1044,9 +1132,7 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   };
   const int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true>)
                       : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true>);
-  if (rc) return rc;
-  return (int)cudaMemcpyAsync(d_counts, &ctl->hist[0][0], (num_splitters + 1) * sizeof(uint64_t),
-                              cudaMemcpyDeviceToDevice, stream);
+  return rc;
 }
 
 template <typename UK>
@@ -1109,6 +1195,46 @@ extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_k
   }
 #undef TB200_PART
   return TB200_ERR_UNSUPPORTED;
+}
+
+namespace tb200 {
+namespace {
+int partition_phase(int phase, void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, uint64_t n,
+                    int key_dtype, int val_bytes, const void* d_splitters, uint32_t num_splitters,
+                    uint64_t* d_counts, void* const* h_bucket_keys, void* const* h_bucket_vals, cudaStream_t stream) {
+  if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  if (num_splitters > 255) return TB200_ERR_INVALID_ARGUMENT;
+#define TB200_PART(UK, VB) \
+  return partition_impl<UK, VB>(d_temp, temp_bytes, d_keys, d_vals, nullptr, nullptr, n, d_splitters, num_splitters, \
+                                d_counts, stream, phase, h_bucket_keys, h_bucket_vals)
+  if (key_dtype == TB200_U64) {
+    if (val_bytes == 0) TB200_PART(unsigned long long, 0);
+    if (val_bytes == 4) TB200_PART(unsigned long long, 4);
+    if (val_bytes == 8) TB200_PART(unsigned long long, 8);
+  } else if (key_dtype == TB200_U32) {
+    if (val_bytes == 0) TB200_PART(uint32_t, 0);
+    if (val_bytes == 4) TB200_PART(uint32_t, 4);
+    if (val_bytes == 8) TB200_PART(uint32_t, 8);
+  }
+#undef TB200_PART
+  return TB200_ERR_UNSUPPORTED;
+}
+}  // namespace
+}  // namespace tb200
+
+extern "C" int tb200_partition_count(void* d_temp, size_t* temp_bytes, const void* d_keys, uint64_t n, int key_dtype,
+                                     int val_bytes, const void* d_splitters, uint32_t num_splitters,
+                                     uint64_t* d_counts, tb200_stream_t stream) {
+  return tb200::partition_phase(tb200::kPhaseBegin, d_temp, temp_bytes, d_keys, nullptr, n, key_dtype, val_bytes,
+                                d_splitters, num_splitters, d_counts, nullptr, nullptr, stream);
+}
+
+extern "C" int tb200_partition_scatter(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                                       uint64_t n, int key_dtype, int val_bytes, const void* d_splitters,
+                                       uint32_t num_splitters, void* const* h_bucket_keys,
+                                       void* const* h_bucket_vals, tb200_stream_t stream) {
+  return tb200::partition_phase(tb200::kPhaseFinish, d_temp, temp_bytes, d_keys, d_vals, n, key_dtype, val_bytes,
+                                d_splitters, num_splitters, nullptr, h_bucket_keys, h_bucket_vals, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -93,6 +93,32 @@ class DeviceOps:
                                             C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
         return counts
 
+    def partition_count(self, keys: torch.Tensor, n: int, splitters: torch.Tensor) -> torch.Tensor:
+        """Bucket sizes of the stable partition by ``splitters`` (int64 tensor); first half of a push."""
+        capi = self.capi
+        counts = torch.empty(splitters.numel() + 1, dtype=torch.int64, device=self.device)
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_partition_count(C.c_void_p(self.temp.data_ptr()), C.byref(have),
+                                                  C.c_void_p(keys.data_ptr()), n, capi.U64, 4,
+                                                  C.c_void_p(splitters.data_ptr()), splitters.numel(),
+                                                  C.c_void_p(counts.data_ptr()), self._stream()),
+                   "tb200_partition_count")
+        return counts
+
+    def partition_scatter(self, keys: torch.Tensor, vals: torch.Tensor, n: int, splitters: torch.Tensor,
+                          bucket_keys, bucket_vals) -> None:
+        """Second half: bucket b goes to the device addresses bucket_keys[b] / bucket_vals[b]
+        (integers; peer mappings allowed)."""
+        capi = self.capi
+        g = splitters.numel() + 1
+        pk = (C.c_void_p * g)(*bucket_keys)
+        pv = (C.c_void_p * g)(*bucket_vals)
+        have = C.c_size_t(self.temp.numel())
+        capi.check(capi.lib.tb200_partition_scatter(C.c_void_p(self.temp.data_ptr()), C.byref(have),
+                                                    C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), n,
+                                                    capi.U64, 4, C.c_void_p(splitters.data_ptr()), splitters.numel(),
+                                                    pk, pv, self._stream()), "tb200_partition_scatter")
+
     def sort_begin(self, n: int) -> None:
         """First half of sort_pairs: clears the scratch; the key gather then counts the digits."""
         capi = self.capi
@@ -144,19 +170,30 @@ def pick_splitters(sorted_samples: torch.Tensor, world: int) -> torch.Tensor:
     return sorted_samples[pos.to(sorted_samples.device)]
 
 
+def push_offsets(matrix, rank: int):
+    """matrix[r][b] = pairs rank r sends to rank b. Returns, for every destination b, the element
+    offset inside b's receive buffer where THIS rank's bucket starts: the buckets of lower source
+    ranks come first, which keeps the received runs in source-rank order."""
+    world = len(matrix)
+    return [int(sum(matrix[r][b] for r in range(rank))) for b in range(world)]
+
+
 class ShardedSorter:
     """Sorts one shard per rank; after ``sort`` rank r holds the r-th slice of the global order."""
 
     def __init__(self, n: int, device: torch.device, world_size: int = 1, rank: int = 0, seed: int = 0,
                  ops=None, group=None, slack: Optional[float] = None, pipeline: str = "partition_first",
                  exchange: str = "auto"):
-        """exchange: "peer" — every GPU pulls its runs out of the other GPUs' partition buffers with
-        one kernel of peer loads over NVLink (buffers in torch symmetric memory, no multicast);
-        "nccl" — all-to-all-v through torch.distributed; "auto" — "peer" on CUDA with the
-        partition_first pipeline when the symmetric-memory rendezvous succeeds, else "nccl"."""
+        """exchange: "push" — the partition kernel stores every bucket straight into its
+        destination GPU's receive buffer over NVLink (receive buffers in torch symmetric memory,
+        plain peer stores, no multicast), so partition and exchange are one pass over the shard;
+        "peer" — partition locally, then every GPU pulls its runs out of the other GPUs' partition
+        buffers with one kernel of peer loads; "nccl" — all-to-all-v through torch.distributed;
+        "auto" — "push" on CUDA with the partition_first pipeline when the symmetric-memory
+        rendezvous succeeds, else "nccl"."""
         if pipeline not in ("partition_first", "sort_first"):
             raise ValueError(pipeline)
-        if exchange not in ("auto", "peer", "nccl"):
+        if exchange not in ("auto", "push", "peer", "nccl"):
             raise ValueError(exchange)
         self.n, self.device, self.world, self.rank, self.seed = n, device, world_size, rank, seed
         self.group = group
@@ -175,41 +212,48 @@ class ShardedSorter:
         self.recv_k = self.recv_v = self.part_k = self.part_v = None
         self.exchange = "none"
         if world_size > 1:
-            self.recv_k = torch.empty(self.capacity, dtype=torch.int64, device=device)
-            self.recv_v = torch.empty(self.capacity, dtype=torch.int32, device=device)
             self.exchange = "nccl"
             self.peer_k = self.peer_v = None
             if pipeline == "partition_first":
-                want_peer = exchange == "peer" or (exchange == "auto" and device.type == "cuda")
-                if want_peer:
+                want = exchange if exchange in ("push", "peer") else ("push" if exchange == "auto" and device.type == "cuda" else None)
+                if want is not None:
                     try:
-                        self._alloc_symmetric(n)
-                        self.exchange = "peer"
+                        self._alloc_symmetric(n, want)
+                        self.exchange = want
                     except Exception as e:  # symmetric memory unavailable: use the collective
-                        if exchange == "peer":
+                        if exchange in ("push", "peer"):
                             raise
                         self.exchange_fallback_reason = repr(e)
                 if self.exchange == "nccl":
                     self.part_k = torch.empty(n, dtype=torch.int64, device=device)
                     self.part_v = torch.empty(n, dtype=torch.int32, device=device)
+            if self.recv_k is None:
+                self.recv_k = torch.empty(self.capacity, dtype=torch.int64, device=device)
+                self.recv_v = torch.empty(self.capacity, dtype=torch.int32, device=device)
         self.last_counts = None
         self._marks = []
 
-    def _alloc_symmetric(self, n: int) -> None:
-        """Partition buffers in symmetric memory; peer pointers of every rank's buffers."""
+    def _alloc_symmetric(self, n: int, mode: str) -> None:
+        """Buffers the peers touch, in symmetric memory, and every rank's pointers to them:
+        the partition buffers for "peer" (pulled from), the receive buffers for "push"."""
         import os
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads and stores only
         import torch.distributed._symmetric_memory as symm
         grp = self.group if self.group is not None else dist.group.WORLD
-        self.part_k = symm.empty(n, dtype=torch.int64, device=self.device)
-        self.part_v = symm.empty(n, dtype=torch.int32, device=self.device)
-        hk = symm.rendezvous(self.part_k, grp)
-        hv = symm.rendezvous(self.part_v, grp)
+        size = n if mode == "peer" else self.capacity
+        buf_k = symm.empty(size, dtype=torch.int64, device=self.device)
+        buf_v = symm.empty(size, dtype=torch.int32, device=self.device)
+        hk = symm.rendezvous(buf_k, grp)
+        hv = symm.rendezvous(buf_v, grp)
         self.peer_k = [int(p) for p in hk.buffer_ptrs]
         self.peer_v = [int(p) for p in hv.buffer_ptrs]
         self._symm_handles = (hk, hv)
         if len(self.peer_k) != self.world:
             raise RuntimeError("symmetric memory rendezvous returned the wrong number of peers")
+        if mode == "peer":
+            self.part_k, self.part_v = buf_k, buf_v
+        else:
+            self.recv_k, self.recv_v = buf_k, buf_v
 
     def _mark(self, name: str) -> None:
         """Records a CUDA event at a phase boundary (device tensors only)."""
@@ -261,10 +305,13 @@ class ShardedSorter:
             head = self.ops.segment_counts(keys, n, splitters)
             send = torch.cat([head, (n - head.sum()).reshape(1)])
             src_k, src_v = keys, vals
+        elif self.exchange == "push":
+            send = self.ops.partition_count(keys, n, splitters)
+            src_k = src_v = None
         else:
             send = self.ops.partition(keys, vals, n, splitters, self.part_k, self.part_v)
             src_k, src_v = self.part_k, self.part_v
-        self._mark("segments" if sort_first else "partition")
+        self._mark("segments" if sort_first else ("bucket_counts" if self.exchange == "push" else "partition"))
         # 5. the whole G x G count matrix goes to every rank (row r = what rank r sends), so all
         # ranks take the same decision about receive overflow; then the payload
         matrix = torch.empty(G * G, dtype=torch.int64, device=self.device)
@@ -278,6 +325,20 @@ class ShardedSorter:
         if worst > self.capacity:
             raise OverflowError(f"{worst} incoming pairs on one rank exceed the receive capacity {self.capacity}")
         self._mark("count_matrix")
+        if self.exchange == "push" and not sort_first:
+            # Push: my bucket for rank b lands in b's receive buffer behind the buckets of lower
+            # source ranks. The count matrix arrived through a collective that every rank entered
+            # after the previous step's work on its stream, so the receive buffers are free.
+            off = push_offsets(mat.tolist(), self.rank)
+            self.ops.partition_scatter(keys, vals, n, splitters,
+                                       [self.peer_k[b] + 8 * off[b] for b in range(G)],
+                                       [self.peer_v[b] + 4 * off[b] for b in range(G)])
+            # every rank's stores have landed once every rank's partition kernel has finished
+            dist.barrier(group=self.group)
+            self._mark("partition_and_exchange")
+            self.ops.sort_pairs(self.recv_k, self.recv_v, m)
+            self._mark("final_sort")
+            return self.recv_k, self.recv_v, m
         if self.exchange == "peer" and not sort_first:
             # Pull: rank r's bucket for me starts where the buckets of lower destinations end.
             # The count matrix arrived through a collective that every rank entered after its
