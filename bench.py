@@ -169,7 +169,7 @@ def run_reference(args, rank: int):
 def workload_config(n_gpus: int):
     return {
         "workload": f"sharded stable sort_by_key, 2^{PER_GPU_LOG2} (uint64 key, uint32 value=global index) pairs per GPU, "
-                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: regular-sample splitters, stable partition, partition stored straight into the destination GPUs' receive buffers over NVLink (or peer-load gather / NCCL all-to-all), one local onesweep sort'}",
+                    f"seed {SEED}, {'local onesweep radix sort' if n_gpus == 1 else 'sample sort: regular-sample splitters, stable partition, partition pass storing straight into the receive buffers of the destination GPUs over NVLink (or peer-load gather / NCCL all-to-all), one local onesweep sort'}",
         "pairs_per_gpu": 1 << PER_GPU_LOG2, "total_pairs": n_gpus << PER_GPU_LOG2,
         "l2_policy": "inputs (12 GiB per GPU) larger than L2; input restored by a device copy between steps",
     }

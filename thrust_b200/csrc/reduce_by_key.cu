@@ -269,7 +269,7 @@ reduce_by_key_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* 
 
 // ---------------------------------------------------------------------------------------
 // Streaming variant (16-byte aligned inputs): the structure of the streaming scan kernel.
-// Persistent CTAs, one per SM, 16 compute warps + two look-back warps; a ring of four slots,
+// Persistent CTAs, one per SM, 16 compute warps + one look-back warp; a ring of four slots,
 // each holding one tile of keys and one of values, filled by bulk asynchronous copies.
 // Thread t owns 3*E consecutive elements of the tile (48 bytes of the wider type: a
 // bank-conflict-free stride), so head flags need one shuffle and the tile-local
@@ -366,8 +366,8 @@ rbk_stream_kernel(const K* __restrict__ keys, const V* __restrict__ vals, K* __r
   __syncthreads();
 
   // ------------------------------------------------------------------ look-back warps
-  // One look-back takes longer than the compute warps need for a tile, so two warps take
-  // turns; each resolves its tiles independently of the other.
+  // kRsLookWarps warps take turns, each resolving its tiles independently of the others. One
+  // warp measured fastest: a second poller slows the chain it waits on more than it overlaps.
   if (warp >= kRsWarps) {
     for (unsigned j = warp - kRsWarps;; j += kRsLookWarps) {
       const int slot = j % S;
