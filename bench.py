@@ -231,6 +231,15 @@ def bench_others(dev, peak):
     temp = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
     entry("inclusive_scan_f32_2^30", lambda: tb.inclusive_scan(x, out=y, sync=False, temp=temp), lambda: None,
           n, "Gelem/s", 8.0 * n, "1 read + 1 write x 4 B = 8 B/element")
+    # next row of the path: thrust::reduce over the same 2^30 floats (one read)
+    red_out = torch.empty(16, dtype=torch.uint8, device=dev)
+    red_have = C.c_size_t(temp.numel())
+    red_stream = C.c_void_p(stream.cuda_stream)
+
+    def red():
+        capi.check(capi.lib.tb200_reduce(C.c_void_p(temp.data_ptr()), C.byref(red_have), C.c_void_p(x.data_ptr()), n,
+                                         capi.F32, None, C.c_void_p(red_out.data_ptr()), red_stream), "tb200_reduce")
+    entry("reduce_f32_2^30", red, lambda: None, n, "Gelem/s", 4.0 * n, "1 read x 4 B = 4 B/element")
     del x, y
     x = g.scan_i64(n, dev)
     y = torch.empty_like(x)

@@ -159,6 +159,17 @@ int tb200_reduce_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys_in,
                         uint64_t* d_num_runs, uint64_t n, int key_dtype, int val_dtype,
                         tb200_stream_t stream);
 
+/* ---- reduce ---------------------------------------------------------------------------
+ * *d_out = init + in[0] + ... + in[n-1] with thrust::plus in the element type (integer sums
+ * wrap; dtype: any integer or floating-point code, not BOOL). h_init is a HOST pointer to
+ * one element, NULL = 0; d_out is a device pointer to one element; n = 0 gives init. The
+ * sum is reproducible from run to run on one device; for floating point it differs from the
+ * left-to-right order of the reference's CPU systems (sequential/reduce.h:43-62) by rounding
+ * only. Replaces thrust::cuda_cub::detail::reduce_n_impl and its cub::DeviceReduce::Reduce
+ * (thrust/system/cuda/detail/reduce.h:930-1000, entry points reduce.h:1029-1062). */
+int tb200_reduce(void* d_temp, size_t* temp_bytes, const void* d_in, uint64_t n, int dtype, const void* h_init,
+                 void* d_out, tb200_stream_t stream);
+
 /* ---- sort-based histogram -----------------------------------------------------------
  * Second half of the dense-histogram recipe (examples/histogram.cu:84-97): given SORTED
  * data (dtype in {I32,U32,I64,U64,F32,F64}) and num_bins ascending bin values of the same
@@ -189,7 +200,8 @@ int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream);
  * synchronises, writes the device time of launch i (milliseconds) to ms[i] and what it was
  * to kinds[i] (may be NULL) for i < capacity and returns the number of launches (negative:
  * -cudaError_t). kinds: 1 sort histogram, 2 radix pass, 3 sort copy-back, 4 scan,
- * 5 reduce_by_key, 6 histogram of sorted data, 7 partition histogram, 8 partition pass. */
+ * 5 reduce_by_key, 6 histogram of sorted data, 7 partition histogram, 8 partition pass,
+ * 9 reduce. */
 int tb200_trace_begin(tb200_stream_t stream);
 int tb200_trace_end(float* ms, int* kinds, int capacity);
 

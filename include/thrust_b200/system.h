@@ -1,6 +1,6 @@
 // thrust_b200::system — a Thrust custom system (in the style of the reference's
 // examples/minimal_custom_backend.cu:17-37) that routes sort / stable_sort /
-// sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / reduce_by_key
+// sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / reduce / reduce_by_key
 // on contiguous arithmetic data to the sm_100a kernels behind the C ABI of
 // thrust_b200.h, and everything else to the CUDA system it derives from.
 //
@@ -268,6 +268,51 @@ OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result, Init init) 
 template <typename InIt, typename OutIt>
 OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result) {
   return exclusive_scan(s, first, last, result, detail::value_t<InIt>{});  // scan.h:340-349
+}
+
+// ---- reduce (cuda/detail/reduce.h:1029-1062) ---------------------------------------------
+// The accumulator and the result have the type of `init`; the fast path needs it to be the
+// input's value type and the operator to be thrust::plus. Like the reference the call
+// synchronises to read the result (reduce.h:984-1000), whatever the policy says.
+namespace detail {
+template <typename T> struct is_reduce_type
+    : std::integral_constant<bool, is_plain_arithmetic<T>::value && !std::is_same<T, bool>::value> {};
+template <typename InIt, typename T, typename Op>
+constexpr bool reduce_fast_v = contiguous_v<InIt> && is_reduce_type<T>::value &&
+                               std::is_same<value_t<InIt>, T>::value && is_plus<Op, T>::value;
+template <typename InIt, typename T>
+T reduce_fast(system& s, InIt first, InIt last, T init) {
+  const uint64_t n = (uint64_t)(last - first);
+  size_t bytes = 0;
+  throw_on_error(tb200_reduce(nullptr, &bytes, nullptr, n, dtype_of<T>(), nullptr, nullptr, s.stream), "tb200_reduce");
+  // the result lives in the first 256 bytes of the workspace, the library's scratch behind it
+  char* ws = static_cast<char*>(workspace(bytes + 256, s.stream));
+  throw_on_error(tb200_reduce(ws + 256, &bytes, n ? (const void*)raw(first) : nullptr, n, dtype_of<T>(), &init, ws,
+                              s.stream), "tb200_reduce");
+  ++fast_calls();
+  T result;
+  throw_on_error((int)cudaMemcpyAsync(&result, ws, sizeof(T), cudaMemcpyDeviceToHost, s.stream), "tb200_reduce");
+  throw_on_error((int)cudaStreamSynchronize(s.stream), "tb200_reduce");
+  return result;
+}
+}  // namespace detail
+
+template <typename InIt, typename T, typename Op>
+T reduce(system& s, InIt first, InIt last, T init, Op op) {
+  if constexpr (detail::reduce_fast_v<InIt, T, Op>) {
+    return detail::reduce_fast<InIt, T>(s, first, last, init);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::reduce(detail::inherited(s), first, last, init, op);
+  }
+}
+template <typename InIt, typename T>
+T reduce(system& s, InIt first, InIt last, T init) {
+  return reduce(s, first, last, init, thrust::plus<T>());  // reduce.h:1045-1051
+}
+template <typename InIt>
+detail::value_t<InIt> reduce(system& s, InIt first, InIt last) {
+  return reduce(s, first, last, detail::value_t<InIt>(0));  // reduce.h:1057-1063
 }
 
 // ---- reduce_by_key (cuda/detail/reduce_by_key.h:1118-1200) --------------------------------

@@ -57,6 +57,8 @@ class CpuChecker:
         self._scan.argtypes, self._scan.restype = [vp, vp, u64, i32, i32, vp], i32
         self._rbk = getattr(self._lib, prefix + "reduce_by_key")
         self._rbk.argtypes, self._rbk.restype = [vp, vp, vp, vp, u64, i32, i32], C.c_int64
+        self._reduce = getattr(self._lib, prefix + "reduce")
+        self._reduce.argtypes, self._reduce.restype = [vp, u64, i32, vp, vp], i32
         self._hist = getattr(self._lib, prefix + "histogram")
         self._hist.argtypes, self._hist.restype = [vp, u64, i32, vp, u32, vp], i32
         self.threads = 1
@@ -98,6 +100,15 @@ class CpuChecker:
         rc = self._scan(self._p(a), self._p(out), a.size, dt_of(a), int(exclusive), self._p(ini))
         assert rc == 0, rc
         return out
+
+    def reduce(self, a: np.ndarray, init=None):
+        """init + sum of ``a`` in a's type (a numpy scalar of that type)."""
+        a = np.ascontiguousarray(a)
+        out = np.zeros(1, dtype=a.dtype)
+        ini = None if init is None else np.array([init], dtype=a.dtype)
+        rc = self._reduce(self._p(a), a.size, dt_of(a), self._p(ini), self._p(out))
+        assert rc == 0, rc
+        return out[0]
 
     def reduce_by_key(self, keys: np.ndarray, vals: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
         keys = np.ascontiguousarray(keys)

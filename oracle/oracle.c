@@ -14,6 +14,7 @@
  *   LSD radix sort    thrust/system/detail/sequential/stable_radix_sort.inl:224-339
  *   greater<T>        thrust/system/detail/sequential/sort.inl:54-104
  *   scans             thrust/system/detail/sequential/scan.h:39-116
+ *   reduce            thrust/system/detail/sequential/reduce.h:43-62
  *   reduce_by_key     thrust/system/detail/sequential/reduce_by_key.h:34-96
  *   histogram         examples/histogram.cu:60-101 (+ generic/binary_search.inl:95-133)
  */
@@ -178,6 +179,30 @@ int oracle_scan(const void* in, void* out, uint64_t n, int dtype, int exclusive,
     case DT_I64: case DT_U64: SCAN_BODY(uint64_t);
     case DT_F32: SCAN_BODY(float);
     case DT_F64: SCAN_BODY(double);
+    default: return -1;
+  }
+}
+
+/* reduce with plus (sequential/reduce.h:43-62): the accumulator starts as init, has its
+ * type, and adds the elements left to right. The narrow integer types add in int and
+ * convert back after every step, which is addition modulo 2^width. init == NULL is 0. */
+#define REDUCE_BODY(T)                                                      \
+  do {                                                                      \
+    const T* a = (const T*)in;                                              \
+    T sum = init ? *(const T*)init : (T)0;                                  \
+    for (uint64_t i = 0; i < n; ++i) sum = (T)(sum + a[i]);                 \
+    *(T*)out = sum;                                                         \
+    return 0;                                                               \
+  } while (0)
+
+int oracle_reduce(const void* in, uint64_t n, int dtype, const void* init, void* out) {
+  switch (dtype) {
+    case DT_I8: case DT_U8: REDUCE_BODY(uint8_t);   /* two's-complement wrap == unsigned add */
+    case DT_I16: case DT_U16: REDUCE_BODY(uint16_t);
+    case DT_I32: case DT_U32: REDUCE_BODY(uint32_t);
+    case DT_I64: case DT_U64: REDUCE_BODY(uint64_t);
+    case DT_F32: REDUCE_BODY(float);
+    case DT_F64: REDUCE_BODY(double);
     default: return -1;
   }
 }

@@ -88,6 +88,14 @@ static int sort_pairs_k(void* keys, void* vals, uint64_t n, int val_bytes, int d
     default: return -1;                                         \
   }
 
+template <typename K>
+static int reduce_t(const void* in, uint64_t n, const void* init, void* out) {
+  const K* i = static_cast<const K*>(in);
+  *static_cast<K*>(out) = init ? thrust::reduce(thrust::device, i, i + n, *static_cast<const K*>(init))
+                               : thrust::reduce(thrust::device, i, i + n);
+  return 0;
+}
+
 template <typename T>
 static int scan_t(const void* in, void* out, uint64_t n, int exclusive, const void* init) {
   const T* i = static_cast<const T*>(in);
@@ -159,6 +167,13 @@ int ref_sort_by_key(void* keys, void* vals, uint64_t n, int key_dtype, int val_b
 // 4-argument exclusive_scan (init = value_type{}).
 int ref_scan(const void* in, void* out, uint64_t n, int dtype, int exclusive, const void* init) {
   DISPATCH_NUM(dtype, scan_t<T>(in, out, n, exclusive, init));
+}
+
+// thrust::reduce(first, last, init) with plus; init == NULL means the 2-argument form
+// (init = value_type(0)).
+int ref_reduce(const void* in, uint64_t n, int dtype, const void* init, void* out) {
+  if (dtype == DT_BOOL) return -1;
+  DISPATCH_KEY(dtype, reduce_t<K>(in, n, init, out));
 }
 
 // thrust::reduce_by_key(keys, keys+n, vals, keys_out, vals_out) (equal_to, plus).

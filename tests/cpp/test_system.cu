@@ -119,6 +119,21 @@ void test_scan_type(size_t n) {
   CHECK(thrust::host_vector<T>(d) == h);
 }
 
+template <typename T>
+void test_reduce_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "reduce %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<T> h = random_vec<T>(n, 37 + (unsigned)n, -1000, 1000);
+  thrust::device_vector<T> d = h;
+  const auto f0 = fast();
+  // all three arities (the CUDA system forwards the short forms with qualified calls,
+  // thrust/system/cuda/detail/reduce.h:1045-1063)
+  CHECK(thrust::reduce(tb::par, d.begin(), d.end()) == thrust::reduce(thrust::host, h.begin(), h.end()));
+  CHECK(thrust::reduce(tb::par, d.begin(), d.end(), (T)13) == thrust::reduce(thrust::host, h.begin(), h.end(), (T)13));
+  CHECK(thrust::reduce(tb::par, d.begin(), d.end(), (T)13, thrust::plus<T>()) ==
+        thrust::reduce(thrust::host, h.begin(), h.end(), (T)13));
+  CHECK(fast() == f0 + 3);
+}
+
 template <typename K, typename V>
 void test_rbk_type(size_t n) {
   std::snprintf(g_ctx, sizeof g_ctx, "rbk %s n=%zu", __PRETTY_FUNCTION__, n);
@@ -172,6 +187,12 @@ int main() {
     for (int i = 0; i < 5; ++i) CHECK(in[i] == w1[i]);
   }
   {
+    const int raw[3] = {1, -2, 3};  // testing/reduce.cu:26-38
+    thrust::device_vector<int> v(raw, raw + 3);
+    CHECK(thrust::reduce(tb::par, v.begin(), v.end()) == 2);
+    CHECK(thrust::reduce(tb::par, v.begin(), v.end(), 10) == 12);
+  }
+  {
     const int rk[9] = {11, 11, 21, 20, 21, 21, 21, 37, 37};
     thrust::device_vector<int> k(rk, rk + 9), v(9), ko(9), vo(9);
     thrust::sequence(v.begin(), v.end());
@@ -199,6 +220,10 @@ int main() {
     test_scan_type<int>(n);
     test_scan_type<unsigned int>(n);
     test_scan_type<long long>(n);
+    test_reduce_type<signed char>(n);
+    test_reduce_type<unsigned short>(n);
+    test_reduce_type<int>(n);
+    test_reduce_type<unsigned long long>(n);
     test_rbk_type<int, unsigned int>(n);
     test_rbk_type<unsigned char, long long>(n);
     test_rbk_type<long long, int>(n);
@@ -230,6 +255,16 @@ int main() {
     thrust::exclusive_scan(tb::par, fin.begin(), fin.end(), iout.begin(), (int)0);
     CHECK(fwd() == w0 + 4);
     CHECK(iout[0] == 0 && iout[1] == 1 && iout[2] == 2 && iout[3] == 3);
+    // reduce: float input with an int accumulator, and int input with a float one
+    // (testing/reduce.cu:99-119), then an operator that is not plus
+    thrust::device_vector<float> fr(4);
+    fr[0] = 1.5f; fr[1] = 2.5f; fr[2] = 3.5f; fr[3] = 4.5f;
+    thrust::device_vector<int> ir(4);
+    ir[0] = 1; ir[1] = 2; ir[2] = 3; ir[3] = 4;
+    CHECK(thrust::reduce(tb::par, fr.begin(), fr.end(), (int)0) == 10);
+    CHECK(thrust::reduce(tb::par, ir.begin(), ir.end(), 0.5f) == 10.5f);
+    CHECK(thrust::reduce(tb::par, ir.begin(), ir.end(), 0, thrust::maximum<int>()) == 4);
+    CHECK(fwd() == w0 + 7);
   }
 
   // ---- dispatch by iterator tag, streams, nosync ---------------------------------------------

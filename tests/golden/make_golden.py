@@ -68,6 +68,16 @@ def main():
     out["hist/data"] = data
     out["hist/bins"] = np.arange(64, dtype=np.int32)
     out["hist/counts"] = ref.histogram(data, np.arange(64, dtype=np.int32))
+    # reduce: drawn last, so the arrays above do not change when this block is extended
+    for t in TYPES:
+        if t == "bool":
+            continue
+        dt = np.dtype(t)
+        a = rng.uniform(-1, 1, size=N).astype(dt) if dt.kind == "f" else \
+            rng.integers(np.iinfo(dt).min, np.iinfo(dt).max, size=N, dtype=dt, endpoint=True)
+        out[f"reduce/{t}/in"] = a
+        out[f"reduce/{t}/sum"] = np.array([ref.reduce(a)])
+        out[f"reduce/{t}/sum_init13"] = np.array([ref.reduce(a, 13)])
     np.savez_compressed(Path(__file__).with_name("reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays; reference Thrust version", ref.thrust_version)
 

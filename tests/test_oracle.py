@@ -43,6 +43,10 @@ def test_known_answers(port):
     assert port.scan(f).tolist() == s["float_inclusive"]
     assert port.scan(f, True, 5.5).tolist() == s["float_exclusive_init_5.5"]
     assert port.scan(np.array(s["int_input"], dtype=np.int32)).tolist() == s["int_inclusive"]
+    s = KA["reduce_simple"]
+    for dt in (np.int8, np.int32, np.int64, np.float32, np.float64):
+        a = np.array(s["input"], dtype=dt)
+        assert port.reduce(a) == s["sum"] and port.reduce(a, 10) == s["sum_init_10"]
     s = KA["reduce_by_key_simple"]
     for dt in (np.int8, np.int32, np.uint64):
         ko, vo = port.reduce_by_key(np.array(s["keys"], dtype=dt), np.array(s["values"], dtype=np.int32))
@@ -75,6 +79,13 @@ def test_scan_and_rbk_match_reference_vectors(port, vectors, t):
     assert vo.tobytes() == vectors[f"rbk/{t}/out_vals"].tobytes()
 
 
+@pytest.mark.parametrize("t", [t for t in TYPES if t != "bool"])
+def test_reduce_matches_reference_vectors(port, vectors, t):
+    a = vectors[f"reduce/{t}/in"]
+    assert np.array([port.reduce(a)]).tobytes() == vectors[f"reduce/{t}/sum"].tobytes()
+    assert np.array([port.reduce(a, 13)]).tobytes() == vectors[f"reduce/{t}/sum_init13"].tobytes()
+
+
 def test_histogram_matches_reference_vectors(port, vectors):
     assert port.histogram(vectors["hist/data"], vectors["hist/bins"]).tolist() == vectors["hist/counts"].tolist()
 
@@ -87,6 +98,7 @@ def test_edge_cases(port):
         assert port.sort(one, True).tolist() == one.tolist()
     k, v = port.reduce_by_key(np.empty(0, dtype=np.int32), np.empty(0, dtype=np.float32))
     assert k.size == 0 and v.size == 0
+    assert port.reduce(np.empty(0, dtype=np.int32)) == 0 and port.reduce(np.empty(0, dtype=np.float32), 2.5) == 2.5
     # float keys: bitwise total order, -0.0 before +0.0, NaNs at the ends by sign
     f = np.array([0.0, -0.0, np.inf, -np.inf, 1.0, -1.0], dtype=np.float32)
     assert port.sort(f).view(np.uint32).tolist() == np.array([-np.inf, -1.0, -0.0, 0.0, 1.0, np.inf], dtype=np.float32).view(np.uint32).tolist()
@@ -131,3 +143,8 @@ def test_port_matches_live_reference(port, system):
             assert x[1].tobytes() == y[1].tobytes()
         else:
             assert np.allclose(x[1], y[1], rtol=1e-4, atol=1e-3)
+        for init in (None, 7):
+            if dt.kind != "f" or system == "cpp":  # the OMP system adds per-thread partial sums
+                assert np.array([port.reduce(a, init)]).tobytes() == np.array([ref.reduce(a, init)]).tobytes()
+            else:
+                assert abs(float(port.reduce(a, init)) - float(ref.reduce(a, init))) <= 1e-5 * float(np.abs(a).sum())

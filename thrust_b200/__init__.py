@@ -12,7 +12,7 @@ ImportError (there is no CPU or PyTorch fallback).
 import importlib
 
 _ALGORITHMS = (
-    "sort", "stable_sort", "sort_by_key", "stable_sort_by_key", "inclusive_scan", "exclusive_scan",
+    "sort", "stable_sort", "sort_by_key", "stable_sort_by_key", "inclusive_scan", "exclusive_scan", "reduce",
     "reduce_by_key", "histogram_sorted", "dense_histogram", "tb200_dtype",
 )
 __all__ = ["Tb200Error", "_capi", "algorithms", "datagen", "sample_sort", *_ALGORITHMS]

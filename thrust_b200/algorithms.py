@@ -140,6 +140,39 @@ def exclusive_scan(inp: torch.Tensor, out: Optional[torch.Tensor] = None, init=N
     return _scan(inp, out, True, init, dtype, sync, temp)
 
 
+def reduce(inp: torch.Tensor, init=None, dtype: Optional[int] = None, out: Optional[torch.Tensor] = None,
+           temp: Optional[torch.Tensor] = None):
+    """thrust::reduce with plus (thrust/reduce.h; cuda/detail/reduce.h:1029-1062): init + the sum of
+    ``inp`` in the element type (integers wrap). Returns a Python number; like the reference it
+    synchronises to read the result back (cuda/detail/reduce.h:984-1000)."""
+    _check_tensor(inp, "input")
+    dt = tb200_dtype(inp, dtype)
+    ctypes_of = {capi.I8: C.c_int8, capi.U8: C.c_uint8, capi.I16: C.c_int16, capi.U16: C.c_uint16,
+                 capi.I32: C.c_int32, capi.U32: C.c_uint32, capi.I64: C.c_int64, capi.U64: C.c_uint64,
+                 capi.F32: C.c_float, capi.F64: C.c_double}
+    if dt not in ctypes_of:
+        raise TypeError("reduce supports integers of 1 to 8 bytes, float32 and float64")
+    ctype = ctypes_of[dt]
+    init_buf = ctype(init) if init is not None else None
+    n = inp.numel()
+    if out is None:
+        out = torch.empty(16, dtype=torch.uint8, device=inp.device)
+    with torch.cuda.device(inp.device):
+        stream = _stream(inp)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_reduce(None, C.byref(need), None, n, dt, None, None, stream), "tb200_reduce(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, inp.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_reduce(C.c_void_p(temp.data_ptr()), C.byref(have),
+                                         C.c_void_p(inp.data_ptr()) if n else None, n, dt,
+                                         C.byref(init_buf) if init_buf is not None else None,
+                                         C.c_void_p(out.data_ptr()), stream), "tb200_reduce")
+        _finish(temp, stream, "tb200_reduce", True)
+    raw = bytes(out.view(torch.uint8)[:C.sizeof(ctype)].cpu().numpy().tobytes())
+    return ctype.from_buffer_copy(raw).value
+
+
 def reduce_by_key(keys: torch.Tensor, values: torch.Tensor, keys_out: Optional[torch.Tensor] = None,
                   values_out: Optional[torch.Tensor] = None, key_dtype: Optional[int] = None,
                   val_dtype: Optional[int] = None,
