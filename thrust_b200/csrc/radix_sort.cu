@@ -816,7 +816,7 @@ enum { kPhaseAll = 0, kPhaseBegin = 1, kPhaseFinish = 2 };
 
 template <typename UK, int VB>
 struct Tuning {
-  // threads x items per thread of one onesweep tile, and CTAs the register budget must allow per SM
+  // threads x items per thread of one onesweep tile, and CTAs that must fit the register file of one SM
 #ifdef TB200_TUNE_THREADS
   static constexpr int kThreads = TB200_TUNE_THREADS;
   static constexpr int kItems = TB200_TUNE_ITEMS;
@@ -970,13 +970,42 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
   for (int i = threadIdx.x; i < kRadix; i += kHistThreads) s_hist[i] = 0;
   for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) s_split[i] = splitters[i];
   __syncthreads();
-  // Whole warps walk the keys together: equal buckets inside a warp are found with one ballot
-  // per bucket-id bit and counted by one lane, so a handful of buckets does not serialise the
-  // shared-memory atomics.
+  // Two forms. Up to seven splitters (eight GPUs): the splitters live in registers, padded with
+  // the largest key, the search is at most three compare-and-select levels, and every thread
+  // counts into eight 8-bit fields of one register that it adds to the shared counters every
+  // 248 keys. More splitters: binary search in shared memory; equal buckets inside a warp are
+  // found with one ballot per bucket-id bit and counted by one lane, so the shared-memory
+  // atomics do not serialise.
+  const bool few = num_split <= 7;
+  UK sp[7];
+#pragma unroll
+  for (int j = 0; j < 7; ++j) sp[j] = (few && (unsigned)j < num_split) ? s_split[j] : (UK)~(UK)0;
+  unsigned long long packed = 0;
+  unsigned since = 0;
+  auto flush = [&]() {
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+      const unsigned c = (unsigned)(packed >> (8 * b)) & 0xffu;
+      if (c) atomicAdd(&s_hist[b], c);
+    }
+    packed = 0;
+    since = 0;
+  };
+  auto bucket_few = [&](UK k) -> unsigned {  // number of splitters strictly below k
+    if (num_split <= 1) return sp[0] < k;
+    if (num_split <= 3) {
+      const bool c1 = sp[1] < k;
+      return 2u * c1 + (unsigned)((c1 ? sp[2] : sp[0]) < k);
+    }
+    const bool c1 = sp[3] < k;
+    const bool c2 = (c1 ? sp[5] : sp[1]) < k;
+    const bool c3 = (c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0])) < k;
+    return 4u * c1 + 2u * c2 + (unsigned)c3;
+  };
   const int split_bits = 32 - __clz(num_split | 1u);
   const unsigned lt_mask = lanemask_lt();
-  auto count = [&](UK k, bool valid) {
-    unsigned lo = 0, hi = num_split;  // number of splitters strictly below k
+  auto count_many = [&](UK k, bool valid) {
+    unsigned lo = 0, hi = num_split;
     while (lo < hi) {
       const unsigned mid = (lo + hi) >> 1;
       if (s_split[mid] < k) lo = mid + 1; else hi = mid;
@@ -992,17 +1021,34 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
     KeyVec<UK> v[kHistUnroll];
 #pragma unroll
     for (int u = 0; u < kHistUnroll; ++u) v[u] = src[u * kHistThreads + threadIdx.x];
+    if (few) {
 #pragma unroll
-    for (int u = 0; u < kHistUnroll; ++u)
+      for (int u = 0; u < kHistUnroll; ++u)
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) count(v[u].v[j], true);
+        for (int j = 0; j < VEC; ++j) packed += 1ull << (8 * bucket_few(v[u].v[j]));
+      since += VEC * kHistUnroll;
+      if (since + VEC * kHistUnroll > 255u) flush();
+    } else {
+#pragma unroll
+      for (int u = 0; u < kHistUnroll; ++u)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) count_many(v[u].v[j], true);
+    }
   }
   for (uint64_t base = full_chunks * CHUNK + (uint64_t)blockIdx.x * kHistThreads; base < n;
        base += (uint64_t)gridDim.x * kHistThreads) {
     const uint64_t i = base + threadIdx.x;
     const bool valid = i < n;
-    count(valid ? keys[i] : UK(0), valid);
+    if (few) {
+      if (valid) {
+        packed += 1ull << (8 * bucket_few(keys[i]));
+        if (++since >= 255u) flush();
+      }
+    } else {
+      count_many(valid ? keys[i] : UK(0), valid);
+    }
   }
+  if (few) flush();
   __syncthreads();
   for (int i = threadIdx.x; i <= (int)num_split; i += kHistThreads)
     if (s_hist[i]) atomicAdd(&ctl->hist[0][i], (unsigned long long)s_hist[i]);
