@@ -126,6 +126,8 @@ def cpu_sort_sample(log2_n: int, reps: int, warmup: int):
     from thrust_b200 import datagen as g
     if oracle.have_ref("omp"):
         chk, kind = oracle.ref("omp"), "reference"
+        # all host cores this process may use, whatever OMP_NUM_THREADS the launcher exported
+        chk.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     else:
         chk, kind = oracle.port(), "port"
         log2_n = min(log2_n, 22)

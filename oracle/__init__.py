@@ -68,6 +68,17 @@ class CpuChecker:
             self._lib.ref_thrust_version.restype = i32
             self.thrust_version = int(self._lib.ref_thrust_version())
 
+    def set_threads(self, n: int) -> int:
+        """Asks the OMP reference library for n threads (no-op for the others); returns the count in use."""
+        if hasattr(self._lib, "ref_set_num_threads") and self.kind != "port":
+            try:
+                self._lib.ref_set_num_threads.argtypes = [C.c_int]
+                self._lib.ref_set_num_threads(int(n))
+                self.threads = int(self._lib.ref_num_threads())
+            except AttributeError:
+                pass
+        return self.threads
+
     @staticmethod
     def _p(a: Optional[np.ndarray]):
         return None if a is None else C.c_void_p(a.ctypes.data)

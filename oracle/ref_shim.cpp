@@ -145,6 +145,16 @@ int ref_thrust_version(void) { return THRUST_VERSION; }
 
 int ref_device_system(void) { return THRUST_DEVICE_SYSTEM; }
 
+// Launchers that start one process per GPU export OMP_NUM_THREADS=1; the timed baseline asks
+// for the host's cores explicitly.
+void ref_set_num_threads(int n) {
+#if defined(_OPENMP)
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int ref_num_threads(void) {
 #if defined(_OPENMP)
   return omp_get_max_threads();
