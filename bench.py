@@ -266,7 +266,16 @@ def bench_others(dev, peak):
     nruns = int(runs.item())
     entry("reduce_by_key_i32_f32_2^28", rbk, lambda: None, n, "Gelem/s", 8.0 * (n + nruns),
           f"(n + runs) x (4 B key + 4 B value), runs = {nruns}")
-    del keys, vals, ko, vo
+    # next row of the path: inclusive_scan_by_key over the same keys and values
+    so = torch.empty_like(vals)
+
+    def sbk():
+        capi.check(capi.lib.tb200_scan_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
+            C.c_void_p(so.data_ptr()), n, capi.I32, capi.F32, 0, None, st), "tb200_scan_by_key")
+    entry("inclusive_scan_by_key_i32_f32_2^28", sbk, lambda: None, n, "Gelem/s", 12.0 * n,
+          "4 B key + 4 B value read, 4 B value written = 12 B/element")
+    del keys, vals, ko, vo, so
 
     # C3: stable sort_by_key of 2^28 (uint64, uint32) pairs
     k0, v0 = g.pairs_u64_u32(n, g.SEED_PAIRS_U64, 0, dev)

@@ -159,6 +159,20 @@ int tb200_reduce_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys_in,
                         uint64_t* d_num_runs, uint64_t n, int key_dtype, int val_dtype,
                         tb200_stream_t stream);
 
+/* ---- scan_by_key ----------------------------------------------------------------------
+ * Segmented prefix sums with thrust::equal_to on consecutive keys and thrust::plus:
+ * out[i] = sum of the elements of i's run up to and including i (exclusive == 0), or
+ * init + the sum of those before i (exclusive != 0: every run restarts at init; h_init is a
+ * HOST pointer to one value, NULL = 0). Keys: any dtype code (integers by bit pattern,
+ * floating point with IEEE ==); values: 4- or 8-byte integers, F32, F64. d_vals_out may be
+ * d_vals_in. Integer sums are exact (they wrap); floating-point sums are formed in scan-tree
+ * order. Replaces thrust::cuda_cub::detail::{inclusive,exclusive}_scan_by_key_n and their
+ * cub::DispatchScanByKey (thrust/system/cuda/detail/scan_by_key.h:96-290); semantics of
+ * thrust/system/detail/sequential/scan_by_key.h:34-146. */
+int tb200_scan_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals_in,
+                      void* d_vals_out, uint64_t n, int key_dtype, int val_dtype, int exclusive,
+                      const void* h_init, tb200_stream_t stream);
+
 /* ---- reduce ---------------------------------------------------------------------------
  * *d_out = init + in[0] + ... + in[n-1] with thrust::plus in the element type (integer sums
  * wrap; dtype: any integer or floating-point code, not BOOL). h_init is a HOST pointer to
@@ -201,7 +215,7 @@ int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream);
  * to kinds[i] (may be NULL) for i < capacity and returns the number of launches (negative:
  * -cudaError_t). kinds: 1 sort histogram, 2 radix pass, 3 sort copy-back, 4 scan,
  * 5 reduce_by_key, 6 histogram of sorted data, 7 partition histogram, 8 partition pass,
- * 9 reduce. */
+ * 9 reduce, 10 scan_by_key. */
 int tb200_trace_begin(tb200_stream_t stream);
 int tb200_trace_end(float* ms, int* kinds, int capacity);
 

@@ -1,6 +1,7 @@
 // thrust_b200::system — a Thrust custom system (in the style of the reference's
 // examples/minimal_custom_backend.cu:17-37) that routes sort / stable_sort /
-// sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / reduce / reduce_by_key
+// sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / inclusive_scan_by_key /
+// exclusive_scan_by_key / reduce / reduce_by_key
 // on contiguous arithmetic data to the sm_100a kernels behind the C ABI of
 // thrust_b200.h, and everything else to the CUDA system it derives from.
 //
@@ -268,6 +269,72 @@ OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result, Init init) 
 template <typename InIt, typename OutIt>
 OutIt exclusive_scan(system& s, InIt first, InIt last, OutIt result) {
   return exclusive_scan(s, first, last, result, detail::value_t<InIt>{});  // scan.h:340-349
+}
+
+// ---- scan_by_key (cuda/detail/scan_by_key.h:296-485) --------------------------------------
+// Fast path: contiguous iterators, arithmetic keys, equal_to, plus, and one 4- or 8-byte
+// numeric type for values, output and (exclusive) init.
+namespace detail {
+template <typename KeyIt, typename ValIt, typename OutIt, typename Acc, typename Pred, typename Op>
+constexpr bool scan_by_key_fast_v =
+    contiguous_v<KeyIt> && contiguous_v<ValIt> && contiguous_v<OutIt> && is_plain_arithmetic<value_t<KeyIt>>::value &&
+    is_scan_type<Acc>::value && std::is_same<value_t<ValIt>, Acc>::value && std::is_same<value_t<OutIt>, Acc>::value &&
+    is_equal_to<Pred, value_t<KeyIt>>::value && is_plus<Op, Acc>::value;
+template <typename KeyIt, typename ValIt, typename OutIt, typename T>
+OutIt scan_by_key_fast(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, bool exclusive, const T* init) {
+  using K = value_t<KeyIt>;
+  const uint64_t n = (uint64_t)(kl - kf);
+  size_t bytes = 0;
+  throw_on_error(tb200_scan_by_key(nullptr, &bytes, nullptr, nullptr, nullptr, n, dtype_of<K>(), dtype_of<T>(),
+                                   exclusive, init, s.stream), "tb200_scan_by_key");
+  void* temp = workspace(bytes, s.stream);
+  throw_on_error(tb200_scan_by_key(temp, &bytes, n ? (const void*)raw(kf) : nullptr,
+                                   n ? (const void*)raw(vf) : nullptr, n ? (void*)raw(result) : nullptr, n,
+                                   dtype_of<K>(), dtype_of<T>(), exclusive, init, s.stream), "tb200_scan_by_key");
+  ++fast_calls();
+  finish(s, temp, "tb200_scan_by_key");
+  return result + (kl - kf);
+}
+}  // namespace detail
+
+template <typename KeyIt, typename ValIt, typename OutIt, typename Pred, typename Op>
+OutIt inclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, Pred pred, Op op) {
+  using T = detail::value_t<ValIt>;  // accumulator = value type (sequential/scan_by_key.h:52-53)
+  if constexpr (detail::scan_by_key_fast_v<KeyIt, ValIt, OutIt, T, Pred, Op>) {
+    return detail::scan_by_key_fast<KeyIt, ValIt, OutIt, T>(s, kf, kl, vf, result, false, nullptr);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::inclusive_scan_by_key(detail::inherited(s), kf, kl, vf, result, pred, op);
+  }
+}
+template <typename KeyIt, typename ValIt, typename OutIt, typename Pred>
+OutIt inclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, Pred pred) {
+  return inclusive_scan_by_key(s, kf, kl, vf, result, pred, thrust::plus<>{});  // scan_by_key.h:338-352
+}
+template <typename KeyIt, typename ValIt, typename OutIt>
+OutIt inclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result) {
+  return inclusive_scan_by_key(s, kf, kl, vf, result, thrust::equal_to<detail::value_t<KeyIt>>());  // :359-372
+}
+template <typename KeyIt, typename ValIt, typename OutIt, typename Init, typename Pred, typename Op>
+OutIt exclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, Init init, Pred pred, Op op) {
+  if constexpr (detail::scan_by_key_fast_v<KeyIt, ValIt, OutIt, Init, Pred, Op>) {  // accumulator = type of init
+    return detail::scan_by_key_fast<KeyIt, ValIt, OutIt, Init>(s, kf, kl, vf, result, true, &init);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::exclusive_scan_by_key(detail::inherited(s), kf, kl, vf, result, init, pred, op);
+  }
+}
+template <typename KeyIt, typename ValIt, typename OutIt, typename Init, typename Pred>
+OutIt exclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, Init init, Pred pred) {
+  return exclusive_scan_by_key(s, kf, kl, vf, result, init, pred, thrust::plus<>{});  // scan_by_key.h:425-441
+}
+template <typename KeyIt, typename ValIt, typename OutIt, typename Init>
+OutIt exclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, Init init) {
+  return exclusive_scan_by_key(s, kf, kl, vf, result, init, thrust::equal_to<detail::value_t<KeyIt>>());  // :449-463
+}
+template <typename KeyIt, typename ValIt, typename OutIt>
+OutIt exclusive_scan_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result) {
+  return exclusive_scan_by_key(s, kf, kl, vf, result, detail::value_t<ValIt>{});  // scan_by_key.h:471-485
 }
 
 // ---- reduce (cuda/detail/reduce.h:1029-1062) ---------------------------------------------

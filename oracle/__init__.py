@@ -57,6 +57,8 @@ class CpuChecker:
         self._scan.argtypes, self._scan.restype = [vp, vp, u64, i32, i32, vp], i32
         self._rbk = getattr(self._lib, prefix + "reduce_by_key")
         self._rbk.argtypes, self._rbk.restype = [vp, vp, vp, vp, u64, i32, i32], C.c_int64
+        self._sbk_scan = getattr(self._lib, prefix + "scan_by_key")
+        self._sbk_scan.argtypes, self._sbk_scan.restype = [vp, vp, vp, u64, i32, i32, i32, vp], i32
         self._reduce = getattr(self._lib, prefix + "reduce")
         self._reduce.argtypes, self._reduce.restype = [vp, u64, i32, vp, vp], i32
         self._hist = getattr(self._lib, prefix + "histogram")
@@ -109,6 +111,16 @@ class CpuChecker:
         out = a if inplace else np.empty_like(a)
         ini = None if init is None else np.array([init], dtype=a.dtype)
         rc = self._scan(self._p(a), self._p(out), a.size, dt_of(a), int(exclusive), self._p(ini))
+        assert rc == 0, rc
+        return out
+
+    def scan_by_key(self, keys: np.ndarray, vals: np.ndarray, exclusive: bool = False, init=None) -> np.ndarray:
+        keys = np.ascontiguousarray(keys)
+        vals = np.ascontiguousarray(vals)
+        out = np.empty_like(vals)
+        ini = None if init is None else np.array([init], dtype=vals.dtype)
+        rc = self._sbk_scan(self._p(keys), self._p(vals), self._p(out), keys.size, dt_of(keys), dt_of(vals),
+                            int(exclusive), self._p(ini))
         assert rc == 0, rc
         return out
 

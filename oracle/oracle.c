@@ -16,6 +16,7 @@
  *   scans             thrust/system/detail/sequential/scan.h:39-116
  *   reduce            thrust/system/detail/sequential/reduce.h:43-62
  *   reduce_by_key     thrust/system/detail/sequential/reduce_by_key.h:34-96
+ *   scan_by_key       thrust/system/detail/sequential/scan_by_key.h:34-146
  *   histogram         examples/histogram.cu:60-101 (+ generic/binary_search.inl:95-133)
  */
 #include <stdint.h>
@@ -233,6 +234,56 @@ int oracle_reduce(const void* in, uint64_t n, int dtype, const void* init, void*
     case DT_F64: RBK_BODY(KT, double, EQ_PLAIN);                            \
     default: return -1;                                                     \
   }
+
+/* inclusive / exclusive scan_by_key with equal_to / plus (scan_by_key.h:34-146): consecutive
+ * keys are compared; the inclusive accumulator has the values' type; the exclusive one starts
+ * every run at init and adds left to right ((init + v0) + v1 ...). init == NULL is 0. */
+#define SBK_BODY(KT, VT)                                                    \
+  do {                                                                      \
+    const KT* k = (const KT*)kin; const VT* v = (const VT*)vin;             \
+    VT* o = (VT*)vout;                                                      \
+    const VT ini = init ? *(const VT*)init : (VT)0;                         \
+    if (n == 0) return 0;                                                   \
+    if (!exclusive) {                                                       \
+      VT pv = v[0]; o[0] = pv;                                              \
+      for (uint64_t i = 1; i < n; ++i) {                                    \
+        const VT x = v[i];                                                  \
+        pv = (k[i - 1] == k[i]) ? (VT)(pv + x) : x;                         \
+        o[i] = pv;                                                          \
+      }                                                                     \
+    } else {                                                                \
+      VT next = ini;                                                        \
+      for (uint64_t i = 0; i < n; ++i) {                                    \
+        const VT x = v[i];                                                  \
+        if (i > 0 && !(k[i - 1] == k[i])) next = ini;                       \
+        o[i] = next;                                                        \
+        next = (VT)(next + x);                                              \
+      }                                                                     \
+    }                                                                       \
+    return 0;                                                               \
+  } while (0)
+
+#define SBK_VALS(KT)                                                        \
+  switch (val_dtype) {                                                      \
+    case DT_I32: case DT_U32: SBK_BODY(KT, uint32_t);                       \
+    case DT_I64: case DT_U64: SBK_BODY(KT, uint64_t);                       \
+    case DT_F32: SBK_BODY(KT, float);                                       \
+    case DT_F64: SBK_BODY(KT, double);                                      \
+    default: return -1;                                                     \
+  }
+
+int oracle_scan_by_key(const void* kin, const void* vin, void* vout, uint64_t n, int key_dtype, int val_dtype,
+                       int exclusive, const void* init) {
+  switch (key_dtype) {
+    case DT_I8: case DT_U8: case DT_BOOL: SBK_VALS(uint8_t);
+    case DT_I16: case DT_U16: SBK_VALS(uint16_t);
+    case DT_I32: case DT_U32: SBK_VALS(uint32_t);
+    case DT_I64: case DT_U64: SBK_VALS(uint64_t);
+    case DT_F32: SBK_VALS(float);
+    case DT_F64: SBK_VALS(double);
+    default: return -1;
+  }
+}
 
 int64_t oracle_reduce_by_key(const void* kin, const void* vin, void* kout, void* vout, uint64_t n,
                              int key_dtype, int val_dtype) {

@@ -96,6 +96,30 @@ static int reduce_t(const void* in, uint64_t n, const void* init, void* out) {
   return 0;
 }
 
+template <typename K, typename V>
+static int sbk_t(const void* kin, const void* vin, void* vout, uint64_t n, int exclusive, const void* init) {
+  const K* k = static_cast<const K*>(kin);
+  const V* v = static_cast<const V*>(vin);
+  V* o = static_cast<V*>(vout);
+  if (!exclusive)      thrust::inclusive_scan_by_key(thrust::device, k, k + n, v, o);
+  else if (init)       thrust::exclusive_scan_by_key(thrust::device, k, k + n, v, o, *static_cast<const V*>(init));
+  else                 thrust::exclusive_scan_by_key(thrust::device, k, k + n, v, o);
+  return 0;
+}
+template <typename K>
+static int sbk_k(const void* kin, const void* vin, void* vout, uint64_t n, int val_dtype, int exclusive,
+                 const void* init) {
+  switch (val_dtype) {
+    case DT_I32: return sbk_t<K, int>(kin, vin, vout, n, exclusive, init);
+    case DT_U32: return sbk_t<K, unsigned int>(kin, vin, vout, n, exclusive, init);
+    case DT_I64: return sbk_t<K, long long>(kin, vin, vout, n, exclusive, init);
+    case DT_U64: return sbk_t<K, unsigned long long>(kin, vin, vout, n, exclusive, init);
+    case DT_F32: return sbk_t<K, float>(kin, vin, vout, n, exclusive, init);
+    case DT_F64: return sbk_t<K, double>(kin, vin, vout, n, exclusive, init);
+    default: return -1;
+  }
+}
+
 template <typename T>
 static int scan_t(const void* in, void* out, uint64_t n, int exclusive, const void* init) {
   const T* i = static_cast<const T*>(in);
@@ -184,6 +208,13 @@ int ref_scan(const void* in, void* out, uint64_t n, int dtype, int exclusive, co
 int ref_reduce(const void* in, uint64_t n, int dtype, const void* init, void* out) {
   if (dtype == DT_BOOL) return -1;
   DISPATCH_KEY(dtype, reduce_t<K>(in, n, init, out));
+}
+
+// thrust::inclusive_scan_by_key / exclusive_scan_by_key (equal_to, plus); init == NULL means
+// the form without init (0).
+int ref_scan_by_key(const void* kin, const void* vin, void* vout, uint64_t n, int key_dtype, int val_dtype,
+                    int exclusive, const void* init) {
+  DISPATCH_KEY(key_dtype, sbk_k<K>(kin, vin, vout, n, val_dtype, exclusive, init));
 }
 
 // thrust::reduce_by_key(keys, keys+n, vals, keys_out, vals_out) (equal_to, plus).

@@ -119,6 +119,44 @@ void test_scan_type(size_t n) {
   CHECK(thrust::host_vector<T>(d) == h);
 }
 
+template <typename K, typename V>
+void test_scan_by_key_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "scan_by_key %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<K> hk(n);
+  std::mt19937 rng(53 + (unsigned)n);
+  K cur = 0;
+  for (size_t i = 0; i < n; ++i) { if (rng() % 5 == 0) cur = (K)(cur + 1); hk[i] = cur; }
+  thrust::host_vector<V> hv = random_vec<V>(n, 59, 0, 1000), hout(n);
+  thrust::device_vector<K> dk = hk;
+  thrust::device_vector<V> dv = hv, out(n);
+  const auto f0 = fast();
+  auto e = thrust::inclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin());
+  CHECK(e == out.end());
+  thrust::inclusive_scan_by_key(thrust::host, hk.begin(), hk.end(), hv.begin(), hout.begin());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::inclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin(), thrust::equal_to<K>());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::inclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin(), thrust::equal_to<K>(),
+                                thrust::plus<V>());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::exclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin());
+  thrust::exclusive_scan_by_key(thrust::host, hk.begin(), hk.end(), hv.begin(), hout.begin());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::exclusive_scan_by_key(thrust::host, hk.begin(), hk.end(), hv.begin(), hout.begin(), (V)11);
+  thrust::exclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin(), (V)11);
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::exclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin(), (V)11, thrust::equal_to<K>());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  thrust::exclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), out.begin(), (V)11, thrust::equal_to<K>(),
+                                thrust::plus<V>());
+  CHECK(thrust::host_vector<V>(out) == hout);
+  CHECK(fast() == f0 + 7);
+  // in place on the values
+  thrust::inclusive_scan_by_key(tb::par, dk.begin(), dk.end(), dv.begin(), dv.begin());
+  thrust::inclusive_scan_by_key(thrust::host, hk.begin(), hk.end(), hv.begin(), hv.begin());
+  CHECK(thrust::host_vector<V>(dv) == hv);
+}
+
 template <typename T>
 void test_reduce_type(size_t n) {
   std::snprintf(g_ctx, sizeof g_ctx, "reduce %s n=%zu", __PRETTY_FUNCTION__, n);
@@ -187,6 +225,30 @@ int main() {
     for (int i = 0; i < 5; ++i) CHECK(in[i] == w1[i]);
   }
   {
+    const int rk[7] = {0, 1, 1, 1, 2, 3, 3}, rv[7] = {1, 2, 3, 4, 5, 6, 7};  // testing/scan_by_key.inclusive.cu:12-60
+    thrust::device_vector<int> k(rk, rk + 7), v(rv, rv + 7), o(7);
+    thrust::inclusive_scan_by_key(tb::par, k.begin(), k.end(), v.begin(), o.begin());
+    const int w1[7] = {1, 2, 5, 9, 5, 6, 13};
+    for (int i = 0; i < 7; ++i) CHECK(o[i] == w1[i]);
+    thrust::exclusive_scan_by_key(tb::par, k.begin(), k.end(), v.begin(), o.begin());
+    const int w2[7] = {0, 0, 2, 5, 0, 0, 6};
+    for (int i = 0; i < 7; ++i) CHECK(o[i] == w2[i]);
+    thrust::exclusive_scan_by_key(tb::par, k.begin(), k.end(), v.begin(), o.begin(), 10);
+    const int w3[7] = {10, 10, 12, 15, 10, 10, 16};
+    for (int i = 0; i < 7; ++i) CHECK(o[i] == w3[i]);
+    // multiplies is not plus: forwarded, same answers as the reference's test
+    const auto w0 = fwd();
+    thrust::inclusive_scan_by_key(tb::par, k.begin(), k.end(), v.begin(), o.begin(), thrust::equal_to<int>(),
+                                  thrust::multiplies<int>());
+    const int w4[7] = {1, 2, 6, 24, 5, 6, 42};
+    for (int i = 0; i < 7; ++i) CHECK(o[i] == w4[i]);
+    thrust::exclusive_scan_by_key(tb::par, k.begin(), k.end(), v.begin(), o.begin(), 10, thrust::equal_to<int>(),
+                                  thrust::multiplies<int>());
+    const int w5[7] = {10, 10, 20, 60, 10, 10, 60};
+    for (int i = 0; i < 7; ++i) CHECK(o[i] == w5[i]);
+    CHECK(fwd() == w0 + 2);
+  }
+  {
     const int raw[3] = {1, -2, 3};  // testing/reduce.cu:26-38
     thrust::device_vector<int> v(raw, raw + 3);
     CHECK(thrust::reduce(tb::par, v.begin(), v.end()) == 2);
@@ -220,6 +282,9 @@ int main() {
     test_scan_type<int>(n);
     test_scan_type<unsigned int>(n);
     test_scan_type<long long>(n);
+    test_scan_by_key_type<int, int>(n);
+    test_scan_by_key_type<unsigned char, long long>(n);
+    test_scan_by_key_type<long long, unsigned int>(n);
     test_reduce_type<signed char>(n);
     test_reduce_type<unsigned short>(n);
     test_reduce_type<int>(n);

@@ -78,6 +78,15 @@ def main():
         out[f"reduce/{t}/in"] = a
         out[f"reduce/{t}/sum"] = np.array([ref.reduce(a)])
         out[f"reduce/{t}/sum_init13"] = np.array([ref.reduce(a, 13)])
+    # scan_by_key: drawn after everything above
+    for t in NUMERIC:
+        dt = np.dtype(t)
+        keys = np.cumsum(rng.random(N) < 0.3).astype(np.int32)
+        vals = rng.uniform(-50, 50, size=N).astype(dt) if dt.kind == "f" else rng.integers(0, 1000, size=N).astype(dt)
+        out[f"sbk/{t}/keys"], out[f"sbk/{t}/vals"] = keys, vals
+        out[f"sbk/{t}/inclusive"] = ref.scan_by_key(keys, vals)
+        out[f"sbk/{t}/exclusive"] = ref.scan_by_key(keys, vals, True)
+        out[f"sbk/{t}/exclusive_init11"] = ref.scan_by_key(keys, vals, True, 11)
     np.savez_compressed(Path(__file__).with_name("reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays; reference Thrust version", ref.thrust_version)
 

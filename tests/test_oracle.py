@@ -47,6 +47,12 @@ def test_known_answers(port):
     for dt in (np.int8, np.int32, np.int64, np.float32, np.float64):
         a = np.array(s["input"], dtype=dt)
         assert port.reduce(a) == s["sum"] and port.reduce(a, 10) == s["sum_init_10"]
+    s = KA["scan_by_key_simple"]
+    for kd in (np.int8, np.int32, np.uint64, np.float32):
+        k, v = np.array(s["keys"], dtype=kd), np.array(s["values"], dtype=np.int32)
+        assert port.scan_by_key(k, v).tolist() == s["inclusive"]
+        assert port.scan_by_key(k, v, True).tolist() == s["exclusive"]
+        assert port.scan_by_key(k, v, True, 10).tolist() == s["exclusive_init_10"]
     s = KA["reduce_by_key_simple"]
     for dt in (np.int8, np.int32, np.uint64):
         ko, vo = port.reduce_by_key(np.array(s["keys"], dtype=dt), np.array(s["values"], dtype=np.int32))
@@ -84,6 +90,14 @@ def test_reduce_matches_reference_vectors(port, vectors, t):
     a = vectors[f"reduce/{t}/in"]
     assert np.array([port.reduce(a)]).tobytes() == vectors[f"reduce/{t}/sum"].tobytes()
     assert np.array([port.reduce(a, 13)]).tobytes() == vectors[f"reduce/{t}/sum_init13"].tobytes()
+
+
+@pytest.mark.parametrize("t", NUMERIC)
+def test_scan_by_key_matches_reference_vectors(port, vectors, t):
+    k, v = vectors[f"sbk/{t}/keys"], vectors[f"sbk/{t}/vals"]
+    assert port.scan_by_key(k, v).tobytes() == vectors[f"sbk/{t}/inclusive"].tobytes()
+    assert port.scan_by_key(k, v, True).tobytes() == vectors[f"sbk/{t}/exclusive"].tobytes()
+    assert port.scan_by_key(k, v, True, 11).tobytes() == vectors[f"sbk/{t}/exclusive_init11"].tobytes()
 
 
 def test_histogram_matches_reference_vectors(port, vectors):
@@ -143,6 +157,12 @@ def test_port_matches_live_reference(port, system):
             assert x[1].tobytes() == y[1].tobytes()
         else:
             assert np.allclose(x[1], y[1], rtol=1e-4, atol=1e-3)
+        for ex, init in [(False, None), (True, None), (True, 7)]:
+            x, y = port.scan_by_key(keys, a, ex, init), ref.scan_by_key(keys, a, ex, init)
+            if dt.kind != "f" or system == "cpp":
+                assert x.tobytes() == y.tobytes()
+            else:
+                assert np.allclose(x, y, rtol=1e-4, atol=1e-3)
         for init in (None, 7):
             if dt.kind != "f" or system == "cpp":  # the OMP system adds per-thread partial sums
                 assert np.array([port.reduce(a, init)]).tobytes() == np.array([ref.reduce(a, init)]).tobytes()

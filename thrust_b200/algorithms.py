@@ -173,6 +173,58 @@ def reduce(inp: torch.Tensor, init=None, dtype: Optional[int] = None, out: Optio
     return ctype.from_buffer_copy(raw).value
 
 
+def _scan_by_key(keys: torch.Tensor, values: torch.Tensor, out: Optional[torch.Tensor], exclusive: bool, init,
+                 key_dtype: Optional[int], val_dtype: Optional[int], sync: bool,
+                 temp: Optional[torch.Tensor]) -> torch.Tensor:
+    _check_tensor(keys, "keys")
+    _check_tensor(values, "values")
+    n = keys.numel()
+    if values.numel() != n:
+        raise ValueError("keys and values differ in length")
+    kd = tb200_dtype(keys, key_dtype)
+    vd = tb200_dtype(values, val_dtype)
+    if vd not in _NUMERIC:
+        raise TypeError("scan_by_key supports 4- and 8-byte integer, float32 and float64 values")
+    if out is None:
+        out = torch.empty_like(values)
+    _check_tensor(out, "output")
+    if out.numel() != n or out.element_size() != values.element_size():
+        raise ValueError("output must match the values")
+    init_buf = None
+    if exclusive and init is not None:
+        ctype = {capi.I32: C.c_int32, capi.U32: C.c_uint32, capi.I64: C.c_int64, capi.U64: C.c_uint64,
+                 capi.F32: C.c_float, capi.F64: C.c_double}[vd]
+        init_buf = ctype(init)
+    with torch.cuda.device(keys.device):
+        stream = _stream(keys)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_scan_by_key(None, C.byref(need), None, None, None, n, kd, vd, int(exclusive), None,
+                                              stream), "tb200_scan_by_key(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, keys.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_scan_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(values.data_ptr()),
+            C.c_void_p(out.data_ptr()), n, kd, vd, int(exclusive),
+            C.byref(init_buf) if init_buf is not None else None, stream), "tb200_scan_by_key")
+        _finish(temp, stream, "tb200_scan_by_key", sync)
+    return out
+
+
+def inclusive_scan_by_key(keys: torch.Tensor, values: torch.Tensor, out: Optional[torch.Tensor] = None,
+                          key_dtype: Optional[int] = None, val_dtype: Optional[int] = None, sync: bool = True,
+                          temp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """thrust::inclusive_scan_by_key (equal_to, plus); ``out`` may be ``values``."""
+    return _scan_by_key(keys, values, out, False, None, key_dtype, val_dtype, sync, temp)
+
+
+def exclusive_scan_by_key(keys: torch.Tensor, values: torch.Tensor, out: Optional[torch.Tensor] = None, init=None,
+                          key_dtype: Optional[int] = None, val_dtype: Optional[int] = None, sync: bool = True,
+                          temp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """thrust::exclusive_scan_by_key (equal_to, plus): every run restarts at ``init`` (default 0)."""
+    return _scan_by_key(keys, values, out, True, init, key_dtype, val_dtype, sync, temp)
+
+
 def reduce_by_key(keys: torch.Tensor, values: torch.Tensor, keys_out: Optional[torch.Tensor] = None,
                   values_out: Optional[torch.Tensor] = None, key_dtype: Optional[int] = None,
                   val_dtype: Optional[int] = None,

@@ -45,7 +45,8 @@ __host__ inline int dtype_bytes(int dt) {
 // tracing on, every kernel launch of the library is followed by an event record, so
 // a benchmark can read per-launch device times without a profiler. Off by default.
 enum TraceKind { kTraceOther = 0, kTraceSortHistogram = 1, kTraceSortPass = 2, kTraceSortCopyBack = 3, kTraceScan = 4,
-                 kTraceReduceByKey = 5, kTraceHistogramSorted = 6, kTracePartitionHistogram = 7, kTracePartitionPass = 8, kTraceReduce = 9 };
+                 kTraceReduceByKey = 5, kTraceHistogramSorted = 6, kTracePartitionHistogram = 7, kTracePartitionPass = 8, kTraceReduce = 9,
+                 kTraceScanByKey = 10 };
 void trace_mark(cudaStream_t stream, int kind = kTraceOther);
 
 #define TB200_CUDA_TRY(expr)                       \
