@@ -2,7 +2,8 @@
 
     python -m thrust_b200.profile_cases <case> [log2_n]
 
-cases: sort_u64_u32, sort_i32, sort_f32_i32, scan_f32, scan_i64, reduce_by_key.
+cases: sort_u64_u32, sort_i32, sort_f32_i32, scan_f32, scan_i64, reduce_by_key, scan_by_key,
+reduce_f32.
 Each case generates its seeded input on the device (larger than L2 from log2_n = 26),
 runs the algorithm a few times through the C ABI and exits; it holds well under a few GB,
 which is what a multi-pass profiler capture needs.
@@ -45,6 +46,15 @@ def run(case: str, log2_n: int = 26, reps: int = 3) -> None:
         k, v = g.rbk_inputs(n, dev)
         for _ in range(reps):
             alg.reduce_by_key(k, v)
+    elif case == "scan_by_key":
+        k, v = g.rbk_inputs(n, dev)
+        out = torch.empty_like(v)
+        for _ in range(reps):
+            alg.inclusive_scan_by_key(k, v, out=out)
+    elif case == "reduce_f32":
+        x = g.scan_f32(n, dev)
+        for _ in range(reps):
+            alg.reduce(x)
     else:
         raise SystemExit(f"unknown case {case!r}")
     torch.cuda.synchronize()
