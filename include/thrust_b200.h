@@ -134,16 +134,21 @@ int tb200_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out, 
  * another component owns the allocator (a framework's caching pool, a fixed arena sized at
  * start-up), latency-critical loops where cudaMalloc's device-wide synchronisation is not
  * acceptable, and processes near their memory limit where a late allocation could fail.
- * The look-back descriptors live in a device array inside the library (about 1 MiB on every
+ * The look-back descriptors live in a device array inside the library (about 2 MiB on every
  * GPU that loads it, held until the process exits), so the caller passes only input and
- * output. Limits: n <= 2^31 elements for 4-byte types, n <= 2^29 for 8-byte types; larger n
- * returns TB200_ERR_OVERFLOW (use tb200_scan). The first call on each device looks up the
+ * output. Limits: n <= 2^31 elements for 4-byte types, n <= 2^29 for 8-byte types (both
+ * inclusive); larger n returns TB200_ERR_OVERFLOW before anything is enqueued (use
+ * tb200_scan). The first call on each device looks up the
  * array's device address; make that first call outside any stream capture. All calls on a
  * device share the one array (each call clears what it needs on `stream` first), so calls
  * that can overlap on the GPU — different streams without ordering — race; keep them
  * stream-ordered. Makes no cudaMalloc / cudaFree and calls no allocating library routine. */
 int tb200_scan_static(const void* d_in, void* d_out, uint64_t n, int dtype, int exclusive,
                       const void* h_init, tb200_stream_t stream);
+/* Device status word of the last tb200_scan_static call on the current device (0 or a
+ * tb200_error such as TB200_ERR_WAIT_TIMEOUT): tb200_temp_status for the library's own array,
+ * which the caller cannot name. Synchronises `stream`. No counterpart in the reference. */
+int tb200_scan_static_status(tb200_stream_t stream);
 
 /* ---- reduce_by_key ------------------------------------------------------------------
  * Runs of consecutive equal keys (thrust::equal_to<Key>) are reduced with plus over the

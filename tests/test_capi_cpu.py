@@ -39,6 +39,14 @@ def test_size_queries_and_argument_errors_need_no_gpu():
     assert capi.lib.tb200_radix_sort(None, None, None, None, 10, capi.I32, 0, 0, 0, 32, None) == capi.ERR_INVALID_ARGUMENT
 
 
+def test_static_scan_refuses_sizes_beyond_its_documented_limits_without_a_gpu():
+    from thrust_b200 import _capi as capi
+    for dtype, limit in ((capi.F32, 1 << 31), (capi.U32, 1 << 31), (capi.I64, 1 << 29), (capi.F64, 1 << 29)):
+        assert capi.lib.tb200_scan_static(None, None, limit + 1, dtype, 0, None, None) == capi.ERR_OVERFLOW
+        # at the limit the size check passes (what comes back is an argument or device error)
+        assert capi.lib.tb200_scan_static(None, None, limit, dtype, 0, None, None) != capi.ERR_OVERFLOW
+
+
 def test_python_front_end_refuses_cpu_tensors():
     import torch
     import thrust_b200 as tb

@@ -1,8 +1,8 @@
 """tb200_scan_static — the scan entry point that allocates nothing (its look-back scratch is a
 fixed array inside the library) — must give exactly what tb200_scan gives, on two calls in a
 row (the second call finds the first call's descriptors in the shared array and has to clear
-them itself). Collected last on purpose: a run that stops at the first failure has then
-already run every other test.
+them itself), and what the CPU oracle gives. Collected last on purpose: a run that stops at the
+first failure has then already run every other test.
 """
 import ctypes as C
 
@@ -10,6 +10,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from thrust_b200 import _capi as capi
 
 pytestmark = pytest.mark.gpu
@@ -23,6 +24,8 @@ def _scan(entry, x: torch.Tensor, dtype: int, exclusive: int, init) -> torch.Ten
         rc = capi.lib.tb200_scan_static(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()), n, dtype, exclusive,
                                         init, stream)
         capi.check(rc, "tb200_scan_static")
+        # the device status word of the library's own array (a bounded wait that ran out would show here)
+        capi.check(capi.lib.tb200_scan_static_status(stream), "tb200_scan_static_status")
     else:
         need = C.c_size_t(0)
         capi.check(capi.lib.tb200_scan(None, C.byref(need), None, None, n, dtype, exclusive, init, stream), "size")
@@ -47,16 +50,24 @@ def test_static_scan_matches_scan_twice_in_a_row(cuda_device):
             x = host.to(cuda_device)
             want = _scan("plain", x, dtype, exclusive, init)
             got = _scan("static", x, dtype, exclusive, init)
+            ini = None if init is None else init._obj.value
+            cpu = torch.from_numpy(oracle.port().scan(host.numpy(), bool(exclusive), ini))
             if dtype in (capi.F32, capi.F64):
                 tol = 1e-5 * float(host.abs().double().sum())
                 assert float((got.double() - want.double()).abs().max()) <= tol, (call, dtype)
+                assert float((got.cpu().double() - cpu.double()).abs().max()) <= tol, (call, dtype)
             else:
                 assert torch.equal(got, want), (call, dtype)
+                assert torch.equal(got.cpu(), cpu), (call, dtype)
 
 
-def test_static_scan_rejects_sizes_beyond_its_scratch(cuda_device):
-    # size check only: nothing is launched for an oversized n
-    too_many = (1 << 31) + (1 << 20)
-    rc = capi.lib.tb200_scan_static(None, None, too_many, capi.I64, 0, None, None)
-    assert rc == capi.ERR_OVERFLOW
+def test_static_scan_limits_are_the_documented_ones(cuda_device):
+    # Size path only: with NULL data pointers nothing is launched. At the documented maximum the
+    # call gets as far as the argument check; one element more is refused as an overflow.
+    for dtype, limit in ((capi.F32, 1 << 31), (capi.I32, 1 << 31), (capi.I64, 1 << 29), (capi.F64, 1 << 29)):
+        assert capi.lib.tb200_scan_static(None, None, limit, dtype, 0, None, None) == capi.ERR_INVALID_ARGUMENT
+        assert capi.lib.tb200_scan_static(None, None, limit + 1, dtype, 0, None, None) == capi.ERR_OVERFLOW
+    assert capi.lib.tb200_scan_static(None, None, (1 << 31) + (1 << 20), capi.I64, 0, None, None) == capi.ERR_OVERFLOW
     assert capi.lib.tb200_scan_static(None, None, 0, capi.I16, 0, None, None) == capi.ERR_UNSUPPORTED
+    torch.cuda.synchronize(cuda_device)
+    assert capi.lib.tb200_scan_static_status(None) == 0

@@ -19,11 +19,8 @@ namespace {
 // 512 threads x 8 vectors = 64 KiB per tile. Large tiles keep the number of tiles
 // per microsecond (about 50 at full HBM speed) well below what the look-back chain
 // can resolve: a warp inspects 64 predecessors per L2 round trip.
-#ifndef TB200_SCAN_THREADS
-#define TB200_SCAN_THREADS 512
-#define TB200_SCAN_MINB 2
-#endif
-constexpr int kScanThreads = TB200_SCAN_THREADS;
+constexpr int kScanThreads = 512;
+constexpr int kScanMinCtas = 2;
 constexpr int kScanWarps = kScanThreads / kWarp;
 constexpr int kScanVecs = 8;  // 16-byte vectors per thread
 
@@ -56,10 +53,7 @@ struct Words {
 // Warp 0 walks back over predecessor descriptors, 32 * kLookSlots at a time (kLookSlots
 // per lane, all loads in flight together), until it meets one that carries a full prefix.
 // Returns the sum of everything before `tile`.
-#ifndef TB200_SCAN_LOOK_SLOTS
-#define TB200_SCAN_LOOK_SLOTS 1
-#endif
-constexpr int kLookSlots = TB200_SCAN_LOOK_SLOTS;
+constexpr int kLookSlots = 1;
 template <typename T>
 __device__ T lookback_sum(const TileWords<Words<T>::W>* tiles, unsigned tile, int* status) {
   constexpr int W = Words<T>::W;
@@ -119,7 +113,7 @@ __device__ T lookback_sum(const TileWords<Words<T>::W>* tiles, unsigned tile, in
 }
 
 template <typename T, bool EXCLUSIVE, bool ALIGNED>
-__global__ void __launch_bounds__(kScanThreads, TB200_SCAN_MINB)
+__global__ void __launch_bounds__(kScanThreads, kScanMinCtas)
 scan_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr,
             TileWords<Words<T>::W>* tiles) {
   constexpr int W = Words<T>::W;
@@ -256,15 +250,12 @@ scan_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr,
 //    data path;
 //  * the compute warps then re-read the parked tile lane-strided, add the prefix and store
 //    it with coalesced 16-byte stores, after which the slot is refilled.
-// Tiles are dealt round-robin at the start and by atomic ticket afterwards, so that tiles in
-// flight are neighbours in the look-back chain and every predecessor of a tile is owned
-// by a CTA that is already running.
+// Every tile, the first ring-full of a CTA included, is drawn from one atomic ticket counter:
+// a tile is only ever owned by a CTA that is already running, so a look-back never waits for a
+// CTA that has not been scheduled (whatever else occupies the GPU), and the tiles in flight
+// are neighbours in the look-back chain.
 // ---------------------------------------------------------------------------------------
-#ifndef TB200_STREAM_THREADS
-#define TB200_STREAM_THREADS 512
-#define TB200_STREAM_MINB 1
-#endif
-constexpr int kStreamThreads = TB200_STREAM_THREADS;  // compute threads; the CTA has one more warp
+constexpr int kStreamThreads = 512;  // compute threads; the CTA has one more warp
 constexpr int kStreamWarps = kStreamThreads / kWarp;
 constexpr int kStreamCta = kStreamThreads + kWarp;
 // Per element size: 16-byte vectors per thread (tile = threads x vectors x 16 B) and the
@@ -280,7 +271,7 @@ template <int ELEM_BYTES> struct StreamShape {
 constexpr unsigned kNoTile = 0xffffffffu;
 
 template <typename T, bool EXCLUSIVE>
-__global__ void __launch_bounds__(kStreamCta, TB200_STREAM_MINB)
+__global__ void __launch_bounds__(kStreamCta, 1)
 scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, TileWords<Words<T>::W>* tiles,
                    unsigned num_tiles) {
   constexpr int W = Words<T>::W;
@@ -306,8 +297,7 @@ scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, Til
   const unsigned lane = lane_id();
   int* status = &hdr->status;
 
-  const unsigned first_dynamic = S * gridDim.x;
-  unsigned pending = 0;  // thread 0: next dynamic tile
+  unsigned pending = 0;  // thread 0: the next tile of this CTA, already drawn
   auto start_load = [&](int slot, unsigned t) {
     s_tile[slot] = t;
     if (t < num_tiles && (uint64_t)(t + 1) * TILE <= n) {
@@ -323,8 +313,12 @@ scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, Til
       mbar_init(&s_resolved[s], 1);
     }
     mbar_init_fence();
-    for (int s = 0; s < S; ++s) start_load(s, s * gridDim.x + blockIdx.x);
-    pending = first_dynamic + atomicAdd(&hdr->ticket, 1u);
+    unsigned first[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) first[s] = atomicAdd(&hdr->ticket, 1u);
+#pragma unroll
+    for (int s = 0; s < S; ++s) start_load(s, first[s]);
+    pending = atomicAdd(&hdr->ticket, 1u);
   }
   __syncthreads();
 
@@ -340,11 +334,7 @@ scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, Til
       if (tile == 0) {
         prefix = EXCLUSIVE ? init : T(0);
       } else {
-#ifdef TB200_EXPERIMENT_NO_LOOKBACK
-        prefix = T(0);
-#else
         prefix = lookback_sum<T>(tiles, tile, status);
-#endif
       }
       if (lane == 0) {
         unsigned payload[W];
@@ -392,7 +382,7 @@ scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, Til
       named_barrier(1, kStreamThreads);  // the slot has been read by every compute thread
       if (threadIdx.x == 0) {
         start_load(slot, pending);
-        pending = first_dynamic + atomicAdd(&hdr->ticket, 1u);
+        pending = atomicAdd(&hdr->ticket, 1u);
       }
     }
   };
@@ -524,7 +514,6 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
   const T* in = static_cast<const T*>(d_in);
   T* out = static_cast<T*>(d_out);
   const bool aligned = ((reinterpret_cast<uintptr_t>(d_in) | reinterpret_cast<uintptr_t>(d_out)) % 16) == 0;
-#ifndef TB200_SCAN_NO_STREAM
   if (aligned && stream_tiles >= 8) {
     int dev = 0, sms = 0;
     TB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -535,7 +524,7 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
       int per_sm = 0;
       TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kStreamCta, smem));
       if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
-      // all CTAs must be resident at once: the first tiles are dealt statically
+      // one CTA per slot of the GPU: more would only queue behind them
       const uint64_t resident = (uint64_t)sms * per_sm;
       const unsigned grid = (unsigned)(stream_tiles < resident ? stream_tiles : resident);
       kernel<<<grid, kStreamCta, smem, stream>>>(in, out, n, init, hdr, desc, (unsigned)stream_tiles);
@@ -546,7 +535,6 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
     trace_mark(stream, kTraceScan);
     return (int)cudaGetLastError();
   }
-#endif
   const dim3 grid((unsigned)tiles), block(kScanThreads);
   if (exclusive) {
     if (aligned) scan_kernel<T, true, true><<<grid, block, 0, stream>>>(in, out, n, init, hdr, desc);
@@ -588,9 +576,18 @@ namespace tb200 {
 namespace {
 
 // Look-back descriptors of tb200_scan_static. Lives in every GPU that loads this library,
-// from load until the process exits. 1 MiB + header: up to 131072 tiles of a 4-byte type
-// (n <= 2^31 elements) or 65536 tiles of an 8-byte type (n <= 2^29 elements).
-constexpr size_t kStaticScanBytes = kHeaderBytes + (1u << 20);
+// from load until the process exits. The size is whatever the streaming kernel's tiles need
+// at the documented limits (checked below), rounded up to 2 MiB.
+constexpr uint64_t kStaticScanMaxN4 = 1ull << 31;  // 4-byte element types
+constexpr uint64_t kStaticScanMaxN8 = 1ull << 29;  // 8-byte element types
+constexpr size_t kStaticScanBytes = kHeaderBytes + (2u << 20);
+template <int ELEM_BYTES>
+constexpr size_t static_scan_need(uint64_t n) {
+  constexpr uint64_t tile = (uint64_t)kStreamThreads * StreamShape<ELEM_BYTES>::kVecs * (16 / ELEM_BYTES);
+  return kHeaderBytes + (size_t)((n + tile - 1) / tile) * sizeof(TileWords<ELEM_BYTES / 4>);
+}
+static_assert(static_scan_need<4>(kStaticScanMaxN4) <= kStaticScanBytes, "static scratch too small for 2^31 4-byte elements");
+static_assert(static_scan_need<8>(kStaticScanMaxN8) <= kStaticScanBytes, "static scratch too small for 2^29 8-byte elements");
 static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
 
 constexpr int kMaxDevices = 64;
@@ -619,10 +616,14 @@ int static_scan_scratch(void** out) {
 extern "C" int tb200_scan_static(const void* d_in, void* d_out, uint64_t n, int dtype, int exclusive,
                                  const void* h_init, tb200_stream_t stream) {
   using namespace tb200;
+  const int eb = dtype_bytes(dtype);
+  if (eb != 4 && eb != 8) return TB200_ERR_UNSUPPORTED;
+  // the documented limits, checked before anything touches the device
+  if (n > (eb == 4 ? kStaticScanMaxN4 : kStaticScanMaxN8)) return TB200_ERR_OVERFLOW;
   size_t need = 0;
   int rc = tb200_scan(nullptr, &need, nullptr, nullptr, n, dtype, exclusive, h_init, stream);
   if (rc) return rc;
-  if (need > kStaticScanBytes) return TB200_ERR_OVERFLOW;  // n beyond the fixed scratch: use tb200_scan
+  if (need > kStaticScanBytes) return TB200_ERR_OVERFLOW;  // cannot happen inside the limits (static_assert above)
   void* scratch = nullptr;
   rc = static_scan_scratch(&scratch);
   if (rc) return rc;
@@ -630,4 +631,12 @@ extern "C" int tb200_scan_static(const void* d_in, void* d_out, uint64_t n, int 
   // tb200_scan clears the part of the scratch it uses (header and descriptors) on `stream`
   // before the kernel, so what the previous call left behind is never read.
   return tb200_scan(scratch, &have, d_in, d_out, n, dtype, exclusive, h_init, stream);
+}
+
+extern "C" int tb200_scan_static_status(tb200_stream_t stream) {
+  using namespace tb200;
+  void* scratch = nullptr;
+  const int rc = static_scan_scratch(&scratch);
+  if (rc) return rc;
+  return tb200_temp_status(scratch, stream);
 }
