@@ -178,6 +178,32 @@ int tb200_scan_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys, cons
                       void* d_vals_out, uint64_t n, int key_dtype, int val_dtype, int exclusive,
                       const void* h_init, tb200_stream_t stream);
 
+/* ---- unique_by_key / unique ------------------------------------------------------------
+ * Keeps the FIRST (key, value) pair of every run of consecutive equal keys (thrust::equal_to:
+ * integers by bit pattern, floating point with IEEE ==), in input order, and writes the number
+ * of pairs kept to *d_num_out (device, 8-byte aligned). Keys: any dtype code; values: opaque
+ * payloads of val_bytes in {1,2,4,8,16}, or val_bytes == 0 for the keys-only form
+ * (thrust::unique / unique_copy; d_vals_in and d_vals_out ignored). The outputs may be the
+ * inputs themselves (d_keys_out == d_keys_in and d_vals_out == d_vals_in: the in-place forms
+ * thrust::unique_by_key / thrust::unique); no other overlap.
+ * Replaces thrust::cuda_cub::unique_by_key_copy / unique_by_key and the UniqueByKeyAgent
+ * behind them (thrust/system/cuda/detail/unique_by_key.h:190-590, 716-905); semantics of
+ * thrust/system/detail/sequential/unique_by_key.h:38-90. */
+int tb200_unique_by_key(void* d_temp, size_t* temp_bytes, const void* d_keys_in, const void* d_vals_in,
+                        void* d_keys_out, void* d_vals_out, uint64_t* d_num_out, uint64_t n, int key_dtype,
+                        int val_bytes, tb200_stream_t stream);
+
+/* ---- copy of flagged elements (copy_if with a stencil) -----------------------------------
+ * d_out receives, in input order, every element d_in[i] (opaque, elem_bytes in {1,2,4,8,16})
+ * whose flag d_flags[i] (any dtype code) is non-zero; *d_num_out (device, 8-byte aligned)
+ * the number copied. This is thrust::copy_if(first, last, stencil, result,
+ * thrust::identity<Flag>()). Output must not overlap the inputs.
+ * Replaces thrust::cuda_cub::__copy_if::copy_if and its CopyIfAgent
+ * (thrust/system/cuda/detail/copy_if.h:161-570, 699-826); semantics of
+ * thrust/system/detail/sequential/copy_if.h:38-67. */
+int tb200_copy_flagged(void* d_temp, size_t* temp_bytes, const void* d_in, const void* d_flags, void* d_out,
+                       uint64_t* d_num_out, uint64_t n, int elem_bytes, int flag_dtype, tb200_stream_t stream);
+
 /* ---- reduce ---------------------------------------------------------------------------
  * *d_out = init + in[0] + ... + in[n-1] with thrust::plus in the element type (integer sums
  * wrap; dtype: any integer or floating-point code, not BOOL). h_init is a HOST pointer to
@@ -220,7 +246,7 @@ int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream);
  * to kinds[i] (may be NULL) for i < capacity and returns the number of launches (negative:
  * -cudaError_t). kinds: 1 sort histogram, 2 radix pass, 3 sort copy-back, 4 scan,
  * 5 reduce_by_key, 6 histogram of sorted data, 7 partition histogram, 8 partition pass,
- * 9 reduce, 10 scan_by_key. */
+ * 9 reduce, 10 scan_by_key, 11 unique_by_key, 12 copy of flagged elements. */
 int tb200_trace_begin(tb200_stream_t stream);
 int tb200_trace_end(float* ms, int* kinds, int capacity);
 

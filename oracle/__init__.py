@@ -12,6 +12,7 @@ Only tests/, ``__graft_entry__.smoke()`` and bench.py's CPU-baseline legs may im
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 from typing import Optional, Tuple
@@ -32,11 +33,17 @@ def dt_of(a: np.ndarray) -> int:
     return _NP_TO_DT[a.dtype]
 
 
+def reference_tree() -> Path:
+    """Where the reference project is looked for: $REF, else the Makefile's default."""
+    return Path(os.environ.get("REF", "/root/reference"))
+
+
 def build(ref: bool = True) -> None:
     """Compile liboracle.so and, when the reference tree is present, oracle/_ref."""
     subprocess.run(["make", "-s", "-C", str(HERE), "oracle"], check=True)
-    if ref and Path("/root/reference/thrust/version.h").exists():
-        subprocess.run(["make", "-s", "-j2", "-C", str(HERE), "ref"], check=True)
+    tree = reference_tree()
+    if ref and (tree / "thrust" / "version.h").exists():
+        subprocess.run(["make", "-s", "-j2", "-C", str(HERE), "ref", f"REF={tree}"], check=True)
 
 
 class CpuChecker:
@@ -63,6 +70,10 @@ class CpuChecker:
         self._reduce.argtypes, self._reduce.restype = [vp, u64, i32, vp, vp], i32
         self._hist = getattr(self._lib, prefix + "histogram")
         self._hist.argtypes, self._hist.restype = [vp, u64, i32, vp, u32, vp], i32
+        self._ubk = getattr(self._lib, prefix + "unique_by_key")
+        self._ubk.argtypes, self._ubk.restype = [vp, vp, vp, vp, u64, i32, i32], C.c_int64
+        self._cpf = getattr(self._lib, prefix + "copy_flagged")
+        self._cpf.argtypes, self._cpf.restype = [vp, vp, vp, u64, i32, i32], C.c_int64
         self.threads = 1
         if prefix == "ref_":
             self._lib.ref_num_threads.restype = i32
@@ -141,6 +152,33 @@ class CpuChecker:
         r = self._rbk(self._p(keys), self._p(vals), self._p(ko), self._p(vo), keys.size, dt_of(keys), dt_of(vals))
         assert r >= 0, r
         return ko[:r].copy(), vo[:r].copy()
+
+    def unique_by_key(self, keys: np.ndarray, vals: Optional[np.ndarray] = None, inplace: bool = False
+                      ) -> Tuple[np.ndarray, Optional[np.ndarray]]:
+        """First (key, value) of every run of equal consecutive keys; vals=None is thrust::unique.
+        inplace=True runs the in-place form on copies of the inputs."""
+        keys = np.ascontiguousarray(keys)
+        vb = 0 if vals is None else vals.dtype.itemsize
+        if inplace:
+            ko = keys.copy()
+            vo = None if vals is None else np.ascontiguousarray(vals).copy()
+            r = self._ubk(self._p(ko), self._p(vo), self._p(ko), self._p(vo), keys.size, dt_of(keys), vb)
+        else:
+            ko = np.empty_like(keys)
+            vo = None if vals is None else np.empty_like(vals)
+            vin = None if vals is None else np.ascontiguousarray(vals)
+            r = self._ubk(self._p(keys), self._p(vin), self._p(ko), self._p(vo), keys.size, dt_of(keys), vb)
+        assert r >= 0, r
+        return ko[:r].copy(), (None if vo is None else vo[:r].copy())
+
+    def copy_flagged(self, data: np.ndarray, flags: np.ndarray) -> np.ndarray:
+        """thrust::copy_if(data, stencil=flags, identity): the elements whose flag is non-zero."""
+        data = np.ascontiguousarray(data)
+        flags = np.ascontiguousarray(flags)
+        out = np.empty_like(data)
+        r = self._cpf(self._p(data), self._p(flags), self._p(out), data.size, data.dtype.itemsize, dt_of(flags))
+        assert r >= 0, r
+        return out[:r].copy()
 
     def histogram(self, data: np.ndarray, bin_values: np.ndarray) -> np.ndarray:
         d = np.ascontiguousarray(data).copy()

@@ -18,6 +18,8 @@
  *   reduce_by_key     thrust/system/detail/sequential/reduce_by_key.h:34-96
  *   scan_by_key       thrust/system/detail/sequential/scan_by_key.h:34-146
  *   histogram         examples/histogram.cu:60-101 (+ generic/binary_search.inl:95-133)
+ *   unique_by_key     thrust/system/detail/sequential/unique_by_key.h:38-90
+ *   copy_if (stencil) thrust/system/detail/sequential/copy_if.h:38-67
  */
 #include <stdint.h>
 #include <stddef.h>
@@ -328,4 +330,73 @@ int oracle_histogram(void* data, uint64_t n, int dtype, const void* bin_values, 
   }
   for (uint32_t j = num_bins; j-- > 1;) counts[j] -= counts[j - 1];
   return 0;
+}
+
+/* unique_by_key_copy with equal_to (unique_by_key.h:38-90): the first (key, value) pair of every
+ * run is kept; every later key is compared with the KEPT key of the run (temp_key), not with its
+ * neighbour. Values are opaque (val_bytes 0 = the keys-only form, thrust::unique). The outputs
+ * may be the inputs (the reference's in-place form is this same loop). Returns the pairs kept. */
+#define UBK_BODY(KT)                                                        \
+  do {                                                                      \
+    const KT* k = (const KT*)kin; KT* ko = (KT*)kout;                       \
+    const unsigned char* v = (const unsigned char*)vin;                     \
+    unsigned char* vo = (unsigned char*)vout;                               \
+    unsigned char tv[16];                                                   \
+    if (n == 0) return 0;                                                   \
+    int64_t r = 0; KT tk = k[0];                                            \
+    if (val_bytes) memcpy(tv, v, (size_t)val_bytes);                        \
+    for (uint64_t i = 1; i < n; ++i) {                                      \
+      const KT key = k[i];                                                  \
+      unsigned char val[16];                                                \
+      if (val_bytes) memcpy(val, v + i * (uint64_t)val_bytes, (size_t)val_bytes); \
+      if (!(tk == key)) {                                                   \
+        ko[r] = tk;                                                         \
+        if (val_bytes) memcpy(vo + (uint64_t)r * val_bytes, tv, (size_t)val_bytes); \
+        ++r; tk = key;                                                      \
+        if (val_bytes) memcpy(tv, val, (size_t)val_bytes);                  \
+      }                                                                     \
+    }                                                                       \
+    ko[r] = tk;                                                             \
+    if (val_bytes) memcpy(vo + (uint64_t)r * val_bytes, tv, (size_t)val_bytes); \
+    return r + 1;                                                           \
+  } while (0)
+
+int64_t oracle_unique_by_key(const void* kin, const void* vin, void* kout, void* vout, uint64_t n, int key_dtype,
+                             int val_bytes) {
+  if (val_bytes < 0 || val_bytes > 16) return -1;
+  switch (key_dtype) {
+    case DT_I8: case DT_U8: case DT_BOOL: UBK_BODY(uint8_t);
+    case DT_I16: case DT_U16: UBK_BODY(uint16_t);
+    case DT_I32: case DT_U32: UBK_BODY(uint32_t);
+    case DT_I64: case DT_U64: UBK_BODY(uint64_t);
+    case DT_F32: UBK_BODY(float);     /* IEEE ==: -0.0 equals +0.0, NaN equals nothing */
+    case DT_F64: UBK_BODY(double);
+    default: return -1;
+  }
+}
+
+/* copy_if(first, last, stencil, result, identity) (copy_if.h:38-67): element i is copied when
+ * its stencil value converts to true, i.e. is non-zero. Elements are opaque. Returns the count. */
+#define CPF_BODY(FT)                                                        \
+  do {                                                                      \
+    const FT* f = (const FT*)flags;                                         \
+    const unsigned char* d = (const unsigned char*)in;                      \
+    unsigned char* o = (unsigned char*)out;                                 \
+    int64_t r = 0;                                                          \
+    for (uint64_t i = 0; i < n; ++i)                                        \
+      if (f[i] != (FT)0) { memcpy(o + (uint64_t)r * elem_bytes, d + i * (uint64_t)elem_bytes, (size_t)elem_bytes); ++r; } \
+    return r;                                                               \
+  } while (0)
+
+int64_t oracle_copy_flagged(const void* in, const void* flags, void* out, uint64_t n, int elem_bytes, int flag_dtype) {
+  if (elem_bytes < 1 || elem_bytes > 16) return -1;
+  switch (flag_dtype) {
+    case DT_I8: case DT_U8: case DT_BOOL: CPF_BODY(uint8_t);
+    case DT_I16: case DT_U16: CPF_BODY(uint16_t);
+    case DT_I32: case DT_U32: CPF_BODY(uint32_t);
+    case DT_I64: case DT_U64: CPF_BODY(uint64_t);
+    case DT_F32: CPF_BODY(float);
+    case DT_F64: CPF_BODY(double);
+    default: return -1;
+  }
 }

@@ -13,6 +13,8 @@
 //   scan            thrust/detail/scan.inl:36-111 -> sequential/scan.h:39-116
 //   reduce_by_key   generic/reduce_by_key.inl:67-132 (OMP), sequential/reduce_by_key.h:34-96 (CPP)
 //   histogram       the recipe of examples/histogram.cu:60-101
+//   unique_by_key   thrust/detail/unique.inl -> generic/unique_by_key.inl (OMP), sequential/unique_by_key.h:38-90 (CPP)
+//   copy_if         thrust/detail/copy_if.inl -> generic/copy_if.inl (OMP), sequential/copy_if.h:38-67 (CPP)
 #include <thrust/execution_policy.h>
 #include <thrust/sort.h>
 #include <thrust/scan.h>
@@ -20,6 +22,8 @@
 #include <thrust/binary_search.h>
 #include <thrust/adjacent_difference.h>
 #include <thrust/functional.h>
+#include <thrust/unique.h>
+#include <thrust/copy.h>
 #include <thrust/version.h>
 
 #include <cstdint>
@@ -32,6 +36,53 @@
 enum { DT_I8 = 0, DT_U8, DT_I16, DT_U16, DT_I32, DT_U32, DT_I64, DT_U64, DT_F32, DT_F64, DT_BOOL };
 
 struct v16 { uint64_t a, b; };
+
+template <typename K, typename V>
+static int64_t ubk_kv(const void* kin, const void* vin, void* kout, void* vout, uint64_t n) {
+  const K* k = static_cast<const K*>(kin);
+  const V* v = static_cast<const V*>(vin);
+  K* ko = static_cast<K*>(kout);
+  V* vo = static_cast<V*>(vout);
+  if (kin == kout) {  // the in-place form
+    thrust::pair<K*, V*> e = thrust::unique_by_key(thrust::device, ko, ko + n, vo);
+    return static_cast<int64_t>(e.first - ko);
+  }
+  thrust::pair<K*, V*> e = thrust::unique_by_key_copy(thrust::device, k, k + n, v, ko, vo);
+  return static_cast<int64_t>(e.first - ko);
+}
+template <typename K>
+static int64_t ubk_k(const void* kin, const void* vin, void* kout, void* vout, uint64_t n, int val_bytes) {
+  switch (val_bytes) {
+    case 0: {
+      const K* k = static_cast<const K*>(kin);
+      K* ko = static_cast<K*>(kout);
+      if (kin == kout) return static_cast<int64_t>(thrust::unique(thrust::device, ko, ko + n) - ko);
+      return static_cast<int64_t>(thrust::unique_copy(thrust::device, k, k + n, ko) - ko);
+    }
+    case 1: return ubk_kv<K, uint8_t>(kin, vin, kout, vout, n);
+    case 2: return ubk_kv<K, uint16_t>(kin, vin, kout, vout, n);
+    case 4: return ubk_kv<K, uint32_t>(kin, vin, kout, vout, n);
+    case 8: return ubk_kv<K, uint64_t>(kin, vin, kout, vout, n);
+    default: return -1;
+  }
+}
+template <typename F, typename T>
+static int64_t cpf_ft(const void* in, const void* flags, void* out, uint64_t n) {
+  const T* d = static_cast<const T*>(in);
+  const F* f = static_cast<const F*>(flags);
+  T* o = static_cast<T*>(out);
+  return static_cast<int64_t>(thrust::copy_if(thrust::device, d, d + n, f, o, thrust::identity<F>()) - o);
+}
+template <typename F>
+static int64_t cpf_f(const void* in, const void* flags, void* out, uint64_t n, int elem_bytes) {
+  switch (elem_bytes) {
+    case 1: return cpf_ft<F, uint8_t>(in, flags, out, n);
+    case 2: return cpf_ft<F, uint16_t>(in, flags, out, n);
+    case 4: return cpf_ft<F, uint32_t>(in, flags, out, n);
+    case 8: return cpf_ft<F, uint64_t>(in, flags, out, n);
+    default: return -1;
+  }
+}
 
 template <typename K>
 static int sort_keys(void* keys, uint64_t n, int descending) {
@@ -234,6 +285,18 @@ int64_t ref_reduce_by_key(const void* kin, const void* vin, void* kout, void* vo
     case DT_F64: return rbk_k<double>(kin, vin, kout, vout, n, val_dtype);
     default: return -1;
   }
+}
+
+// thrust::unique_by_key_copy / unique_by_key (in place when kin == kout) / unique_copy / unique
+// (val_bytes == 0) with equal_to. Returns the number of elements kept, or -1.
+int64_t ref_unique_by_key(const void* kin, const void* vin, void* kout, void* vout, uint64_t n, int key_dtype,
+                          int val_bytes) {
+  DISPATCH_KEY(key_dtype, ubk_k<K>(kin, vin, kout, vout, n, val_bytes));
+}
+
+// thrust::copy_if(first, last, stencil, result, thrust::identity<Flag>()). Returns the count, or -1.
+int64_t ref_copy_flagged(const void* in, const void* flags, void* out, uint64_t n, int elem_bytes, int flag_dtype) {
+  DISPATCH_KEY(flag_dtype, cpf_f<K>(in, flags, out, n, elem_bytes));
 }
 
 // Dense histogram by the sort + upper_bound + adjacent_difference recipe

@@ -87,6 +87,20 @@ def main():
         out[f"sbk/{t}/inclusive"] = ref.scan_by_key(keys, vals)
         out[f"sbk/{t}/exclusive"] = ref.scan_by_key(keys, vals, True)
         out[f"sbk/{t}/exclusive_init11"] = ref.scan_by_key(keys, vals, True, 11)
+    # unique_by_key / unique / copy_if with a stencil: drawn after everything above
+    for t in TYPES:
+        dt = np.dtype(t)
+        ids = np.cumsum(rng.random(N) < 0.3)
+        keys = (ids % 2).astype(dt) if dt.itemsize == 1 else ids.astype(dt)
+        vals = rng.integers(0, 1 << 32, size=N, dtype=np.uint32)
+        out[f"ubk/{t}/keys"], out[f"ubk/{t}/vals"] = keys, vals
+        out[f"ubk/{t}/out_keys"], out[f"ubk/{t}/out_vals"] = ref.unique_by_key(keys, vals)
+        ik, iv = ref.unique_by_key(keys, vals, inplace=True)
+        assert ik.tobytes() == out[f"ubk/{t}/out_keys"].tobytes() and iv.tobytes() == out[f"ubk/{t}/out_vals"].tobytes()
+        out[f"ubk/{t}/unique"] = ref.unique_by_key(keys)[0]
+        flags = (rng.random(N) < 0.4).astype(dt)
+        out[f"cpf/{t}/flags"] = flags
+        out[f"cpf/{t}/out"] = ref.copy_flagged(vals, flags)
     np.savez_compressed(Path(__file__).with_name("reference_vectors.npz"), **out)
     print("wrote", len(out), "arrays; reference Thrust version", ref.thrust_version)
 

@@ -57,6 +57,13 @@ def test_known_answers(port):
     for dt in (np.int8, np.int32, np.uint64):
         ko, vo = port.reduce_by_key(np.array(s["keys"], dtype=dt), np.array(s["values"], dtype=np.int32))
         assert ko.tolist() == s["out_keys"] and vo.tolist() == s["out_values"]
+    s = KA["unique_by_key_simple"]
+    for dt in (np.int8, np.int32, np.uint64, np.float32):
+        k, v = np.array(s["keys"], dtype=dt), np.array(s["values"], dtype=np.int32)
+        for inplace in (False, True):
+            ko, vo = port.unique_by_key(k, v, inplace)
+            assert ko.tolist() == s["out_keys"] and vo.tolist() == s["out_values"]
+        assert port.unique_by_key(k)[0].tolist() == s["out_keys"]
     s = KA["dense_histogram_example"]
     data = np.array(s["data"], dtype=np.int32)
     assert port.sort(data).tolist() == s["sorted"]
@@ -98,6 +105,17 @@ def test_scan_by_key_matches_reference_vectors(port, vectors, t):
     assert port.scan_by_key(k, v).tobytes() == vectors[f"sbk/{t}/inclusive"].tobytes()
     assert port.scan_by_key(k, v, True).tobytes() == vectors[f"sbk/{t}/exclusive"].tobytes()
     assert port.scan_by_key(k, v, True, 11).tobytes() == vectors[f"sbk/{t}/exclusive_init11"].tobytes()
+
+
+@pytest.mark.parametrize("t", TYPES)
+def test_unique_by_key_and_copy_flagged_match_reference_vectors(port, vectors, t):
+    k, v = vectors[f"ubk/{t}/keys"], vectors[f"ubk/{t}/vals"]
+    for inplace in (False, True):
+        ko, vo = port.unique_by_key(k, v, inplace)
+        assert ko.tobytes() == vectors[f"ubk/{t}/out_keys"].tobytes()
+        assert vo.tobytes() == vectors[f"ubk/{t}/out_vals"].tobytes()
+    assert port.unique_by_key(k)[0].tobytes() == vectors[f"ubk/{t}/unique"].tobytes()
+    assert port.copy_flagged(v, vectors[f"cpf/{t}/flags"]).tobytes() == vectors[f"cpf/{t}/out"].tobytes()
 
 
 def test_histogram_matches_reference_vectors(port, vectors):
@@ -145,6 +163,20 @@ def test_port_matches_live_reference(port, system):
             assert port.sort(k, desc).tobytes() == ref.sort(k, desc).tobytes()
             a, b = port.sort_by_key(k, v, desc), ref.sort_by_key(k, v, desc)
             assert a[0].tobytes() == b[0].tobytes() and a[1].tobytes() == b[1].tobytes()
+    for t in TYPES:
+        dt = np.dtype(t)
+        n = 20011
+        ids = np.cumsum(rng.random(n) < 0.2)
+        keys = (ids % 2).astype(dt) if dt.itemsize == 1 else ids.astype(dt)
+        for vd in (None, np.uint8, np.uint16, np.uint32, np.uint64):
+            vals = None if vd is None else rng.integers(0, 200, size=n).astype(vd)
+            for inplace in (False, True):
+                x, y = port.unique_by_key(keys, vals, inplace), ref.unique_by_key(keys, vals, inplace)
+                assert x[0].tobytes() == y[0].tobytes()
+                assert vals is None or x[1].tobytes() == y[1].tobytes()
+            if vals is not None:
+                flags = (rng.random(n) < 0.5).astype(dt)
+                assert port.copy_flagged(vals, flags).tobytes() == ref.copy_flagged(vals, flags).tobytes()
     for t in NUMERIC:
         dt = np.dtype(t)
         a = rng.uniform(-1, 1, size=30011).astype(dt) if dt.kind == "f" else rng.integers(0, 1000, size=30011).astype(dt)

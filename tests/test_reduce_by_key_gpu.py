@@ -49,6 +49,21 @@ def test_rbk_integers_bit_exact(cuda_device, n, kdtype):
         assert gv.tobytes() == wv.tobytes()
 
 
+@pytest.mark.parametrize("kdtype,vdtype", [(np.int32, np.int32), (np.uint64, np.int64), (np.int32, np.uint64)])
+def test_rbk_integers_bit_exact_many_tiles_per_cta(cuda_device, kdtype, vdtype):
+    # enough tiles that every persistent CTA refills its ring several times (tickets, slot reuse)
+    n = (1 << 23) + 13
+    rng = np.random.default_rng(n)
+    chk = oracle.port()
+    for p_new in (1 / 16, 0.9, 0.00001):
+        keys = _grouped_keys(rng, n, p_new, kdtype)
+        vals = rng.integers(0, 1 << 31, size=n).astype(vdtype)
+        wk, wv = chk.reduce_by_key(keys, vals)
+        gk, gv = _run(keys, vals)
+        assert gk.shape == wk.shape, p_new
+        assert gk.tobytes() == wk.tobytes() and gv.tobytes() == wv.tobytes(), p_new
+
+
 @pytest.mark.parametrize("n", [0, 1, 4097, 100003, (1 << 22) + 5])
 @pytest.mark.parametrize("vdtype", [np.float32, np.float64])
 def test_rbk_float_values_within_tolerance(cuda_device, n, vdtype):

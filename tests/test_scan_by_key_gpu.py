@@ -55,6 +55,24 @@ def test_scan_by_key_integers_bit_exact(cuda_device, kdtype, vdtype):
             assert to_host(dv, vdtype).tobytes() == chk.scan_by_key(k, v).tobytes(), (n, p)
 
 
+@pytest.mark.parametrize("kdtype,vdtype", [(np.int32, np.int32), (np.uint64, np.int64), (np.uint8, np.uint64)])
+def test_scan_by_key_integers_bit_exact_many_tiles_per_cta(cuda_device, kdtype, vdtype):
+    # enough tiles that every persistent CTA refills its ring several times (tickets, slot reuse)
+    n = (1 << 23) + 13
+    rng = np.random.default_rng(n)
+    chk = oracle.port()
+    for p in (1 / 16, 0.9, 0.00001):
+        k = _keys(rng, n, kdtype, p)
+        ii = np.iinfo(vdtype)
+        v = rng.integers(ii.min, ii.max, size=n, dtype=vdtype, endpoint=True)
+        dk, dv = to_device(k), to_device(v)
+        assert to_host(tb.inclusive_scan_by_key(dk, dv), vdtype).tobytes() == chk.scan_by_key(k, v).tobytes(), p
+        assert to_host(tb.exclusive_scan_by_key(dk, dv, init=7), vdtype).tobytes() == \
+            chk.scan_by_key(k, v, True, 7).tobytes(), p
+        tb.inclusive_scan_by_key(dk, dv, out=dv)
+        assert to_host(dv, vdtype).tobytes() == chk.scan_by_key(k, v).tobytes(), p
+
+
 @pytest.mark.parametrize("vdtype", [np.float32, np.float64])
 def test_scan_by_key_floats_within_tolerance(cuda_device, vdtype):
     chk = oracle.port()

@@ -48,6 +48,20 @@ def test_scan_integers_bit_exact(cuda_device, dtype, n):
     assert to_host(e, dtype).tobytes() == chk.scan(a, True, 3).tobytes()
 
 
+@pytest.mark.parametrize("dtype", [np.int32, np.uint64])
+@pytest.mark.parametrize("n", [(1 << 23) + 13, (1 << 24) + 7])
+def test_scan_integers_bit_exact_many_tiles_per_cta(cuda_device, dtype, n):
+    # enough tiles that every persistent CTA refills its ring several times (tickets, slot reuse)
+    rng = np.random.default_rng(n)
+    a = _data(rng, n, dtype)
+    chk = oracle.port()
+    d = to_device(a)
+    assert to_host(tb.inclusive_scan(d), dtype).tobytes() == chk.scan(a).tobytes()
+    assert to_host(tb.exclusive_scan(d, init=5), dtype).tobytes() == chk.scan(a, True, 5).tobytes()
+    tb.inclusive_scan(d, out=d)
+    assert to_host(d, dtype).tobytes() == chk.scan(a).tobytes()
+
+
 @pytest.mark.parametrize("dtype", FLT_TYPES)
 @pytest.mark.parametrize("n", [0, 1, 5, 4097, 100003, (1 << 22) + 5])
 def test_scan_floats_within_tolerance(cuda_device, dtype, n):

@@ -14,7 +14,7 @@ import importlib
 _ALGORITHMS = (
     "sort", "stable_sort", "sort_by_key", "stable_sort_by_key", "inclusive_scan", "exclusive_scan", "reduce",
     "inclusive_scan_by_key", "exclusive_scan_by_key",
-    "reduce_by_key", "histogram_sorted", "dense_histogram", "tb200_dtype",
+    "reduce_by_key", "unique_by_key", "unique", "copy_flagged", "histogram_sorted", "dense_histogram", "tb200_dtype",
 )
 __all__ = ["Tb200Error", "_capi", "algorithms", "datagen", "sample_sort", *_ALGORITHMS]
 

@@ -47,6 +47,8 @@ def _load() -> C.CDLL:
         "tb200_reduce_by_key": ([vp, psz, vp, vp, vp, vp, vp, u64, i32, i32, vp], i32),
         "tb200_reduce": ([vp, psz, vp, u64, i32, vp, vp, vp], i32),
         "tb200_scan_by_key": ([vp, psz, vp, vp, vp, u64, i32, i32, i32, vp, vp], i32),
+        "tb200_unique_by_key": ([vp, psz, vp, vp, vp, vp, vp, u64, i32, i32, vp], i32),
+        "tb200_copy_flagged": ([vp, psz, vp, vp, vp, vp, u64, i32, i32, vp], i32),
         "tb200_histogram_sorted": ([vp, u64, i32, vp, u32, vp, vp], i32),
         "tb200_temp_status": ([vp, vp], i32),
         "tb200_selftest_wait_timeout": ([u32, vp], i32),
@@ -71,7 +73,7 @@ def _load() -> C.CDLL:
 lib = _load()
 
 EXPORTS = [
-    "tb200_version", "tb200_error_string", "tb200_radix_sort", "tb200_partition", "tb200_partition_count", "tb200_partition_scatter", "tb200_gather_segments", "tb200_radix_sort_begin", "tb200_radix_sort_finish", "tb200_scan", "tb200_scan_static", "tb200_scan_static_status", "tb200_reduce_by_key", "tb200_reduce", "tb200_scan_by_key",
+    "tb200_version", "tb200_error_string", "tb200_radix_sort", "tb200_partition", "tb200_partition_count", "tb200_partition_scatter", "tb200_gather_segments", "tb200_radix_sort_begin", "tb200_radix_sort_finish", "tb200_scan", "tb200_scan_static", "tb200_scan_static_status", "tb200_reduce_by_key", "tb200_reduce", "tb200_scan_by_key", "tb200_unique_by_key", "tb200_copy_flagged",
     "tb200_histogram_sorted", "tb200_temp_status", "tb200_selftest_wait_timeout", "tb200_trace_begin", "tb200_trace_end",
     "tb200_datagen", "tb200_datagen_hash", "tb200_check_hashed_pairs", "tb200_workspace_acquire",
     "tb200_workspace_release_all", "tb200_radix_sort_host", "tb200_scan_host",

@@ -259,6 +259,85 @@ def reduce_by_key(keys: torch.Tensor, values: torch.Tensor, keys_out: Optional[t
         return keys_out, values_out, int(runs.item())
 
 
+def unique_by_key(keys: torch.Tensor, values: Optional[torch.Tensor] = None, keys_out: Optional[torch.Tensor] = None,
+                  values_out: Optional[torch.Tensor] = None, key_dtype: Optional[int] = None, inplace: bool = False,
+                  temp: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor], int]:
+    """thrust::unique_by_key_copy (thrust/unique.h): the first (key, value) of every run of equal
+    consecutive keys. values=None is thrust::unique_copy; inplace=True compacts the inputs
+    themselves (thrust::unique_by_key / thrust::unique). Returns (keys_out, values_out, count);
+    synchronises to read the count like the reference (cuda/detail/unique_by_key.h:789-791)."""
+    _check_tensor(keys, "keys")
+    n = keys.numel()
+    kd = tb200_dtype(keys, key_dtype)
+    vb = 0
+    if values is not None:
+        _check_tensor(values, "values")
+        if values.numel() != n:
+            raise ValueError("keys and values differ in length")
+        vb = values.element_size()
+    if inplace:
+        keys_out, values_out = keys, values
+    else:
+        if keys_out is None:
+            keys_out = torch.empty_like(keys)
+        if values is not None and values_out is None:
+            values_out = torch.empty_like(values)
+    with torch.cuda.device(keys.device):
+        stream = _stream(keys)
+        count = torch.zeros(1, dtype=torch.int64, device=keys.device)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_unique_by_key(None, C.byref(need), None, None, None, None, None, n, kd, vb, stream),
+                   "tb200_unique_by_key(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, keys.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_unique_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()),
+            C.c_void_p(values.data_ptr()) if values is not None else None, C.c_void_p(keys_out.data_ptr()),
+            C.c_void_p(values_out.data_ptr()) if values_out is not None else None, C.c_void_p(count.data_ptr()), n, kd,
+            vb, stream), "tb200_unique_by_key")
+        _finish(temp, stream, "tb200_unique_by_key", True)
+        return keys_out, values_out, int(count.item())
+
+
+def unique(keys: torch.Tensor, out: Optional[torch.Tensor] = None, key_dtype: Optional[int] = None,
+           inplace: bool = False) -> Tuple[torch.Tensor, int]:
+    """thrust::unique_copy / thrust::unique (inplace=True) with equal_to."""
+    k, _, r = unique_by_key(keys, None, out, None, key_dtype, inplace)
+    return k, r
+
+
+def copy_flagged(data: torch.Tensor, flags: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 flag_dtype: Optional[int] = None, temp: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, int]:
+    """thrust::copy_if(first, last, stencil, result, thrust::identity<Flag>()) (thrust/copy.h): the
+    elements whose flag is non-zero, in input order. Returns (out, count); synchronises to read the
+    count like the reference (cuda/detail/copy_if.h:771-773)."""
+    _check_tensor(data, "data")
+    _check_tensor(flags, "flags")
+    n = data.numel()
+    if flags.numel() != n:
+        raise ValueError("data and flags differ in length")
+    fd = tb200_dtype(flags, flag_dtype)
+    if out is None:
+        out = torch.empty_like(data)
+    _check_tensor(out, "out")
+    with torch.cuda.device(data.device):
+        stream = _stream(data)
+        count = torch.zeros(1, dtype=torch.int64, device=data.device)
+        need = C.c_size_t(0)
+        capi.check(capi.lib.tb200_copy_flagged(None, C.byref(need), None, None, None, None, n, data.element_size(), fd,
+                                               stream), "tb200_copy_flagged(size)")
+        if temp is None or temp.numel() < need.value:
+            temp = _temp(need.value, data.device)
+        have = C.c_size_t(temp.numel())
+        capi.check(capi.lib.tb200_copy_flagged(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(data.data_ptr()), C.c_void_p(flags.data_ptr()),
+            C.c_void_p(out.data_ptr()), C.c_void_p(count.data_ptr()), n, data.element_size(), fd, stream),
+            "tb200_copy_flagged")
+        _finish(temp, stream, "tb200_copy_flagged", True)
+        return out, int(count.item())
+
+
 def histogram_sorted(sorted_data: torch.Tensor, bin_values: torch.Tensor, dtype: Optional[int] = None,
                      sync: bool = True) -> torch.Tensor:
     """upper_bound of every bin value in sorted data + adjacent_difference (examples/histogram.cu:84-97)."""

@@ -46,7 +46,7 @@ __host__ inline int dtype_bytes(int dt) {
 // a benchmark can read per-launch device times without a profiler. Off by default.
 enum TraceKind { kTraceOther = 0, kTraceSortHistogram = 1, kTraceSortPass = 2, kTraceSortCopyBack = 3, kTraceScan = 4,
                  kTraceReduceByKey = 5, kTraceHistogramSorted = 6, kTracePartitionHistogram = 7, kTracePartitionPass = 8, kTraceReduce = 9,
-                 kTraceScanByKey = 10 };
+                 kTraceScanByKey = 10, kTraceUniqueByKey = 11, kTraceCopyFlagged = 12 };
 void trace_mark(cudaStream_t stream, int kind = kTraceOther);
 
 #define TB200_CUDA_TRY(expr)                       \
