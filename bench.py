@@ -13,6 +13,9 @@ configurations (int32 sort, float32 / int64 scan, reduce_by_key, (u64,u32) and
 `--impl reference` times the reference's own CPU implementation (Thrust 2.2.0 built
 with its OMP device system, oracle/_ref) on a bounded sample of the same workload.
 
+`--case NAME [--log2-n N]` runs one small single-GPU case a few times and exits: the
+command the profiler captures under profiles/ were taken with (nothing is timed or printed).
+
 Timing: CUDA events on the launching stream, >= 3 warm-up steps, inputs (12 GiB per
 GPU) far larger than L2, input restored by a device copy outside the timed events,
 max over ranks.
@@ -196,15 +199,48 @@ def time_calls(fn, restore, steps: int, warmup: int, stream):
     return out
 
 
+def _sorted_pairs_ok(k0, v0, k, v, kview=None):
+    """Device-side check of a stable sort_by_key whose values were the original indices 0..n-1:
+    keys ascending (in `kview` order: an order-preserving integer view of the keys), every output key
+    is the input key at its value's index (so the output is a permutation of the input), and equal
+    neighbouring keys keep increasing indices (stability)."""
+    import torch
+    n = k.numel()
+    ok = True
+    chunk = 1 << 26
+    for s in range(0, n, chunk):
+        e = min(n, s + chunk + 1)
+        kk = k[s:e] if kview is None else kview(k[s:e])
+        idx = v[s:e].to(torch.int64) & 0xFFFFFFFF
+        ok = ok and bool((kk[1:] >= kk[:-1]).all())
+        ok = ok and bool(((kk[1:] != kk[:-1]) | (idx[1:] > idx[:-1])).all())
+        ok = ok and bool((k0[idx] == k[s:e]).all())
+    return ok
+
+
+def _u64_order(t):
+    """int64 storage of uint64 keys -> int64 values in the same order (flip the sign bit)."""
+    return t ^ (-0x8000000000000000)
+
+
+def _f32_order(t):
+    """float32 keys -> int32 values in the bitwise total order the sort uses."""
+    import torch
+    i = t.view(torch.int32)
+    return torch.where(i < 0, i ^ 0x7FFFFFFF, i)
+
+
 def bench_others(dev, peak):
-    """The remaining single-GPU configurations; each entry carries its own roofline fraction."""
+    """The remaining single-GPU configurations; each entry carries its own roofline fraction and the
+    outcome of a device-side check of the last timed result (`verified`)."""
     import torch
     import thrust_b200 as tb
     from thrust_b200 import _capi as capi, datagen as g
     res = {}
     stream = torch.cuda.current_stream(dev)
 
-    def entry(name, fn, restore, units, unit_name, bytes_model, note, steps=10):
+    def entry(name, fn, restore, units, unit_name, bytes_model, note, verify=None, moved_bytes=None, moved_note=None,
+              steps=10):
         try:
             ms = time_calls(fn, restore, steps, 3, stream)
             best, med = min(ms), statistics.median(ms)
@@ -213,6 +249,13 @@ def bench_others(dev, peak):
                 "algorithmic_GBps": bytes_model / (med * 1e-3) / 1e9,
                 "frac_of_hbm_peak": bytes_model / (med * 1e-3) / 1e9 / peak, "bytes_model": note,
             }
+            if moved_bytes is not None:  # what the kernels really move, beside the model's figure
+                res[name]["moved_GBps"] = moved_bytes / (med * 1e-3) / 1e9
+                res[name]["moved_frac_of_hbm_peak"] = moved_bytes / (med * 1e-3) / 1e9 / peak
+                res[name]["moved_bytes_model"] = moved_note
+            if verify is not None:
+                torch.cuda.synchronize(dev)
+                res[name]["verified"] = bool(verify())
         except Exception as e:  # keep the headline even if a side configuration fails
             res[name] = {"error": repr(e)}
         torch.cuda.empty_cache()
@@ -222,8 +265,14 @@ def bench_others(dev, peak):
     k0 = g.sort_i32(n, dev)
     k = k0.clone()
     temp = torch.empty(n * 4 + (64 << 20), dtype=torch.uint8, device=dev)
+
+    def c1_ok():
+        return bool((k[1:] >= k[:-1]).all()) and int(k.sum()) == int(k0.sum()) and \
+            bool((torch.bincount((k & 0xFFFF).to(torch.int64), minlength=1 << 16) ==
+                  torch.bincount((k0 & 0xFFFF).to(torch.int64), minlength=1 << 16)).all())
     entry("sort_i32_2^25", lambda: tb.sort(k, sync=False, temp=temp), lambda: k.copy_(k0), n, "Gkeys/s", 48.0 * n,
-          "4 passes x (2 reads + 1 write) x 4 B = 48 B/key")
+          "4 passes x (2 reads + 1 write) x 4 B = 48 B/key", verify=c1_ok, moved_bytes=36.0 * n,
+          moved_note="one histogram read + 4 passes x (1 read + 1 write) x 4 B = 36 B/key")
     del k, k0, temp
 
     # C2: scans over 2^30 elements
@@ -231,8 +280,21 @@ def bench_others(dev, peak):
     x = g.scan_f32(n, dev)
     y = torch.empty_like(x)
     temp = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+
+    def scan_ok(exact):
+        # prefix sums at a few positions against float64 / int64 sums of the input
+        ok = True
+        for pos in (0, 1, 10239, 10240, 123456789, n // 2 + 7, n - 1):
+            want = x[:pos + 1].sum(dtype=torch.int64 if exact else torch.float64)
+            got = y[pos]
+            if exact:
+                ok = ok and int(got) == int(want)
+            else:
+                tol = 1e-5 * float(x[:pos + 1].abs().sum(dtype=torch.float64)) + 1e-6
+                ok = ok and abs(float(got) - float(want)) <= tol
+        return ok
     entry("inclusive_scan_f32_2^30", lambda: tb.inclusive_scan(x, out=y, sync=False, temp=temp), lambda: None,
-          n, "Gelem/s", 8.0 * n, "1 read + 1 write x 4 B = 8 B/element")
+          n, "Gelem/s", 8.0 * n, "1 read + 1 write x 4 B = 8 B/element", verify=lambda: scan_ok(False))
     # next row of the path: thrust::reduce over the same 2^30 floats (one read)
     red_out = torch.empty(16, dtype=torch.uint8, device=dev)
     red_have = C.c_size_t(temp.numel())
@@ -241,12 +303,17 @@ def bench_others(dev, peak):
     def red():
         capi.check(capi.lib.tb200_reduce(C.c_void_p(temp.data_ptr()), C.byref(red_have), C.c_void_p(x.data_ptr()), n,
                                          capi.F32, None, C.c_void_p(red_out.data_ptr()), red_stream), "tb200_reduce")
-    entry("reduce_f32_2^30", red, lambda: None, n, "Gelem/s", 4.0 * n, "1 read x 4 B = 4 B/element")
+
+    def red_ok():
+        want = float(x.sum(dtype=torch.float64))
+        got = float(red_out[:4].view(torch.float32)[0])
+        return abs(got - want) <= 1e-5 * float(x.abs().sum(dtype=torch.float64))
+    entry("reduce_f32_2^30", red, lambda: None, n, "Gelem/s", 4.0 * n, "1 read x 4 B = 4 B/element", verify=red_ok)
     del x, y
     x = g.scan_i64(n, dev)
     y = torch.empty_like(x)
     entry("inclusive_scan_i64_2^30", lambda: tb.inclusive_scan(x, out=y, sync=False, temp=temp), lambda: None,
-          n, "Gelem/s", 16.0 * n, "1 read + 1 write x 8 B = 16 B/element")
+          n, "Gelem/s", 16.0 * n, "1 read + 1 write x 8 B = 16 B/element", verify=lambda: scan_ok(True))
     del x, y
 
     # C2: reduce_by_key over 2^28 grouped keys, mean run 16
@@ -264,8 +331,22 @@ def bench_others(dev, peak):
             st), "tb200_reduce_by_key")
     rbk()
     nruns = int(runs.item())
+    # keys are run ids 0..runs-1 (already grouped): per-run sums in float64 are one index_add away
+    run_of = keys.to(torch.int64)
+
+    def seg_sums(v):
+        out = torch.zeros(int(run_of[-1]) + 1, dtype=torch.float64, device=dev)
+        for s in range(0, n, 1 << 26):
+            out.index_add_(0, run_of[s:s + (1 << 26)], v[s:s + (1 << 26)].to(torch.float64))
+        return out
+
+    def rbk_ok():
+        want, wabs = seg_sums(vals), seg_sums(vals.abs())
+        r = int(runs.item())
+        return r == want.numel() and bool((ko[:r] == torch.arange(r, dtype=torch.int32, device=dev)).all()) and \
+            bool(((vo[:r].to(torch.float64) - want).abs() <= 1e-5 * wabs + 1e-30).all())
     entry("reduce_by_key_i32_f32_2^28", rbk, lambda: None, n, "Gelem/s", 8.0 * (n + nruns),
-          f"(n + runs) x (4 B key + 4 B value), runs = {nruns}")
+          f"(n + runs) x (4 B key + 4 B value), runs = {nruns}", verify=rbk_ok)
     # next row of the path: inclusive_scan_by_key over the same keys and values
     so = torch.empty_like(vals)
 
@@ -273,9 +354,35 @@ def bench_others(dev, peak):
         capi.check(capi.lib.tb200_scan_by_key(
             C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
             C.c_void_p(so.data_ptr()), n, capi.I32, capi.F32, 0, None, st), "tb200_scan_by_key")
+
+    def sbk_ok():
+        # the last element of every run holds the run's sum; the first holds its own value
+        want, wabs = seg_sums(vals), seg_sums(vals.abs())
+        last = torch.ones(n, dtype=torch.bool, device=dev)
+        last[:-1] = keys[1:] != keys[:-1]
+        first = torch.ones(n, dtype=torch.bool, device=dev)
+        first[1:] = last[:-1]
+        return bool(((so[last].to(torch.float64) - want).abs() <= 1e-5 * wabs + 1e-30).all()) and \
+            bool((so[first] == vals[first]).all())
     entry("inclusive_scan_by_key_i32_f32_2^28", sbk, lambda: None, n, "Gelem/s", 12.0 * n,
-          "4 B key + 4 B value read, 4 B value written = 12 B/element")
-    del keys, vals, ko, vo, so
+          "4 B key + 4 B value read, 4 B value written = 12 B/element", verify=sbk_ok)
+    # next row of the path: unique_by_key_copy over the same keys and values
+    kept = torch.zeros(1, dtype=torch.int64, device=dev)
+
+    def ubk():
+        capi.check(capi.lib.tb200_unique_by_key(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
+            C.c_void_p(ko.data_ptr()), C.c_void_p(vo.data_ptr()), C.c_void_p(kept.data_ptr()), n, capi.I32, 4, st),
+            "tb200_unique_by_key")
+
+    def ubk_ok():
+        first = torch.ones(n, dtype=torch.bool, device=dev)
+        first[1:] = keys[1:] != keys[:-1]
+        r = int(kept.item())
+        return r == int(first.sum()) and bool((ko[:r] == keys[first]).all()) and bool((vo[:r] == vals[first]).all())
+    entry("unique_by_key_i32_f32_2^28", ubk, lambda: None, n, "Gelem/s", 8.0 * (n + nruns),
+          f"(n + kept) x (4 B key + 4 B value), kept = {nruns}", verify=ubk_ok)
+    del keys, vals, ko, vo, so, run_of
 
     # C3: stable sort_by_key of 2^28 (uint64, uint32) pairs
     k0, v0 = g.pairs_u64_u32(n, g.SEED_PAIRS_U64, 0, dev)
@@ -283,7 +390,9 @@ def bench_others(dev, peak):
     temp = torch.empty(n * 12 + (128 << 20), dtype=torch.uint8, device=dev)
     entry("sort_by_key_u64_u32_2^28", lambda: tb.sort_by_key(k, v, key_dtype=capi.U64, sync=False, temp=temp),
           lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 256.0 * n,
-          "8 passes x (3 x 8 B key + 2 x 4 B value) = 256 B/pair")
+          "8 passes x (3 x 8 B key + 2 x 4 B value) = 256 B/pair",
+          verify=lambda: _sorted_pairs_ok(k0, v0, k, v, _u64_order), moved_bytes=200.0 * n,
+          moved_note="one histogram read (8 B) + 8 passes x (1 read + 1 write) x 12 B = 200 B/pair")
     del k, v, k0, v0
 
     # C4: (float32, int32) pairs, low entropy
@@ -291,19 +400,120 @@ def bench_others(dev, peak):
     k, v = k0.clone(), v0.clone()
     entry("sort_by_key_f32_i32_and3_2^28", lambda: tb.sort_by_key(k, v, sync=False, temp=temp),
           lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 80.0 * n,
-          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair")
+          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair",
+          verify=lambda: _sorted_pairs_ok(k0.view(torch.int32), v0, k.view(torch.int32), v, _f32_order_i32),
+          moved_bytes=68.0 * n, moved_note="one histogram read (4 B) + 4 passes x (1 read + 1 write) x 8 B = 68 B/pair")
     del k0, v0
     k0, v0, table = g.zipf_pairs(n, dev)
     entry("sort_by_key_f32_i32_zipf_2^28", lambda: tb.sort_by_key(k, v, sync=False, temp=temp),
           lambda: (k.copy_(k0), v.copy_(v0)), n, "Gkeys/s", 80.0 * n,
-          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair")
+          "4 passes x (3 x 4 B key + 2 x 4 B value) = 80 B/pair",
+          verify=lambda: _sorted_pairs_ok(k0.view(torch.int32), v0, k.view(torch.int32), v, _f32_order_i32),
+          moved_bytes=68.0 * n, moved_note="one histogram read (4 B) + up to 4 passes x (1 read + 1 write) x 8 B = 68 B/pair")
+    counts_box = [None]
 
     def hist():
         tb.sort(k, sync=False, temp=temp)
-        tb.histogram_sorted(k, table, sync=False)
+        counts_box[0] = tb.histogram_sorted(k, table, sync=False)
+
+    def hist_ok():
+        # the keys are table[rank]: recover every key's rank by search and count the ranks
+        want = torch.zeros(table.numel(), dtype=torch.int64, device=dev)
+        for s in range(0, n, 1 << 26):
+            want += torch.bincount(torch.searchsorted(table, k0[s:s + (1 << 26)]), minlength=table.numel())
+        got = counts_box[0].to(torch.int64) & 0xFFFFFFFF
+        return bool((got == want).all()) and int(got.sum()) == n
     entry("dense_histogram_zipf_f32_65536_bins_2^28", hist, lambda: k.copy_(k0), n, "Gkeys/s", 48.0 * n,
-          "keys-only sort: 4 passes x 12 B = 48 B/key (search + difference touch < 1 MB)")
+          "keys-only sort: 4 passes x 12 B = 48 B/key (search + difference touch < 1 MB)", verify=hist_ok,
+          moved_bytes=36.0 * n, moved_note="one histogram read + up to 4 passes x (1 read + 1 write) x 4 B = 36 B/key")
     return res
+
+
+def _f32_order_i32(i):
+    """int32 view of float32 keys -> int32 values in the bitwise total order the sort uses."""
+    import torch
+    return torch.where(i < 0, i ^ 0x7FFFFFFF, i)
+
+
+CASES = ("sort_u64_u32", "sort_i32", "sort_f32_i32", "scan_f32", "scan_i64", "reduce_by_key", "scan_by_key",
+         "unique_by_key", "copy_flagged", "reduce_f32", "histogram_f32", "partition_u64_u32")
+
+
+def run_case(case: str, log2_n: int, reps: int = 3) -> None:
+    """One small single-GPU case for a profiler capture: seeded input generated on the device
+    (larger than L2 from log2_n = 26, well under a few GB), the algorithm run `reps` times through
+    the C ABI."""
+    import torch
+    import thrust_b200 as tb
+    from thrust_b200 import _capi as capi, datagen as g
+    n = 1 << log2_n
+    dev = torch.device("cuda:0")
+    if case == "sort_u64_u32":
+        k0, v0 = g.pairs_u64_u32(n, SEED, 0, dev)
+        for _ in range(reps):
+            k, v = k0.clone(), v0.clone()
+            tb.sort_by_key(k, v, key_dtype=capi.U64)
+    elif case == "sort_i32":
+        k0 = g.sort_i32(n, dev)
+        for _ in range(reps):
+            k = k0.clone()
+            tb.sort(k)
+    elif case == "sort_f32_i32":
+        k0, v0 = g.and3_pairs(n, dev)
+        for _ in range(reps):
+            k, v = k0.clone(), v0.clone()
+            tb.sort_by_key(k, v)
+    elif case in ("scan_f32", "scan_i64"):
+        x = g.scan_f32(n, dev) if case == "scan_f32" else g.scan_i64(n, dev)
+        y = torch.empty_like(x)
+        for _ in range(reps):
+            tb.inclusive_scan(x, out=y)
+    elif case in ("reduce_by_key", "scan_by_key", "unique_by_key", "copy_flagged"):
+        k, v = g.rbk_inputs(n, dev)
+        out = torch.empty_like(v)
+        flags = (k & 1).to(torch.uint8)
+        for _ in range(reps):
+            if case == "reduce_by_key":
+                tb.reduce_by_key(k, v)
+            elif case == "scan_by_key":
+                tb.inclusive_scan_by_key(k, v, out=out)
+            elif case == "unique_by_key":
+                tb.unique_by_key(k, v)
+            else:
+                tb.copy_flagged(v, flags, out=out)
+    elif case == "reduce_f32":
+        x = g.scan_f32(n, dev)
+        for _ in range(reps):
+            tb.reduce(x)
+    elif case == "histogram_f32":
+        k0, _, table = g.zipf_pairs(n, dev)
+        for _ in range(reps):
+            tb.dense_histogram(k0, table)
+    elif case == "partition_u64_u32":
+        from thrust_b200 import sample_sort as ss
+        k0, v0 = g.pairs_u64_u32(n, SEED, 0, dev)
+        ops = ss.DeviceOps(dev, n)
+        splitters = (torch.arange(1, 8, dtype=torch.int64, device=dev) << 61)
+        ok, ov = torch.empty_like(k0), torch.empty_like(v0)
+        for _ in range(reps):
+            ops.partition(k0, v0, n, splitters, ok, ov)
+    else:
+        raise SystemExit(f"unknown case {case!r}; one of {', '.join(CASES)}")
+    torch.cuda.synchronize()
+    print("done", case, n)
+
+
+def cpp_policy_timing():
+    """Times thrust::sort(thrust_b200::par, ...) on 2^25 int32 keys from the C++ side (pool lease,
+    launches, status read-back included): tests/cpp/bin/bench_system prints one JSON object."""
+    exe = ROOT / "tests" / "cpp" / "bin" / "bench_system"
+    if not exe.exists():
+        return None
+    try:
+        r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+        return json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 else {"error": r.stderr[-300:]}
+    except Exception as e:
+        return {"error": repr(e)}
 
 
 def main():
@@ -318,7 +528,12 @@ def main():
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer", "nccl"],
                     help="exchange step of the sharded sort at --gpus > 1 (default: push over NVLink)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--case", default=None, help=f"run one small case for a profiler and exit: {', '.join(CASES)}")
+    ap.add_argument("--log2-n", type=int, default=26, help="size of --case (default 2^26 elements)")
     args = ap.parse_args()
+    if args.case is not None:
+        run_case(args.case, args.log2_n)
+        return
     args.warmup = max(args.warmup, 3)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -438,6 +653,9 @@ def main():
             line["cpu_baseline"], _ = cpu_sort_sample(25, 3, 1)
         if not args.no_others:
             line["others"] = bench_others(dev, peak)
+            cpp = cpp_policy_timing()
+            if cpp is not None:
+                line["others"]["thrust_sort_through_policy_i32_2^25"] = cpp
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -15,7 +15,7 @@
  *    word in d_temp, read back with tb200_temp_status() after the stream is idle.
  *  - Return value: 0 = success, > 0 = a cudaError_t, < 0 = one of tb200_error.
  *  - Re-entrant: no global mutable state except the optional workspace pool
- *    (mutex protected). Calls that share d_temp must be stream-ordered.
+ *    (mutex protected, leases per call). Calls that share d_temp must be stream-ordered.
  */
 #ifndef THRUST_B200_H_
 #define THRUST_B200_H_
@@ -252,12 +252,17 @@ int tb200_trace_end(float* ms, int* kinds, int capacity);
 
 /* ---- workspace pool -----------------------------------------------------------------
  * The reference allocates and frees scratch with cudaMalloc/cudaFree inside every call
- * (thrust/system/cuda/detail/malloc_and_free.h:53-118). The pool keeps one grow-only
- * buffer per (device, stream) so steady-state calls allocate nothing.
- * tb200_workspace_acquire returns a device buffer of at least `bytes`; it stays owned by
- * the pool and is valid until the next acquire on the same (device, stream) or
- * tb200_workspace_release_all(). */
+ * (thrust/system/cuda/detail/malloc_and_free.h:53-118). The pool keeps device blocks per
+ * (device, stream) and LEASES them per call, so steady-state calls allocate nothing and calls
+ * from several host threads, on one stream or on many, never share a block.
+ * tb200_workspace_acquire leases a block of at least `bytes`; tb200_workspace_release gives it
+ * back once the caller has ENQUEUED its last use (the block is only handed to later work on the
+ * same stream, which runs after it). tb200_workspace_stats reports how many device allocations
+ * the pool has made since the library was loaded and how many bytes it holds;
+ * tb200_workspace_release_all frees everything (no lease may be outstanding). */
 int tb200_workspace_acquire(size_t bytes, tb200_stream_t stream, void** d_ptr);
+int tb200_workspace_release(void* d_ptr);
+int tb200_workspace_stats(uint64_t* device_allocations, uint64_t* bytes_held);
 int tb200_workspace_release_all(void);
 
 /* ---- host-buffer forms --------------------------------------------------------------

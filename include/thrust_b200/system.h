@@ -1,13 +1,15 @@
 // thrust_b200::system — a Thrust custom system (in the style of the reference's
 // examples/minimal_custom_backend.cu:17-37) that routes sort / stable_sort /
 // sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / inclusive_scan_by_key /
-// exclusive_scan_by_key / reduce / reduce_by_key
+// exclusive_scan_by_key / reduce / reduce_by_key / unique / unique_copy / unique_by_key /
+// unique_by_key_copy / copy_if (stencil form)
 // on contiguous arithmetic data to the sm_100a kernels behind the C ABI of
 // thrust_b200.h, and everything else to the CUDA system it derives from.
 //
 //   thrust::sort(thrust_b200::par, v.begin(), v.end());
 //   thrust::inclusive_scan(thrust_b200::par.on(stream), in, in + n, out);
 //   thrust::reduce_by_key(thrust_b200::par_nosync.on(stream), ...);   // still syncs for the count
+//   thrust::sort(thrust_b200::par(my_allocator).on(stream), ...);      // scratch from the caller's allocator
 //
 // The thrust:: signatures and the execution-policy API are untouched: dispatch reaches
 // the overloads below by ADL on the policy type (thrust/detail/sort.inl:30-38,
@@ -33,16 +35,20 @@
 #include <thrust/reduce.h>
 #include <thrust/scan.h>
 #include <thrust/sort.h>
+#include <thrust/copy.h>
+#include <thrust/unique.h>
 #include <thrust/system/cuda/error.h>
 #include <thrust/system/cuda/execution_policy.h>
 #include <thrust/system/system_error.h>
 #include <thrust/type_traits/is_contiguous_iterator.h>
 
 #include <atomic>
+#include <cstddef>
 #include <cstdint>
 #include <new>
 #include <string>
 #include <type_traits>
+#include <utility>
 
 #include "../thrust_b200.h"
 
@@ -53,11 +59,36 @@ namespace thrust_b200 {
 struct system : thrust::device_execution_policy<system> {
   cudaStream_t stream = nullptr;  // legacy default stream, like thrust::cuda::par
   bool sync = true;               // false: par_nosync semantics (cuda/detail/par.h:100-107)
+  // Scratch allocator attached with par(alloc) (thrust/detail/allocator_aware_execution_policy.h:41-96,
+  // examples/cuda/custom_temporary_allocation.cu), type-erased so that one policy type serves every
+  // overload below. Null: scratch is leased from the library's workspace pool.
+  void* alloc_ctx = nullptr;
+  void* (*alloc_fn)(void* ctx, std::size_t bytes) = nullptr;
+  void (*free_fn)(void* ctx, void* ptr, std::size_t bytes) = nullptr;
 
   constexpr system() = default;
   constexpr system(cudaStream_t s, bool sy) : stream(s), sync(sy) {}
   // par.on(stream), cf. thrust/system/cuda/detail/par.h:45-70
-  system on(cudaStream_t s) const { return system(s, sync); }
+  system on(cudaStream_t s) const { system r = *this; r.stream = s; return r; }
+  // par(alloc): every call made with the returned policy takes its scratch from `alloc`
+  // (allocate(n) / deallocate(p, n) in units of Alloc::value_type, like the reference's
+  // temporary_allocator, thrust/detail/allocator/temporary_allocator.inl:40-74) and returns it
+  // before the call returns. The allocator must outlive the policy object.
+  template <typename Alloc>
+  system operator()(Alloc& alloc) const {
+    using T = typename Alloc::value_type;
+    system r = *this;
+    r.alloc_ctx = &alloc;
+    r.alloc_fn = [](void* ctx, std::size_t bytes) -> void* {
+      auto p = static_cast<Alloc*>(ctx)->allocate((bytes + sizeof(T) - 1) / sizeof(T));
+      return static_cast<void*>(thrust::raw_pointer_cast(p));
+    };
+    r.free_fn = [](void* ctx, void* ptr, std::size_t bytes) {
+      using pointer = decltype(std::declval<Alloc&>().allocate(std::size_t(0)));
+      static_cast<Alloc*>(ctx)->deallocate(pointer(static_cast<T*>(ptr)), (bytes + sizeof(T) - 1) / sizeof(T));
+    };
+    return r;
+  }
 };
 
 inline constexpr system par{};
@@ -78,13 +109,41 @@ inline void throw_on_error(int code, const char* what) {
   throw thrust::system_error(code > 0 ? code : (int)cudaErrorUnknown, thrust::cuda_category(), msg);
 }
 
-inline void* workspace(size_t bytes, cudaStream_t stream) {
-  void* p = nullptr;
-  const int rc = tb200_workspace_acquire(bytes, stream, &p);
-  if (rc == (int)cudaErrorMemoryAllocation) throw std::bad_alloc();  // malloc_and_free.h:77-82
-  throw_on_error(rc, "tb200_workspace_acquire");
-  return p;
-}
+// Scratch of one call: from the policy's allocator if it has one (the reference's
+// temporary_array over the policy, thrust/detail/temporary_array.inl:74-80), else a lease of the
+// library's workspace pool. Given back when the call leaves; a block of the caller's allocator
+// only after the stream has drained, because that allocator may hand it to anyone next.
+class scratch {
+ public:
+  scratch(const system& s, std::size_t bytes) : sys_(s), bytes_(bytes + 256) {
+    if (s.alloc_fn) {
+      raw_ = s.alloc_fn(s.alloc_ctx, bytes_);
+      if (raw_ == nullptr) throw std::bad_alloc();
+    } else {
+      const int rc = tb200_workspace_acquire(bytes_, s.stream, &raw_);
+      if (rc == (int)cudaErrorMemoryAllocation) throw std::bad_alloc();  // malloc_and_free.h:77-82
+      throw_on_error(rc, "tb200_workspace_acquire");
+    }
+  }
+  scratch(const scratch&) = delete;
+  scratch& operator=(const scratch&) = delete;
+  ~scratch() {
+    if (raw_ == nullptr) return;
+    if (sys_.free_fn) {
+      cudaStreamSynchronize(sys_.stream);
+      sys_.free_fn(sys_.alloc_ctx, raw_, bytes_);
+    } else {
+      tb200_workspace_release(raw_);
+    }
+  }
+  // 256-byte aligned, as the C ABI asks of d_temp
+  char* get() const { return reinterpret_cast<char*>((reinterpret_cast<std::uintptr_t>(raw_) + 255) / 256 * 256); }
+
+ private:
+  const system& sys_;
+  void* raw_ = nullptr;
+  std::size_t bytes_;
+};
 
 inline void finish(const system& s, const void* temp, const char* what) {
   if (s.sync) throw_on_error(tb200_temp_status(temp, s.stream), what);
@@ -148,7 +207,8 @@ void sort_pairs(system& s, KeyIt kf, KeyIt kl, ValIt vf, Compare comp, bool has_
   size_t bytes = 0;
   throw_on_error(tb200_radix_sort(nullptr, &bytes, nullptr, nullptr, n, dtype_of<K>(), vb, desc, 0, 8 * (int)sizeof(K),
                                   s.stream), "tb200_radix_sort");
-  void* temp = workspace(bytes, s.stream);
+  scratch ws(s, bytes);
+  void* temp = ws.get();
   throw_on_error(tb200_radix_sort(temp, &bytes, n ? (void*)raw(kf) : nullptr, vptr, n, dtype_of<K>(), vb, desc, 0,
                                   8 * (int)sizeof(K), s.stream), "tb200_radix_sort");
   ++fast_calls();
@@ -226,7 +286,8 @@ OutIt scan_fast(system& s, InIt first, InIt last, OutIt result, bool exclusive, 
   const uint64_t n = (uint64_t)(last - first);
   size_t bytes = 0;
   throw_on_error(tb200_scan(nullptr, &bytes, nullptr, nullptr, n, dtype_of<T>(), exclusive, init, s.stream), "tb200_scan");
-  void* temp = workspace(bytes, s.stream);
+  scratch ws(s, bytes);
+  void* temp = ws.get();
   throw_on_error(tb200_scan(temp, &bytes, n ? (const void*)raw(first) : nullptr, n ? (void*)raw(result) : nullptr, n,
                             dtype_of<T>(), exclusive, init, s.stream), "tb200_scan");
   ++fast_calls();
@@ -287,7 +348,8 @@ OutIt scan_by_key_fast(system& s, KeyIt kf, KeyIt kl, ValIt vf, OutIt result, bo
   size_t bytes = 0;
   throw_on_error(tb200_scan_by_key(nullptr, &bytes, nullptr, nullptr, nullptr, n, dtype_of<K>(), dtype_of<T>(),
                                    exclusive, init, s.stream), "tb200_scan_by_key");
-  void* temp = workspace(bytes, s.stream);
+  scratch ws(s, bytes);
+  void* temp = ws.get();
   throw_on_error(tb200_scan_by_key(temp, &bytes, n ? (const void*)raw(kf) : nullptr,
                                    n ? (const void*)raw(vf) : nullptr, n ? (void*)raw(result) : nullptr, n,
                                    dtype_of<K>(), dtype_of<T>(), exclusive, init, s.stream), "tb200_scan_by_key");
@@ -353,7 +415,8 @@ T reduce_fast(system& s, InIt first, InIt last, T init) {
   size_t bytes = 0;
   throw_on_error(tb200_reduce(nullptr, &bytes, nullptr, n, dtype_of<T>(), nullptr, nullptr, s.stream), "tb200_reduce");
   // the result lives in the first 256 bytes of the workspace, the library's scratch behind it
-  char* ws = static_cast<char*>(workspace(bytes + 256, s.stream));
+  scratch lease(s, bytes + 256);
+  char* ws = lease.get();
   throw_on_error(tb200_reduce(ws + 256, &bytes, n ? (const void*)raw(first) : nullptr, n, dtype_of<T>(), &init, ws,
                               s.stream), "tb200_reduce");
   ++fast_calls();
@@ -399,7 +462,8 @@ thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt 
     detail::throw_on_error(tb200_reduce_by_key(nullptr, &bytes, nullptr, nullptr, nullptr, nullptr, nullptr, n,
                                                detail::dtype_of<K>(), detail::dtype_of<V>(), s.stream),
                            "tb200_reduce_by_key");
-    char* ws = static_cast<char*>(detail::workspace(bytes + 256, s.stream));
+    detail::scratch lease(s, bytes + 256);
+    char* ws = lease.get();
     auto* d_runs = reinterpret_cast<uint64_t*>(ws + ((bytes + 255) / 256) * 256);
     detail::throw_on_error(tb200_reduce_by_key(ws, &bytes, detail::raw(kf), detail::raw(vf), detail::raw(ko),
                                                detail::raw(vo), d_runs, n, detail::dtype_of<K>(),
@@ -423,6 +487,142 @@ thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt 
 template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut>
 thrust::pair<KeyOut, ValOut> reduce_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo) {
   return reduce_by_key(s, kf, kl, vf, ko, vo, thrust::equal_to<detail::value_t<KeyIt>>());
+}
+
+// ---- unique / unique_copy / unique_by_key / unique_by_key_copy (cuda/detail/unique_by_key.h:716-905,
+// cuda/detail/unique.h) --------------------------------------------------------------------------
+// Fast path: contiguous iterators, arithmetic keys, thrust::equal_to, values that are trivially
+// copyable and 1, 2, 4, 8 or 16 bytes wide; outputs of the inputs' value types. Like the reference
+// the calls synchronise to read the count (unique_by_key.h:789-791).
+namespace detail {
+template <typename It> constexpr bool payload_v =
+    contiguous_v<It> && std::is_trivially_copyable<value_t<It>>::value && is_value_size<(int)sizeof(value_t<It>)>::value;
+template <typename KeyIt, typename Pred> constexpr bool unique_keys_fast_v =
+    contiguous_v<KeyIt> && is_plain_arithmetic<value_t<KeyIt>>::value && is_equal_to<Pred, value_t<KeyIt>>::value;
+template <typename A, typename B> constexpr bool same_value_v = std::is_same<value_t<A>, value_t<B>>::value;
+
+inline uint64_t unique_by_key_raw(system& s, const void* kin, const void* vin, void* kout, void* vout, uint64_t n,
+                                  int key_dtype, int val_bytes) {
+  if (n == 0) return 0;
+  size_t bytes = 0;
+  throw_on_error(tb200_unique_by_key(nullptr, &bytes, nullptr, nullptr, nullptr, nullptr, nullptr, n, key_dtype,
+                                     val_bytes, s.stream), "tb200_unique_by_key");
+  scratch lease(s, bytes + 256);
+  char* ws = lease.get();
+  auto* d_kept = reinterpret_cast<uint64_t*>(ws + ((bytes + 255) / 256) * 256);
+  throw_on_error(tb200_unique_by_key(ws, &bytes, kin, vin, kout, vout, d_kept, n, key_dtype, val_bytes, s.stream),
+                 "tb200_unique_by_key");
+  ++fast_calls();
+  uint64_t kept = 0;
+  throw_on_error((int)cudaMemcpyAsync(&kept, d_kept, sizeof(kept), cudaMemcpyDeviceToHost, s.stream), "unique: count");
+  throw_on_error(tb200_temp_status(ws, s.stream), "tb200_unique_by_key");
+  return kept;
+}
+template <typename P, typename T> struct is_identity : std::false_type {};
+template <typename T> struct is_identity<thrust::identity<T>, T> : std::true_type {};
+}  // namespace detail
+
+template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut, typename Pred>
+thrust::pair<KeyOut, ValOut> unique_by_key_copy(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo, Pred pred) {
+  if constexpr (detail::unique_keys_fast_v<KeyIt, Pred> && detail::contiguous_v<KeyOut> &&
+                detail::same_value_v<KeyIt, KeyOut> && detail::payload_v<ValIt> && detail::contiguous_v<ValOut> &&
+                detail::same_value_v<ValIt, ValOut>) {
+    const uint64_t n = (uint64_t)(kl - kf);
+    if (n == 0) return thrust::make_pair(ko, vo);
+    const uint64_t kept = detail::unique_by_key_raw(s, detail::raw(kf), detail::raw(vf), detail::raw(ko), detail::raw(vo), n,
+                                                    detail::dtype_of<detail::value_t<KeyIt>>(),
+                                                    (int)sizeof(detail::value_t<ValIt>));
+    return thrust::make_pair(ko + kept, vo + kept);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::unique_by_key_copy(detail::inherited(s), kf, kl, vf, ko, vo, pred);
+  }
+}
+template <typename KeyIt, typename ValIt, typename KeyOut, typename ValOut>
+thrust::pair<KeyOut, ValOut> unique_by_key_copy(system& s, KeyIt kf, KeyIt kl, ValIt vf, KeyOut ko, ValOut vo) {
+  return unique_by_key_copy(s, kf, kl, vf, ko, vo, thrust::equal_to<detail::value_t<KeyIt>>());  // unique_by_key.h:849-864
+}
+// in place: the outputs are the inputs (unique_by_key.h:871-895)
+template <typename KeyIt, typename ValIt, typename Pred>
+thrust::pair<KeyIt, ValIt> unique_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf, Pred pred) {
+  if constexpr (detail::unique_keys_fast_v<KeyIt, Pred> && detail::payload_v<ValIt>) {
+    return unique_by_key_copy(s, kf, kl, vf, kf, vf, pred);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::unique_by_key(detail::inherited(s), kf, kl, vf, pred);
+  }
+}
+template <typename KeyIt, typename ValIt>
+thrust::pair<KeyIt, ValIt> unique_by_key(system& s, KeyIt kf, KeyIt kl, ValIt vf) {
+  return unique_by_key(s, kf, kl, vf, thrust::equal_to<detail::value_t<KeyIt>>());  // unique_by_key.h:898-909
+}
+template <typename InIt, typename OutIt, typename Pred>
+OutIt unique_copy(system& s, InIt first, InIt last, OutIt result, Pred pred) {
+  if constexpr (detail::unique_keys_fast_v<InIt, Pred> && detail::contiguous_v<OutIt> && detail::same_value_v<InIt, OutIt>) {
+    const uint64_t n = (uint64_t)(last - first);
+    if (n == 0) return result;
+    return result + detail::unique_by_key_raw(s, detail::raw(first), nullptr, detail::raw(result), nullptr, n,
+                                              detail::dtype_of<detail::value_t<InIt>>(), 0);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::unique_copy(detail::inherited(s), first, last, result, pred);
+  }
+}
+template <typename InIt, typename OutIt>
+OutIt unique_copy(system& s, InIt first, InIt last, OutIt result) {
+  return unique_copy(s, first, last, result, thrust::equal_to<detail::value_t<InIt>>());
+}
+template <typename It, typename Pred>
+It unique(system& s, It first, It last, Pred pred) {
+  if constexpr (detail::unique_keys_fast_v<It, Pred>) {
+    return unique_copy(s, first, last, first, pred);
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::unique(detail::inherited(s), first, last, pred);
+  }
+}
+template <typename It>
+It unique(system& s, It first, It last) {
+  return unique(s, first, last, thrust::equal_to<detail::value_t<It>>());
+}
+
+// ---- copy_if (cuda/detail/copy_if.h:776-826) ------------------------------------------------
+// Fast path: the stencil form with thrust::identity<Stencil> as the predicate (an element is
+// copied when its stencil value is non-zero), contiguous iterators, an arithmetic stencil and
+// trivially copyable elements of 1, 2, 4, 8 or 16 bytes. Any other predicate needs device code
+// of the caller's and is forwarded.
+template <typename InIt, typename StencilIt, typename OutIt, typename Pred>
+OutIt copy_if(system& s, InIt first, InIt last, StencilIt stencil, OutIt result, Pred pred) {
+  using F = detail::value_t<StencilIt>;
+  if constexpr (detail::payload_v<InIt> && detail::contiguous_v<OutIt> && detail::same_value_v<InIt, OutIt> &&
+                detail::contiguous_v<StencilIt> && detail::is_plain_arithmetic<F>::value &&
+                detail::is_identity<Pred, F>::value) {
+    const uint64_t n = (uint64_t)(last - first);
+    if (n == 0) return result;
+    size_t bytes = 0;
+    const int eb = (int)sizeof(detail::value_t<InIt>);
+    detail::throw_on_error(tb200_copy_flagged(nullptr, &bytes, nullptr, nullptr, nullptr, nullptr, n, eb,
+                                              detail::dtype_of<F>(), s.stream), "tb200_copy_flagged");
+    detail::scratch lease(s, bytes + 256);
+    char* ws = lease.get();
+    auto* d_kept = reinterpret_cast<uint64_t*>(ws + ((bytes + 255) / 256) * 256);
+    detail::throw_on_error(tb200_copy_flagged(ws, &bytes, detail::raw(first), detail::raw(stencil), detail::raw(result),
+                                              d_kept, n, eb, detail::dtype_of<F>(), s.stream), "tb200_copy_flagged");
+    ++detail::fast_calls();
+    uint64_t kept = 0;
+    detail::throw_on_error((int)cudaMemcpyAsync(&kept, d_kept, sizeof(kept), cudaMemcpyDeviceToHost, s.stream),
+                           "copy_if: count");
+    detail::throw_on_error(tb200_temp_status(ws, s.stream), "tb200_copy_flagged");
+    return result + kept;
+  } else {
+    ++detail::forwarded_calls();
+    return thrust::copy_if(detail::inherited(s), first, last, stencil, result, pred);
+  }
+}
+template <typename InIt, typename OutIt, typename Pred>
+OutIt copy_if(system& s, InIt first, InIt last, OutIt result, Pred pred) {
+  ++detail::forwarded_calls();  // the predicate reads the elements themselves: the caller's device code
+  return thrust::copy_if(detail::inherited(s), first, last, result, pred);
 }
 
 }  // namespace thrust_b200

@@ -1,7 +1,8 @@
-"""Build the C++ boundary test (Thrust custom system over the C ABI) for sm_100a.
+"""Build the C++ boundary test (Thrust custom system over the C ABI) and the small C++ timing
+program of the policy path for sm_100a.
 
-Output: tests/cpp/bin/test_system, linked against thrust_b200/libthrust_b200.so by
-relative rpath. Uses the CUDA toolkit's Thrust headers.
+Output: tests/cpp/bin/test_system and tests/cpp/bin/bench_system, linked against
+thrust_b200/libthrust_b200.so by relative rpath. Uses the CUDA toolkit's Thrust headers.
 """
 import os
 import subprocess
@@ -10,23 +11,28 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-SRC = HERE / "test_system.cu"
-OUT = HERE / "bin" / "test_system"
 LIBDIR = ROOT / "thrust_b200"
+PROGRAMS = ("test_system", "bench_system")
 
 
-def build(force: bool = False) -> Path:
-    deps = [SRC, ROOT / "include" / "thrust_b200" / "system.h", ROOT / "include" / "thrust_b200.h"]
-    if not force and OUT.exists() and OUT.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
-        return OUT
-    OUT.parent.mkdir(exist_ok=True)
+def _build_one(name: str, force: bool) -> Path:
+    src, out = HERE / f"{name}.cu", HERE / "bin" / name
+    deps = [src, ROOT / "include" / "thrust_b200" / "system.h", ROOT / "include" / "thrust_b200.h"]
+    if not force and out.exists() and out.stat().st_mtime >= max(d.stat().st_mtime for d in deps):
+        return out
+    out.parent.mkdir(exist_ok=True)
     cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17",
-           "--extended-lambda", "-ccbin", "/usr/bin/g++", "-I", str(ROOT / "include"), str(SRC), "-o", str(OUT),
+           "--extended-lambda", "-ccbin", "/usr/bin/g++", "-I", str(ROOT / "include"), str(src), "-o", str(out),
            "-L", str(LIBDIR), "-lthrust_b200", "-Xlinker", "-rpath=$ORIGIN/../../../thrust_b200"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed for test_system.cu:\n" + r.stdout + r.stderr)
-    return OUT
+        raise RuntimeError(f"nvcc failed for {src.name}:\n" + r.stdout + r.stderr)
+    return out
+
+
+def build(force: bool = False) -> Path:
+    outs = [_build_one(name, force) for name in PROGRAMS]
+    return outs[0]
 
 
 if __name__ == "__main__":

@@ -12,7 +12,10 @@
 #include <thrust/sequence.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
+#include <map>
+#include <thread>
 #include <numeric>
 #include <cstdlib>
 #include <random>
@@ -196,6 +199,93 @@ void test_rbk_type(size_t n) {
   CHECK(thrust::host_vector<V>(dvo) == hvo);
 }
 
+template <typename K, typename V>
+void test_unique_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "unique %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<K> hk(n);
+  std::mt19937 rng(51 + (unsigned)n);
+  K cur = 0;
+  for (size_t i = 0; i < n; ++i) { if (rng() % 3 == 0) cur = (K)(cur + 1); hk[i] = cur; }
+  thrust::host_vector<V> hv = random_vec<V>(n, 53, 0, 100);
+  thrust::device_vector<K> dk = hk, dko(n);
+  thrust::device_vector<V> dv = hv, dvo(n);
+  thrust::host_vector<K> hko(n);
+  thrust::host_vector<V> hvo(n);
+  const auto f0 = fast();
+  auto de = thrust::unique_by_key_copy(tb::par, dk.begin(), dk.end(), dv.begin(), dko.begin(), dvo.begin());
+  CHECK(fast() == f0 + (n ? 1 : 0));
+  auto he = thrust::unique_by_key_copy(thrust::host, hk.begin(), hk.end(), hv.begin(), hko.begin(), hvo.begin());
+  const size_t kept = he.first - hko.begin();
+  CHECK((size_t)(de.first - dko.begin()) == kept);
+  CHECK((size_t)(de.second - dvo.begin()) == kept);
+  hko.resize(kept); hvo.resize(kept);
+  CHECK(thrust::host_vector<K>(dko.begin(), dko.begin() + kept) == hko);
+  CHECK(thrust::host_vector<V>(dvo.begin(), dvo.begin() + kept) == hvo);
+  // keys only, copying and in place
+  auto ue = thrust::unique_copy(tb::par, dk.begin(), dk.end(), dko.begin());
+  CHECK((size_t)(ue - dko.begin()) == kept);
+  CHECK(thrust::host_vector<K>(dko.begin(), dko.begin() + kept) == hko);
+  thrust::device_vector<K> dk2 = dk;
+  auto ie = thrust::unique(tb::par, dk2.begin(), dk2.end());
+  CHECK((size_t)(ie - dk2.begin()) == kept);
+  CHECK(thrust::host_vector<K>(dk2.begin(), dk2.begin() + kept) == hko);
+  // in place by key
+  auto pe = thrust::unique_by_key(tb::par, dk.begin(), dk.end(), dv.begin());
+  CHECK((size_t)(pe.first - dk.begin()) == kept && (size_t)(pe.second - dv.begin()) == kept);
+  CHECK(thrust::host_vector<K>(dk.begin(), dk.begin() + kept) == hko);
+  CHECK(thrust::host_vector<V>(dv.begin(), dv.begin() + kept) == hvo);
+}
+
+template <typename T, typename F>
+void test_copy_if_type(size_t n) {
+  std::snprintf(g_ctx, sizeof g_ctx, "copy_if %s n=%zu", __PRETTY_FUNCTION__, n);
+  thrust::host_vector<T> h = random_vec<T>(n, 61 + (unsigned)n, 0, 100);
+  thrust::host_vector<F> hs = random_vec<F>(n, 62, 0, 2);
+  thrust::device_vector<T> d = h, dout(n);
+  thrust::device_vector<F> ds = hs;
+  thrust::host_vector<T> hout(n);
+  const auto f0 = fast();
+  auto de = thrust::copy_if(tb::par, d.begin(), d.end(), ds.begin(), dout.begin(), thrust::identity<F>());
+  CHECK(fast() == f0 + (n ? 1 : 0));
+  auto he = thrust::copy_if(thrust::host, h.begin(), h.end(), hs.begin(), hout.begin(), thrust::identity<F>());
+  const size_t kept = he - hout.begin();
+  CHECK((size_t)(de - dout.begin()) == kept);
+  hout.resize(kept);
+  CHECK(thrust::host_vector<T>(dout.begin(), dout.begin() + kept) == hout);
+}
+
+template <typename T> struct is_even_pred {
+  __host__ __device__ bool operator()(const T& x) const { return ((int)x & 1) == 0; }
+};
+
+// A caching allocator in the style of examples/cuda/custom_temporary_allocation.cu: blocks are
+// kept and reused by size; `mallocs` counts the cudaMalloc calls it had to make.
+struct caching_allocator {
+  typedef char value_type;
+  std::multimap<std::ptrdiff_t, char*> free_blocks;
+  std::map<char*, std::ptrdiff_t> live;
+  int mallocs = 0, allocations = 0, deallocations = 0;
+  char* allocate(std::ptrdiff_t bytes) {
+    ++allocations;
+    char* p = nullptr;
+    auto it = free_blocks.lower_bound(bytes);
+    if (it != free_blocks.end()) { p = it->second; bytes = it->first; free_blocks.erase(it); }
+    else { ++mallocs; if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) throw std::bad_alloc(); }
+    live[p] = bytes;
+    return p;
+  }
+  void deallocate(char* p, size_t) {
+    ++deallocations;
+    auto it = live.find(p);
+    free_blocks.insert(std::make_pair(it->second, p));
+    live.erase(it);
+  }
+  ~caching_allocator() {
+    for (auto& b : free_blocks) cudaFree(b.second);
+    for (auto& b : live) cudaFree(b.first);
+  }
+};
+
 int main() {
   // ---- known answers -------------------------------------------------------------------
   {
@@ -269,6 +359,35 @@ int main() {
     for (int i = 0; i < 5; ++i) { CHECK(ko[i] == wk[i]); CHECK(vo[i] == wv[i]); }
   }
 
+  {
+    // testing/unique_by_key.cu:127-207 (basic test and a predicate that is forwarded)
+    const int rk[9] = {11, 11, 21, 20, 21, 21, 21, 37, 37};
+    thrust::device_vector<int> k(rk, rk + 9), v(9);
+    thrust::sequence(v.begin(), v.end());
+    auto e = thrust::unique_by_key(tb::par, k.begin(), k.end(), v.begin());
+    CHECK(e.first - k.begin() == 5 && e.second - v.begin() == 5);
+    const int wk[5] = {11, 21, 20, 21, 37}, wv[5] = {0, 2, 3, 4, 7};
+    for (int i = 0; i < 5; ++i) { CHECK(k[i] == wk[i]); CHECK(v[i] == wv[i]); }
+    thrust::device_vector<int> k2(rk, rk + 9), v2(9), ko(9), vo(9);
+    thrust::sequence(v2.begin(), v2.end());
+    auto e2 = thrust::unique_by_key_copy(tb::par, k2.begin(), k2.end(), v2.begin(), ko.begin(), vo.begin());
+    CHECK(e2.first - ko.begin() == 5 && e2.second - vo.begin() == 5);
+    for (int i = 0; i < 5; ++i) { CHECK(ko[i] == wk[i]); CHECK(vo[i] == wv[i]); }
+    const auto w0 = fwd();
+    auto e3 = thrust::unique_by_key_copy(tb::par, k2.begin(), k2.end(), v2.begin(), ko.begin(), vo.begin(),
+                                         [] __host__ __device__(int a, int b) { return a / 10 == b / 10; });
+    CHECK(fwd() == w0 + 1);
+    CHECK(e3.first - ko.begin() == 3);
+    CHECK(ko[0] == 11 && ko[1] == 21 && ko[2] == 37 && vo[0] == 0 && vo[1] == 2 && vo[2] == 7);
+    // copy_if: a predicate on the stencil other than identity, and the form without a stencil, are forwarded
+    thrust::device_vector<int> out(9);
+    auto c1 = thrust::copy_if(tb::par, v2.begin(), v2.end(), k2.begin(), out.begin(), is_even_pred<int>());
+    CHECK(c1 - out.begin() == 1 && out[0] == 3);
+    auto c2 = thrust::copy_if(tb::par, v2.begin(), v2.end(), out.begin(), is_even_pred<int>());
+    CHECK(c2 - out.begin() == 5 && out[4] == 8);
+    CHECK(fwd() == w0 + 3);
+  }
+
   // ---- device == host over types and sizes ---------------------------------------------------
   for (size_t n : {(size_t)0, (size_t)1, (size_t)33, (size_t)10027, (size_t)300007}) {
     test_sort_type<signed char>(n, -128, 127);
@@ -292,6 +411,13 @@ int main() {
     test_rbk_type<int, unsigned int>(n);
     test_rbk_type<unsigned char, long long>(n);
     test_rbk_type<long long, int>(n);
+    test_unique_type<int, unsigned int>(n);
+    test_unique_type<unsigned char, long long>(n);
+    test_unique_type<long long, short>(n);
+    test_unique_type<float, unsigned char>(n);
+    test_copy_if_type<int, unsigned char>(n);
+    test_copy_if_type<long long, int>(n);
+    test_copy_if_type<short, bool>(n);
   }
 
   // ---- everything else is forwarded to the inherited CUDA path and still correct --------------
@@ -356,6 +482,67 @@ int main() {
     thrust::sort(tb::par.on(s), raw, raw + d.size(), thrust::greater<int>());
     CHECK(thrust::is_sorted(d.begin(), d.end(), thrust::greater<int>()));
     cudaStreamDestroy(s);
+  }
+
+  // ---- scratch: the pool allocates nothing in steady state; par(alloc) uses the caller's allocator
+  {
+    std::snprintf(g_ctx, sizeof g_ctx, "scratch");
+    thrust::device_vector<unsigned long long> k = random_vec<unsigned long long>(200000, 5, 0, 1LL << 40);
+    thrust::device_vector<unsigned> v(200000);
+    thrust::device_vector<int> a = random_vec<int>(200000, 6, -100, 100), b(200000);
+    auto step = [&](tb::system pol) {
+      thrust::sort_by_key(pol, k.begin(), k.end(), v.begin());
+      thrust::inclusive_scan(pol, a.begin(), a.end(), b.begin());
+      (void)thrust::reduce(pol, a.begin(), a.end());
+      (void)thrust::unique_copy(pol, a.begin(), a.end(), b.begin());
+    };
+    step(tb::par);  // warm-up: the pool grows to what these calls need
+    uint64_t allocs0 = 0, allocs1 = 0, held = 0;
+    tb200_workspace_stats(&allocs0, &held);
+    CHECK(held > 0);
+    for (int i = 0; i < 100; ++i) step(tb::par);
+    tb200_workspace_stats(&allocs1, &held);
+    CHECK(allocs1 == allocs0);  // 400 steady-state calls, no device allocation
+
+    caching_allocator alloc;
+    const auto f0 = fast();
+    step(tb::par(alloc));
+    const int warm_mallocs = alloc.mallocs;
+    CHECK(warm_mallocs >= 1 && alloc.allocations == 4 && alloc.deallocations == 4);
+    cudaStream_t s;
+    cudaStreamCreate(&s);
+    for (int i = 0; i < 100; ++i) step(tb::par(alloc).on(s));
+    CHECK(alloc.mallocs == warm_mallocs);  // every later call was served from the allocator's cache
+    CHECK(alloc.allocations == 404 && alloc.deallocations == 404 && alloc.live.empty());
+    CHECK(fast() == f0 + 404);
+    tb200_workspace_stats(&allocs1, &held);
+    CHECK(allocs1 == allocs0);  // the pool was not touched by the allocator-aware calls
+    cudaStreamDestroy(s);
+    CHECK(thrust::is_sorted(k.begin(), k.end()));
+  }
+
+  // ---- two host threads on the default stream: every call holds its own scratch -----------------
+  {
+    std::snprintf(g_ctx, sizeof g_ctx, "threads");
+    std::atomic<int> bad{0};
+    auto worker = [&](unsigned seed, size_t n) {
+      for (int rep = 0; rep < 20; ++rep) {
+        thrust::host_vector<int> h = random_vec<int>(n, seed + (unsigned)rep, -1000000, 1000000);
+        thrust::device_vector<int> d = h;
+        thrust::sort(tb::par, d.begin(), d.end());
+        std::sort(h.begin(), h.end());
+        if (!(thrust::host_vector<int>(d) == h)) ++bad;
+        thrust::device_vector<int> out(n);
+        thrust::inclusive_scan(tb::par, d.begin(), d.end(), out.begin());
+        thrust::host_vector<int> hs(n);
+        std::partial_sum(h.begin(), h.end(), hs.begin());
+        if (!(thrust::host_vector<int>(out) == hs)) ++bad;
+      }
+    };
+    std::thread t1(worker, 100u, (size_t)300007), t2(worker, 200u, (size_t)5000011);  // the second keeps growing the pool
+    t1.join();
+    t2.join();
+    CHECK(bad.load() == 0);
   }
 
   CHECK(cudaGetLastError() == cudaSuccess);

@@ -16,10 +16,14 @@ def _declared(header: Path):
 
 def test_library_exports_every_declared_symbol():
     from thrust_b200 import _capi
-    names = _declared(ROOT / "include" / "thrust_b200.h") + _declared(ROOT / "include" / "thrust_b200_datagen.h")
-    assert len(names) >= 15
+    names = _declared(ROOT / "include" / "thrust_b200.h")
+    assert len(names) >= 25
     for n in names:
         assert hasattr(_capi.lib, n), f"{n} declared in include/ but not exported"
+    assert sorted(names) == sorted(_capi.EXPORTS), "the ctypes binding and the header list different entry points"
+    # the benchmark generators and the checker are test support: their own library, not the product's
+    for n in _declared(ROOT / "thrust_b200" / "datagen" / "datagen.h"):
+        assert not hasattr(_capi.lib, n), f"{n} belongs to libtb200_datagen.so, not to the algorithm library"
     assert _capi.lib.tb200_version() >= 100
     assert b"temporary" in _capi.lib.tb200_error_string(_capi.ERR_TEMP_TOO_SMALL)
 

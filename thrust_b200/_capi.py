@@ -54,10 +54,9 @@ def _load() -> C.CDLL:
         "tb200_selftest_wait_timeout": ([u32, vp], i32),
         "tb200_trace_begin": ([vp], i32),
         "tb200_trace_end": ([C.POINTER(C.c_float), C.POINTER(C.c_int), i32], i32),
-        "tb200_datagen": ([vp, u64, u64, i32, u64, vp, u32, i32, vp], i32),
-        "tb200_datagen_hash": ([u64, u64], u64),
-        "tb200_check_hashed_pairs": ([vp, vp, u64, u64, u64, vp, vp], i32),
         "tb200_workspace_acquire": ([sz, vp, C.POINTER(vp)], i32),
+        "tb200_workspace_release": ([vp], i32),
+        "tb200_workspace_stats": ([C.POINTER(u64), C.POINTER(u64)], i32),
         "tb200_workspace_release_all": ([], i32),
         "tb200_radix_sort_host": ([vp, vp, u64, i32, i32, i32, vp], i32),
         "tb200_scan_host": ([vp, vp, u64, i32, i32, vp, vp], i32),
@@ -75,8 +74,8 @@ lib = _load()
 EXPORTS = [
     "tb200_version", "tb200_error_string", "tb200_radix_sort", "tb200_partition", "tb200_partition_count", "tb200_partition_scatter", "tb200_gather_segments", "tb200_radix_sort_begin", "tb200_radix_sort_finish", "tb200_scan", "tb200_scan_static", "tb200_scan_static_status", "tb200_reduce_by_key", "tb200_reduce", "tb200_scan_by_key", "tb200_unique_by_key", "tb200_copy_flagged",
     "tb200_histogram_sorted", "tb200_temp_status", "tb200_selftest_wait_timeout", "tb200_trace_begin", "tb200_trace_end",
-    "tb200_datagen", "tb200_datagen_hash", "tb200_check_hashed_pairs", "tb200_workspace_acquire",
-    "tb200_workspace_release_all", "tb200_radix_sort_host", "tb200_scan_host",
+    "tb200_workspace_acquire",
+    "tb200_workspace_release", "tb200_workspace_stats", "tb200_workspace_release_all", "tb200_radix_sort_host", "tb200_scan_host",
     "tb200_reduce_by_key_host",
 ]
 

@@ -17,6 +17,9 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libthrust_b200.so"
+# test / benchmark support (seeded inputs, reference-free checker): its own library
+DATAGEN_SRC = PKG / "datagen" / "datagen.cu"
+DATAGEN_LIB = PKG / "datagen" / "libtb200_datagen.so"
 ROOT = PKG.parent
 
 NVCC_FLAGS = [
@@ -34,7 +37,8 @@ def _nvcc() -> str:
 
 
 def _newest_header() -> float:
-    hs = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((ROOT / "include").rglob("*.h"))
+    hs = (list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((ROOT / "include").rglob("*.h")) +
+          list(DATAGEN_SRC.parent.glob("*.h")))
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
@@ -61,9 +65,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         o = OBJ / (s.stem + ".o")
         if force or not o.exists() or o.stat().st_mtime < max(s.stat().st_mtime, hdr_time):
             todo.append(s)
-    if todo:
-        with cf.ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
-            list(ex.map(lambda s: _compile(s, verbose), todo))
+    dg_obj = OBJ / (DATAGEN_SRC.stem + ".o")
+    dg_stale = force or not dg_obj.exists() or dg_obj.stat().st_mtime < max(DATAGEN_SRC.stat().st_mtime, hdr_time)
+    work = todo + ([DATAGEN_SRC] if dg_stale else [])
+    if work:
+        with cf.ThreadPoolExecutor(max_workers=min(len(work), os.cpu_count() or 4)) as ex:
+            list(ex.map(lambda s: _compile(s, verbose), work))
+    if dg_stale or not DATAGEN_LIB.exists():
+        cmd = [_nvcc(), "-shared", "-o", str(DATAGEN_LIB), str(dg_obj), "-ccbin", "/usr/bin/g++", "-lcudart", "-lgomp"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     objs = [OBJ / (s.stem + ".o") for s in srcs]
     if todo or not LIB.exists():
         cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-ccbin", "/usr/bin/g++", "-lcudart", "-lgomp"]

@@ -10,15 +10,29 @@
 namespace tb200 {
 namespace {
 
-struct PoolEntry {
+// Workspace pool: blocks are leased per call. A lease is taken from the free blocks of its
+// (device, stream) — so a block is only ever reused by work that is ordered after its previous
+// use on that stream — and two host threads that share a stream simply hold different blocks.
+struct PoolBlock {
   void* ptr = nullptr;
   size_t bytes = 0;
+  bool leased = false;
+};
+struct PoolKeyed {
+  std::vector<PoolBlock> blocks;
 };
 std::mutex g_pool_mutex;
-std::map<std::pair<int, cudaStream_t>, PoolEntry> g_pool;
+std::map<std::pair<int, cudaStream_t>, PoolKeyed> g_pool;
+std::map<void*, std::pair<int, cudaStream_t>> g_pool_owner;  // leased block -> its (device, stream)
+unsigned long long g_pool_mallocs = 0;  // cudaMalloc calls made by the pool since load
+unsigned long long g_pool_bytes = 0;    // bytes the pool holds now
 
-// Two pool buffers per (device, stream) would alias, so host-buffer forms carve
-// their staging arrays and the algorithm scratch out of ONE acquisition.
+// The host-buffer forms carve their staging arrays and the algorithm scratch out of ONE lease.
+struct Lease {  // returns the block to the pool when the host-buffer call leaves
+  void* ptr = nullptr;
+  ~Lease() { tb200_workspace_release(ptr); }
+};
+
 struct Carver {
   char* base;
   size_t off = 0;
@@ -98,28 +112,63 @@ extern "C" int tb200_temp_status(const void* d_temp, tb200_stream_t stream) {
 extern "C" int tb200_workspace_acquire(size_t bytes, tb200_stream_t stream, void** d_ptr) {
   using namespace tb200;
   if (d_ptr == nullptr) return TB200_ERR_INVALID_ARGUMENT;
+  *d_ptr = nullptr;
   int dev = 0;
   TB200_CUDA_TRY(cudaGetDevice(&dev));
+  const auto key = std::make_pair(dev, (cudaStream_t)stream);
   std::lock_guard<std::mutex> lock(g_pool_mutex);
-  PoolEntry& e = g_pool[std::make_pair(dev, (cudaStream_t)stream)];
-  if (e.bytes < bytes) {
-    if (e.ptr) {
-      // the old buffer may still be in use by work queued on this stream
-      TB200_CUDA_TRY(cudaStreamSynchronize(stream));
-      TB200_CUDA_TRY(cudaFree(e.ptr));
-      e.ptr = nullptr;
-      e.bytes = 0;
+  PoolKeyed& k = g_pool[key];
+  // smallest free block that is large enough
+  PoolBlock* best = nullptr;
+  for (PoolBlock& b : k.blocks)
+    if (!b.leased && b.bytes >= bytes && (best == nullptr || b.bytes < best->bytes)) best = &b;
+  if (best == nullptr) {
+    // none fits: the free blocks of this (device, stream) are all too small, so give them back
+    // first (cudaFree waits for the work that still uses them) and allocate one that fits
+    for (size_t i = 0; i < k.blocks.size();) {
+      if (!k.blocks[i].leased) {
+        TB200_CUDA_TRY(cudaFree(k.blocks[i].ptr));
+        g_pool_bytes -= k.blocks[i].bytes;
+        k.blocks.erase(k.blocks.begin() + (long)i);
+      } else {
+        ++i;
+      }
     }
-    const size_t want = align_up(bytes + bytes / 16, (size_t)2 << 20);
-    cudaError_t err = cudaMalloc(&e.ptr, want);
+    PoolBlock nb;
+    nb.bytes = align_up(bytes + bytes / 16, (size_t)2 << 20);
+    const cudaError_t err = cudaMalloc(&nb.ptr, nb.bytes);
     if (err != cudaSuccess) {
       (void)cudaGetLastError();  // clear the sticky allocation error, as the reference does
-      e.ptr = nullptr;
       return (int)err;
     }
-    e.bytes = want;
+    ++g_pool_mallocs;
+    g_pool_bytes += nb.bytes;
+    k.blocks.push_back(nb);
+    best = &k.blocks.back();
   }
-  *d_ptr = e.ptr;
+  best->leased = true;
+  g_pool_owner[best->ptr] = key;
+  *d_ptr = best->ptr;
+  return TB200_OK;
+}
+
+extern "C" int tb200_workspace_release(void* d_ptr) {
+  using namespace tb200;
+  if (d_ptr == nullptr) return TB200_OK;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  auto owner = g_pool_owner.find(d_ptr);
+  if (owner == g_pool_owner.end()) return TB200_ERR_INVALID_ARGUMENT;
+  for (PoolBlock& b : g_pool[owner->second].blocks)
+    if (b.ptr == d_ptr) b.leased = false;
+  g_pool_owner.erase(owner);
+  return TB200_OK;
+}
+
+extern "C" int tb200_workspace_stats(uint64_t* device_allocations, uint64_t* bytes_held) {
+  using namespace tb200;
+  std::lock_guard<std::mutex> lock(g_pool_mutex);
+  if (device_allocations) *device_allocations = g_pool_mallocs;
+  if (bytes_held) *bytes_held = g_pool_bytes;
   return TB200_OK;
 }
 
@@ -130,13 +179,15 @@ extern "C" int tb200_workspace_release_all(void) {
   int cur = 0;
   cudaGetDevice(&cur);
   for (auto& kv : g_pool) {
-    if (kv.second.ptr) {
+    for (PoolBlock& b : kv.second.blocks) {
       cudaSetDevice(kv.first.first);
-      cudaError_t e = cudaFree(kv.second.ptr);
+      const cudaError_t e = cudaFree(b.ptr);
       if (e != cudaSuccess) rc = (int)e;
     }
   }
   g_pool.clear();
+  g_pool_owner.clear();
+  g_pool_bytes = 0;
   cudaSetDevice(cur);
   return rc;
 }
@@ -154,10 +205,10 @@ extern "C" int tb200_scan_host(const void* h_in, void* h_out, uint64_t n, int dt
   Carver size(nullptr);
   size.take(temp_bytes);
   size.take((size_t)n * eb);
-  void* ws = nullptr;
-  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  Lease lease;
+  rc = tb200_workspace_acquire(size.off, stream, &lease.ptr);
   if (rc) return rc;
-  Carver c(ws);
+  Carver c(lease.ptr);
   void* d_temp = c.take(temp_bytes);
   void* d_data = c.take((size_t)n * eb);
   TB200_CUDA_TRY(cudaMemcpyAsync(d_data, h_in, (size_t)n * eb, cudaMemcpyHostToDevice, stream));
@@ -182,10 +233,10 @@ extern "C" int tb200_radix_sort_host(void* h_keys, void* h_vals, uint64_t n, int
   size.take(temp_bytes);
   size.take((size_t)n * kb);
   size.take((size_t)n * val_bytes);
-  void* ws = nullptr;
-  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  Lease lease;
+  rc = tb200_workspace_acquire(size.off, stream, &lease.ptr);
   if (rc) return rc;
-  Carver c(ws);
+  Carver c(lease.ptr);
   void* d_temp = c.take(temp_bytes);
   void* d_keys = c.take((size_t)n * kb);
   void* d_vals = c.take((size_t)n * val_bytes);
@@ -219,10 +270,10 @@ extern "C" int tb200_reduce_by_key_host(const void* h_keys_in, const void* h_val
   size.take(temp_bytes);
   size.take(256);
   for (int i = 0; i < 2; ++i) { size.take((size_t)n * kb); size.take((size_t)n * vb); }
-  void* ws = nullptr;
-  rc = tb200_workspace_acquire(size.off, stream, &ws);
+  Lease lease;
+  rc = tb200_workspace_acquire(size.off, stream, &lease.ptr);
   if (rc) return rc;
-  Carver c(ws);
+  Carver c(lease.ptr);
   void* d_temp = c.take(temp_bytes);
   auto* d_runs = static_cast<uint64_t*>(c.take(256));
   void* d_kin = c.take((size_t)n * kb);
@@ -266,9 +317,10 @@ __global__ void selftest_wait_kernel(const unsigned* flag, unsigned limit_polls,
 extern "C" int tb200_selftest_wait_timeout(uint32_t limit_polls, tb200_stream_t stream) {
   using namespace tb200;
   if (limit_polls == 0 || limit_polls > (1u << 20)) return TB200_ERR_INVALID_ARGUMENT;
-  void* ws = nullptr;
-  int rc = tb200_workspace_acquire(512, stream, &ws);
+  Lease lease;
+  int rc = tb200_workspace_acquire(512, stream, &lease.ptr);
   if (rc) return rc;
+  void* ws = lease.ptr;
   TB200_CUDA_TRY(cudaMemsetAsync(ws, 0, 512, stream));
   int* status = static_cast<int*>(ws);
   const unsigned* flag = reinterpret_cast<const unsigned*>(static_cast<char*>(ws) + 256);

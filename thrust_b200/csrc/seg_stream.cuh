@@ -567,18 +567,6 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   }
 }
 
-// Opt-in to the kernel's dynamic shared memory, once per instantiation and device.
-template <typename Kernel>
-int prepare(Kernel kernel, int smem_bytes) {
-  static unsigned long long done_mask = 0;  // bit d: device d is prepared (benign race: the call is idempotent)
-  int dev = 0;
-  TB200_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && (done_mask >> dev) & 1ull) return TB200_OK;
-  TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-  if (dev < 64) done_mask |= 1ull << dev;
-  return TB200_OK;
-}
-
 inline int sm_count(int* sms) {
   static int cached[64] = {};
   int dev = 0;
@@ -620,10 +608,17 @@ int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long
   a.hdr = static_cast<TempHeader*>(d_temp);
   a.tiles = reinterpret_cast<TileWords<4>*>(static_cast<char*>(d_temp) + kHeaderBytes);
   auto kernel = stream_kernel<MODE, K, V>;
-  int rc = prepare(kernel, S::kSmem);
-  if (rc) return rc;
+  // opt in to the kernel's dynamic shared memory once per device (this function is one
+  // instantiation per kernel, so the flag below belongs to this kernel alone)
+  static unsigned long long prepared = 0;  // bit d: done on device d (benign race: the call is idempotent)
+  int dev = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 64 || !((prepared >> dev) & 1ull)) {
+    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmem));
+    if (dev < 64) prepared |= 1ull << dev;
+  }
   int sms = 0;
-  rc = sm_count(&sms);
+  const int rc = sm_count(&sms);
   if (rc) return rc;
   const unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
   kernel<<<grid, kCtaThreads, S::kSmem, stream>>>(a);

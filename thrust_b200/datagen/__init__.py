@@ -1,27 +1,45 @@
 """Seeded synthetic inputs of the benchmark configurations (counter-based, so the
 host, the device and every rank produce the same element i for a given seed).
 
-Python front end of ``tb200_datagen`` (include/thrust_b200_datagen.h). Device
-variants return CUDA tensors, host variants fill numpy arrays (or pinned tensors).
+Python front end of ``tb200_datagen`` (datagen.h, built into libtb200_datagen.so next to
+this file: test and benchmark support, separate from the algorithm library, which this module
+does not load). Device variants return CUDA tensors, host variants fill numpy arrays (or pinned
+tensors).
 """
 from __future__ import annotations
 
 import ctypes as C
+from pathlib import Path
 from typing import Optional, Tuple
 
 import numpy as np
 import torch
 
-from . import _capi as capi
+_LIB_PATH = Path(__file__).resolve().parent / "libtb200_datagen.so"
+if not _LIB_PATH.exists():
+    raise ImportError(f"{_LIB_PATH} is missing: build it with `python -m thrust_b200.build`")
+
+
+class _Check:
+    @staticmethod
+    def check(code: int, what: str) -> None:
+        if code != 0:
+            raise RuntimeError(f"{what} failed with code {code}")
+
+
+capi = _Check
 
 BITS_U32, BITS_U64, INDEX_U32, UNIFORM_F32, UNIFORM_I64, HEAD_FLAGS_I32, AND3_F32, ZIPF_RANK_U32 = range(8)
 
-_lib = capi.lib
+_lib = C.CDLL(str(_LIB_PATH))
 _lib.tb200_datagen.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_int, C.c_uint64, C.c_void_p,
                                C.c_uint32, C.c_int, C.c_void_p]
 _lib.tb200_datagen.restype = C.c_int
 _lib.tb200_datagen_hash.argtypes = [C.c_uint64, C.c_uint64]
 _lib.tb200_datagen_hash.restype = C.c_uint64
+_lib.tb200_check_hashed_pairs.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p,
+                                          C.c_void_p]
+_lib.tb200_check_hashed_pairs.restype = C.c_int
 
 # seeds of the benchmark configurations
 SEED_SORT_I32 = 1337
@@ -41,6 +59,17 @@ _KIND_DTYPE = {
 
 def hash64(seed: int, i: int) -> int:
     return int(_lib.tb200_datagen_hash(seed, i))
+
+
+def check_hashed_pairs(keys: torch.Tensor, vals: torch.Tensor, m: int, seed: int, total: int) -> torch.Tensor:
+    """Runs the reference-free checker over the first m (key, value) pairs of one sorted shard; returns
+    the 4 x int64 device tensor documented in datagen.h (violations, bad keys, index sum, count)."""
+    res = torch.zeros(4, dtype=torch.int64, device=keys.device)
+    with torch.cuda.device(keys.device):
+        stream = C.c_void_p(torch.cuda.current_stream(keys.device).cuda_stream)
+        capi.check(_lib.tb200_check_hashed_pairs(C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), m, seed, total,
+                                                 C.c_void_p(res.data_ptr()), stream), "tb200_check_hashed_pairs")
+    return res
 
 
 def _aux(kind: int, lo=None, hi=None, period=None):
@@ -112,9 +141,8 @@ def scan_i64(n: int = 1 << 30, dev="cuda:0") -> torch.Tensor:
 def rbk_inputs(n: int = 1 << 28, dev="cuda:0") -> Tuple[torch.Tensor, torch.Tensor]:
     """Already-grouped int32 keys (run id; run lengths geometric with mean 16) and float32 values
     uniform(-50, 50), seed 11. The run ids are the inclusive scan of the head flags minus one."""
-    from .algorithms import inclusive_scan
     flags = device(HEAD_FLAGS_I32, n, SEED_RBK, dev=dev, period=16)
-    keys = inclusive_scan(flags, out=flags)
+    keys = _cumsum_chunks(flags)
     keys.sub_(1)
     vals = device(UNIFORM_F32, n, SEED_RBK + 1, dev=dev, lo=-50.0, hi=50.0)
     return keys, vals
@@ -138,6 +166,18 @@ def zipf_pairs(n: int = 1 << 28, dev="cuda:0") -> Tuple[torch.Tensor, torch.Tens
     ranks = device(ZIPF_RANK_U32, n, SEED_LOW_ENTROPY + 1, dev=dev, cdf=cdf)
     keys = table[ranks.long()] if n <= (1 << 26) else _gather_chunks(table, ranks)
     return keys, device(INDEX_U32, n, 0, dev=dev), table
+
+
+def _cumsum_chunks(flags: torch.Tensor, chunk: int = 1 << 26) -> torch.Tensor:
+    """In-place inclusive prefix sum of int32 flags with torch (input preparation, not the product path)."""
+    carry = 0
+    for s in range(0, flags.numel(), chunk):
+        part = flags[s:s + chunk]
+        part.cumsum_(0)
+        if carry:
+            part.add_(carry)
+        carry = int(part[-1].item()) if part.numel() else carry
+    return flags
 
 
 def _gather_chunks(table: torch.Tensor, ranks: torch.Tensor, chunk: int = 1 << 26) -> torch.Tensor:

@@ -1,7 +1,8 @@
-// Counter-based input generators, identical on host and device
-// (see include/thrust_b200_datagen.h). Test and benchmark support.
-#include "common.cuh"
-#include "../../include/thrust_b200_datagen.h"
+// Counter-based input generators, identical on host and device (see datagen.h), and the
+// reference-free checker of sorted hashed pairs. Test and benchmark support: built into its own
+// library (libtb200_datagen.so), not into the algorithm library.
+#include "../csrc/common.cuh"
+#include "datagen.h"
 
 namespace tb200 {
 namespace {

@@ -4,12 +4,13 @@
  * and the device produce identical data and a checker can regenerate a key from its
  * global index. These stand in for the reference's own hash-generated benchmark inputs
  * (internal/benchmark/random.h:6-92) with the value distributions of this repository's
- * benchmark configurations. Not part of the algorithm ABI.
+ * benchmark configurations. Not part of the algorithm ABI: these live in libtb200_datagen.so,
+ * which only the tests and bench.py load.
  */
 #ifndef THRUST_B200_DATAGEN_H_
 #define THRUST_B200_DATAGEN_H_
 
-#include "thrust_b200.h"
+#include "../../include/thrust_b200.h"
 
 #ifdef __cplusplus
 extern "C" {

@@ -366,16 +366,9 @@ class ShardedSorter:
     # ---- reference-free verification (needs the CUDA library) ------------------------------
     def verify(self, out_k: torch.Tensor, out_v: torch.Tensor, m: int) -> bool:
         """True when the distributed output is the stable sort of keys hash(seed, g), g in [0, G*n)."""
-        from . import _capi as capi
-        lib = capi.lib
-        lib.tb200_check_hashed_pairs.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64,
-                                                 C.c_void_p, C.c_void_p]
-        lib.tb200_check_hashed_pairs.restype = C.c_int
+        from . import datagen
         total = self.n * self.world
-        res = torch.zeros(4, dtype=torch.int64, device=self.device)
-        stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        capi.check(lib.tb200_check_hashed_pairs(C.c_void_p(out_k.data_ptr()), C.c_void_p(out_v.data_ptr()), m,
-                                                self.seed, total, C.c_void_p(res.data_ptr()), stream), "check")
+        res = datagen.check_hashed_pairs(out_k, out_v, m, self.seed, total)
         edge = torch.zeros(4, dtype=torch.int64, device=self.device)  # first key, first value, last key, last value
         if m > 0:
             edge[0], edge[1] = out_k[0], out_v[0].to(torch.int64) & 0xFFFFFFFF
@@ -393,6 +386,16 @@ class ShardedSorter:
         r4 = [x & 0xFFFFFFFFFFFFFFFF for x in res.cpu().tolist()]
         want_sum = (total * (total - 1) // 2) & 0xFFFFFFFFFFFFFFFF
         return ok and r4[0] == 0 and r4[1] == 0 and r4[2] == want_sum and r4[3] == total
+
+
+class _NoOps:
+    """Stand-in for the per-shard device steps where only ShardedSorter.verify is wanted."""
+
+    def release(self) -> None:
+        pass
+
+    def status(self) -> int:
+        return 0
 
 
 def bench_host_path(n: int, device: torch.device, world: int, rank: int, seed: int, steps: int = 3,
@@ -443,14 +446,17 @@ def bench_host_path(n: int, device: torch.device, world: int, rank: int, seed: i
     t = torch.tensor(times, dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        sorter.release()
     ms = float(t.mean().item())
+    # the last step's result, checked in full: keys AND values must be the stable sort of the hashed
+    # pairs (reference-free checker on the device; at one GPU the host result is copied back for it)
     if world == 1:
-        sorted_ok = bool((hk.numpy().view("uint64")[1:] >= hk.numpy().view("uint64")[:-1]).all())
         capi.lib.tb200_workspace_release_all()
+        checker = ShardedSorter(n, device, 1, 0, seed, ops=_NoOps())
+        verified = checker.verify(hk.to(device), hv.to(device), n)
     else:
-        sorted_ok = True
+        verified = sorter.verify(rk, rv, m)
+        sorter.release()
     return {"value": n * world / (ms * 1e-3) / 1e9, "unit": "Gkeys/s", "h2d_bytes_per_step": n * 12,
             "d2h_bytes_per_step": d2h, "ms_per_step": ms, "steps": steps, "host_memory": "pinned",
             "api": "tb200_radix_sort_host" if world == 1 else "ShardedSorter.sort between pinned-host copies",
-            "sorted": sorted_ok}
+            "verified": bool(verified)}
