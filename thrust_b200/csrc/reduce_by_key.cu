@@ -32,7 +32,7 @@ template <typename V> using SegWords = seg::DescWords<V>;
 template <typename V>
 __device__ __forceinline__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* status,
                                              unsigned long long& out_cnt, V& out_val) {
-  seg::lookback<V>(tiles, tile, status, out_cnt, out_val);
+  seg::lookback_chain<V>(tiles, tile, status, out_cnt, out_val);
 }
 
 template <typename K, typename V, bool ALIGNED>
@@ -191,7 +191,7 @@ int launch_rbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
   constexpr uint64_t STREAM_TILE = seg::tile_elems<K, V>();  // the smaller tile sizes the scratch
   const uint64_t tiles = (n + TILE - 1) / TILE;
   const uint64_t stream_tiles = (n + STREAM_TILE - 1) / STREAM_TILE;
-  const size_t need = kHeaderBytes + (size_t)stream_tiles * sizeof(TileWords<4>);
+  const size_t need = seg::scratch_bytes<K, V>(n);  // tile and block descriptors of the streaming kernel
   if (d_temp == nullptr) {
     *temp_bytes = need;
     return TB200_OK;

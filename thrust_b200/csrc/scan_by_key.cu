@@ -22,7 +22,7 @@ template <typename V> using SegWords = seg::DescWords<V>;
 template <typename V>
 __device__ __forceinline__ void lookback_seg(const TileWords<4>* tiles, unsigned tile, int* status,
                                              unsigned long long& out_cnt, V& out_val) {
-  seg::lookback<V>(tiles, tile, status, out_cnt, out_val);
+  seg::lookback_chain<V>(tiles, tile, status, out_cnt, out_val);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -182,7 +182,7 @@ int launch_sbk(void* d_temp, size_t* temp_bytes, const void* kin, const void* vi
   constexpr uint64_t TILE = (uint64_t)kRbkThreads * kRbkChunks * E;
   const uint64_t tiles = (n + TILE - 1) / TILE;
   const uint64_t stream_tiles = (n + seg::tile_elems<K, V>() - 1) / seg::tile_elems<K, V>();  // the smaller tile sizes the scratch
-  const size_t need = kHeaderBytes + (size_t)stream_tiles * sizeof(TileWords<4>);
+  const size_t need = seg::scratch_bytes<K, V>(n);  // tile and block descriptors of the streaming kernel
   if (d_temp == nullptr) {
     *temp_bytes = need;
     return TB200_OK;

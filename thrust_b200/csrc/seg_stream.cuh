@@ -8,12 +8,31 @@
 //     of a tile per slot, completion signalled on the slot's `full` mbarrier;
 //   * kComputeWarps compute warps, each working on its own 32 x kItems slice of every tile
 //     WITHOUT synchronising with the other compute warps: phase A (head flags, run sums inside
-//     the thread, one segmented warp scan, warp total to shared memory, arrive on the slot's
-//     `scanned` mbarrier) and, kPark tiles later, phase C (wait for the slot's `resolved`
+//     the thread, one segmented warp scan, warp total to shared memory; the LAST warp to get
+//     there combines the warp totals, publishes the tile's aggregate to the other CTAs with
+//     plain stores (nothing to wait for) and arrives on the slot's `scanned` mbarrier) and,
+//     whenever a parked tile's prefix has been resolved, phase C (the slot's `resolved`
 //     mbarrier, read the warp's prefix, emit, arrive on the slot's `freed` mbarrier);
-//   * one look-back warp that, per tile, scans the compute warps' totals, publishes the tile
-//     aggregate, resolves the tile's prefix over the predecessor tiles and hands every compute
-//     warp its own prefix.
+//   * one closer warp: when the CTA holds the LAST tile of a block of 32 tiles, it waits for the
+//     block's 32 aggregates and publishes the block's aggregate. This waiting sits on no other
+//     path: a compute warp that took global round trips would be the last again on the next
+//     tile and its loop would set the CTA's pace, and a look-back warp that did it would hold
+//     back the tiles queued behind it;
+//   * two look-back warps that take the CTA's tiles in turn: resolve the tile's prefix over the
+//     predecessor tiles and hand every compute warp its own prefix. (A tile's aggregate never
+//     waits behind a look-back: a look-back that is waiting for other CTAs' aggregates must not
+//     hold back the aggregate those CTAs are waiting for.)
+// The chain over tiles has two levels. Tiles are grouped in blocks of 32; a tile's prefix is the
+// prefix of its block plus the aggregates of the tiles in front of it inside the block. The
+// closer warp of the CTA that holds a block's last tile combines the block's 32 aggregates into
+// the block's aggregate as soon as they are all published; the block's last tile
+// publishes the block's inclusive prefix once it knows the block's prefix; block prefixes are
+// resolved by the usual decoupled look-back, but over BLOCK descriptors. No aggregate, of a
+// tile or of a block, ever waits behind a look-back. A tile therefore
+// resolves in two descriptor reads that are in flight together, however many tiles are
+// unresolved in front of it, and the serial chain is 32 times shorter than the tile sequence:
+// the tile rate a GPU at full HBM speed needs (over 100 tiles per microsecond) does not
+// outrun it.
 // Because every warp runs at its own pace, the latency chains of different warps (shared-memory
 // loads, dependent adds, shuffles, scattered stores) overlap instead of adding up behind CTA
 // barriers. Every tile, the first ring-full included, is drawn by ticket, so a tile is only
@@ -86,11 +105,13 @@ struct DescWords {
   }
 };
 
-// Look-back over (count, value) descriptors by one warp, 32 predecessors per round. The
-// operator is not commutative: far predecessors are combined on the left of near ones.
+// Single-level look-back over (count, value) descriptors by one warp, 32 predecessors per round
+// (states EMPTY -> AGGREGATE -> PREFIX): the chain of the one-tile-per-CTA kernels that serve
+// unaligned and tiny inputs. The operator is not commutative: far predecessors are combined on
+// the left of near ones.
 template <typename A>
-__device__ void lookback(const TileWords<4>* tiles, unsigned tile, int* status, unsigned long long& out_cnt,
-                         A& out_val) {
+__device__ void lookback_chain(const TileWords<4>* tiles, unsigned tile, int* status, unsigned long long& out_cnt,
+                               A& out_val) {
   const unsigned lane = lane_id();
   unsigned long long acc_cnt = 0;
   A acc_val = A(0);
@@ -138,12 +159,202 @@ __device__ void lookback(const TileWords<4>* tiles, unsigned tile, int* status, 
   out_val = acc_val;
 }
 
+constexpr int kBlockTiles = 32;  // tiles per block of the two-level chain (one lane per tile)
+enum : unsigned { kStateInclusive = 2 };  // block descriptors: EMPTY -> AGGREGATE -> INCLUSIVE prefix
+
+// Polls one descriptor until it is published (bounded); false on time-out.
+__device__ __forceinline__ bool poll_desc(const TileWords<4>* d, unsigned& st, unsigned (&payload)[4], int* status) {
+  unsigned polls = 0;
+  while ((st = peek<4>(d, payload)) == kStateEmpty) {
+    backoff(++polls);
+    if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) return false;
+  }
+  return true;
+}
+// Same, continuing from a first peek whose outcome is (st, payload).
+__device__ __forceinline__ bool poll_more(const TileWords<4>* d, unsigned& st, unsigned (&payload)[4], int* status) {
+  unsigned polls = 0;
+  while (st == kStateEmpty) {
+    backoff(++polls);
+    if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) return false;
+    st = peek<4>(d, payload);
+  }
+  return true;
+}
+
+// Waits for the aggregates of all tiles of block b, combines them in tile order and publishes the
+// block's aggregate (one warp, all lanes).
+template <typename A>
+__device__ void close_block(const TileWords<4>* tiles, TileWords<4>* blocks, unsigned b, unsigned tiles_in_block,
+                            int* status) {
+  const unsigned lane = lane_id();
+  unsigned long long cnt = 0;
+  A val = A(0);
+  bool ok = true;
+  if (lane < tiles_in_block) {
+    unsigned st, payload[4];
+    ok = poll_desc(&tiles[(size_t)b * kBlockTiles + lane], st, payload, status);
+    if (ok) DescWords<A>::unpack(payload, cnt, val);
+  }
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
+    const A ov = __shfl_down_sync(0xffffffffu, val, off);
+    if (lane + off < 32) {  // (oc, ov) lies to the RIGHT of (cnt, val)
+      val = oc ? ov : val + ov;
+      cnt = cnt + oc;
+    }
+  }
+  if (!__all_sync(0xffffffffu, ok)) {
+    if (lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+    return;
+  }
+  if (lane == 0) {
+    unsigned payload[4];
+    DescWords<A>::pack(cnt, val, payload);
+    publish<4>(&blocks[b], kStateAggregate, payload);
+  }
+}
+
+// Resolves the state of the scan in front of `tile` (one warp, all lanes), in two levels that are
+// read together:
+//  * the aggregates of the tiles in front of it in its own block AND in the kDirectBlocks blocks
+//    before that, read directly (a contiguous run of descriptors per lane, combined in order):
+//    blocks that young have usually not been closed yet, and waiting for their closers would add
+//    a round trip per level to every tile;
+//  * the prefix of the oldest block read directly, by a decoupled look-back over the BLOCK
+//    descriptors behind it (lane l reads block first-1-l; the walk stops at the nearest
+//    inclusive prefix). Those blocks closed long ago.
+// The block's last tile also publishes the block's inclusive prefix. `total` is the tile's own
+// aggregate.
+#ifndef TB200_SEG_DIRECT
+#define TB200_SEG_DIRECT 0
+#endif
+constexpr int kDirectBlocks = TB200_SEG_DIRECT;
+constexpr int kDirectPerLane = (kDirectBlocks * kBlockTiles + kBlockTiles - 1 + kWarp - 1) / kWarp;  
+
+template <typename A>
+__device__ void resolve(const TileWords<4>* tiles, TileWords<4>* blocks, unsigned tile, unsigned total_cnt, A total_val,
+                        int* status, unsigned long long& out_cnt, A& out_val) {
+  const unsigned lane = lane_id();
+  const unsigned b = tile / kBlockTiles, i = tile % kBlockTiles;
+  bool timed_out = false;
+  const unsigned first_block = b >= (unsigned)kDirectBlocks ? b - kDirectBlocks : 0u;  // oldest block read tile by tile
+  const unsigned lo = first_block * kBlockTiles;
+  const unsigned count = tile - lo;  // tiles read directly: [lo, tile)
+
+  // ---- issue every first read: this lane's run of tile descriptors and its block descriptor
+  unsigned st_t[kDirectPerLane], pay_t[kDirectPerLane][4];
+  const unsigned my_first = lo + lane * kDirectPerLane;
+#pragma unroll
+  for (int m = 0; m < kDirectPerLane; ++m) {
+    st_t[m] = kStateAggregate;
+    if (lane * kDirectPerLane + m < count) st_t[m] = peek<4>(&tiles[my_first + m], pay_t[m]);
+  }
+  unsigned st_b = kStateInclusive, pay_b[4];
+  const long long first_idx = (long long)first_block - 1 - lane;
+  if (first_idx >= 0) st_b = peek<4>(&blocks[first_idx], pay_b);
+
+  // ---- tiles read directly, in tile order: each lane combines its run, then the lanes in order
+  unsigned long long icnt = 0;
+  A ival = A(0);
+#pragma unroll
+  for (int m = 0; m < kDirectPerLane; ++m) {
+    if (lane * kDirectPerLane + m < count) {
+      unsigned long long c = 0;
+      A v = A(0);
+      if (poll_more(&tiles[my_first + m], st_t[m], pay_t[m], status)) DescWords<A>::unpack(pay_t[m], c, v);
+      else timed_out = true;
+      ival = c ? v : ival + v;  // (c, v) lies to the RIGHT of what this lane has
+      icnt = icnt + c;
+    }
+  }
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {  // ordered reduction: lane l holds l (+) l+1 (+) ...
+    const unsigned long long oc = __shfl_down_sync(0xffffffffu, icnt, off);
+    const A ov = __shfl_down_sync(0xffffffffu, ival, off);
+    if (lane + off < 32) {  // (oc, ov) lies to the RIGHT of (icnt, ival)
+      ival = oc ? ov : ival + ov;
+      icnt = icnt + oc;
+    }
+  }
+  icnt = __shfl_sync(0xffffffffu, icnt, 0);
+  ival = __shfl_sync(0xffffffffu, ival, 0);
+
+  // ---- prefix of block `first_block`: look-back over the block descriptors behind it
+  unsigned long long pcnt = 0;
+  A pval = A(0);
+  long long base = (long long)first_block - 1;
+  while (base >= 0) {
+    const long long idx = base - lane;
+    unsigned st = kStateInclusive;
+    unsigned long long cnt = 0;
+    A val = A(0);
+    if (idx >= 0) {
+      unsigned payload[4];
+      bool ok;
+      if (base == (long long)first_block - 1) {  // first window: continue from the read issued above
+        ok = poll_more(&blocks[idx], st_b, pay_b, status);
+        st = st_b;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) payload[w] = pay_b[w];
+      } else {
+        ok = poll_desc(&blocks[idx], st, payload, status);
+      }
+      if (ok) DescWords<A>::unpack(payload, cnt, val);
+      else { timed_out = true; st = kStateInclusive; }
+    }
+    const unsigned pm = __ballot_sync(0xffffffffu, st == kStateInclusive);
+    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+    if (lane > first) { cnt = 0; val = A(0); }
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
+      const A ov = __shfl_down_sync(0xffffffffu, val, off);
+      if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val): farther blocks sit in higher lanes
+        val = cnt ? val : ov + val;
+        cnt = oc + cnt;
+      }
+    }
+    cnt = __shfl_sync(0xffffffffu, cnt, 0);
+    val = __shfl_sync(0xffffffffu, val, 0);
+    pval = pcnt ? pval : val + pval;  // this window lies to the left of what is accumulated
+    pcnt = cnt + pcnt;
+    if (pm) break;
+    base -= 32;
+  }
+  // state in front of the tile = (prefix of first_block) (+) (tiles read directly)
+  out_cnt = pcnt + icnt;
+  out_val = icnt ? ival : pval + ival;
+  if (i == kBlockTiles - 1 && lane == 0) {
+    // The block descriptor has two writers, in this order: the closer warp (aggregate), then this
+    // one (inclusive prefix). Wait for the first, or the two sets of words could mix.
+    unsigned st, payload[4];
+    if (poll_desc(&blocks[b], st, payload, status)) {
+      const unsigned long long inc_cnt = out_cnt + total_cnt;
+      const A inc_val = total_cnt ? total_val : out_val + total_val;
+      DescWords<A>::pack(inc_cnt, inc_val, payload);
+      publish<4>(&blocks[b], kStateInclusive, payload);
+    } else {
+      timed_out = true;
+    }
+  }
+  if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+}
+
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * kWarp;
-constexpr int kCtaThreads = kComputeThreads + 2 * kWarp;  // + look-back warp + producer warp
-constexpr int kPacks = 5;  // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
-constexpr int kPark = 2;   // tiles a scanned tile waits for its prefix while the warp goes on
-constexpr int kStages = 5; // ring slots: kPark parked, one in phase A, two loading
+#ifndef TB200_SEG_PACKS
+#define TB200_SEG_PACKS 5
+#define TB200_SEG_PARK 2
+#define TB200_SEG_STAGES 5
+#define TB200_SEG_LOOK 4
+#endif
+constexpr int kLookWarps = TB200_SEG_LOOK;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
+constexpr int kCtaThreads = kComputeThreads + (kLookWarps + 2) * kWarp;  // + look-back warps + publisher + producer
+constexpr int kPacks = TB200_SEG_PACKS;  // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
+constexpr int kPark = TB200_SEG_PARK;   // tiles a scanned tile waits for its prefix while the warp goes on
+constexpr int kStages = TB200_SEG_STAGES; // ring slots: kPark parked, one in phase A, two loading
 constexpr unsigned kNoTile = 0xffffffffu;
 
 template <typename K, typename V>
@@ -176,7 +387,8 @@ struct Args {
   int bulk;                     // inputs are 16-byte aligned: tiles arrive by bulk copy
   V init;                       // exclusive scan_by_key
   TempHeader* hdr;
-  TileWords<4>* tiles;
+  TileWords<4>* tiles;   // one descriptor per tile: EMPTY -> AGGREGATE
+  TileWords<4>* blocks;  // one per block of kBlockTiles tiles: EMPTY -> AGGREGATE -> INCLUSIVE
 };
 
 template <int MODE, typename V> struct AccOf { using type = unsigned; };
@@ -201,10 +413,19 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   extern __shared__ __align__(128) unsigned char ring[];
   __shared__ __align__(8) unsigned long long s_full[NS], s_scanned[NS], s_resolved[NS], s_freed[NS];
   __shared__ unsigned s_tile[NS];
-  __shared__ unsigned s_wtot_cnt[NS][NW];
+  __shared__ __align__(16) unsigned char s_halo[NS][16];  // the 16 bytes of keys in front of the slot's tile
+  __shared__ unsigned s_arrivals[NS];        // compute warps that have finished phase A of the slot's tile
+  __shared__ unsigned s_wtot_cnt[NS][NW];    // warp totals, then (same cells) the warps' exclusive prefixes inside the tile
   __shared__ A s_wtot_val[NS][NW];
-  __shared__ unsigned long long s_wpre_cnt[NS][NW];
+  __shared__ unsigned s_tot_cnt[NS];         // tile aggregate
+  __shared__ A s_tot_val[NS];
+  __shared__ unsigned long long s_wpre_cnt[NS][NW];  // state of the scan in front of every warp, set by the look-back warp
   __shared__ A s_wpre_val[NS][NW];
+  // what a thread keeps of a scanned tile until its prefix is known (per slot)
+  __shared__ unsigned s_park_heads[NS][kComputeThreads];  // head / selection flags of the thread's items
+  __shared__ unsigned s_park_cnt[NS][kComputeThreads];    // flags set in earlier lanes of the warp
+  __shared__ A s_park_val[kSum ? NS : 1][kComputeThreads];  // run open in front of the thread, from the warp's first element
+  __shared__ unsigned s_park_fh[NS][NW];  // scan_by_key: first head of the warp's slice (kWarpItems: none)
 
   const unsigned warp = threadIdx.x / kWarp;
   const unsigned lane = lane_id();
@@ -218,20 +439,33 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   auto wait_all = [&](unsigned long long* bar, unsigned parity) -> bool {
     return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, status));
   };
+  // non-blocking: has the phase completed? (one answer for the whole warp: lane 0's)
+  auto ready = [&](unsigned long long* bar, unsigned parity) -> bool {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_scanned[s], NW);
+      mbar_init(&s_scanned[s], 1);
       mbar_init(&s_resolved[s], 1);
       mbar_init(&s_freed[s], NW);
+      s_arrivals[s] = 0;
     }
     mbar_init_fence();
   }
   __syncthreads();  // the only CTA-wide barrier of the kernel
 
   // ---------------------------------------------------------------------- producer
-  if (warp == NW + 1) {
+  if (warp == NW + kLookWarps + 1) {
     if (lane != 0) return;
     // tile t goes into `slot`; false when the tickets have run past the last tile
     auto issue = [&](int slot, unsigned t) -> bool {
@@ -243,7 +477,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       s_tile[slot] = t;
       if (a.bulk && (uint64_t)(t + 1) * TILE <= n) {
         fence_proxy_async_smem();  // the slot was last written by ordinary stores (parked values)
-        mbar_expect_tx(&s_full[slot], S::kKeyBytes + S::kValBytes);
+        constexpr bool kNeedsPrev = MODE != kCopyFlagged;  // the key in front of the tile decides its first head
+        mbar_expect_tx(&s_full[slot], S::kKeyBytes + S::kValBytes + ((kNeedsPrev && t != 0) ? 16 : 0));
+        if (kNeedsPrev && t != 0)
+          bulk_load(s_halo[slot], reinterpret_cast<const unsigned char*>(a.keys + (uint64_t)t * TILE) - 16, 16, &s_full[slot]);
         bulk_load(slot_keys(slot), a.keys + (uint64_t)t * TILE, S::kKeyBytes, &s_full[slot]);
         if constexpr (kHasVals)
           bulk_load(slot_vals(slot), a.vals + (uint64_t)t * TILE, S::kValBytes, &s_full[slot]);
@@ -252,70 +489,62 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       return true;
     };
-    unsigned first[NS];
-#pragma unroll
-    for (int s = 0; s < NS; ++s) first[s] = atomicAdd(&a.hdr->ticket, 1u);
-    bool more = true;
-#pragma unroll
-    for (int s = 0; s < NS; ++s)
-      if (more) more = issue(s, first[s]);
-    if (!more) return;
-    unsigned pending = atomicAdd(&a.hdr->ticket, 1u);
-    for (unsigned j = NS;; ++j) {
+    // After the last tile, kLookWarps further slots are marked "no tile": every look-back warp
+    // meets one and stops.
+    // The first ring-full is drawn one ticket at a time, each after the previous tile has landed:
+    // all CTAs start together, so their draws interleave and a CTA's k-th tile comes k rounds
+    // after its first in ticket order too. (Drawn in one burst, a CTA's first tiles would be
+    // consecutive tickets; every other CTA's first look-back would then wait for tiles this CTA
+    // scans several iterations later, and the whole grid would start up one CTA after the other.)
+    int stops = 0;
+    for (int s = 0; s < NS && stops < kLookWarps; ++s) {
+      if (!issue(s, stops ? kNoTile : atomicAdd(&a.hdr->ticket, 1u))) ++stops;
+      if (!mbar_wait_bounded(&s_full[s], 0u, status)) return;
+    }
+    // A ticket is drawn only when its slot is free: a drawn tile starts loading at once, so no
+    // tile that successors will wait for sits idle.
+    for (unsigned j = NS; stops < kLookWarps; ++j) {
       const int slot = j % NS;
-      const unsigned t = pending;
-      pending = atomicAdd(&a.hdr->ticket, 1u);  // in flight while this thread waits for the slot
       if (!mbar_wait_bounded(&s_freed[slot], ((j / NS) - 1u) & 1u, status)) return;
-      if (!issue(slot, t)) return;
+      if (!issue(slot, stops ? kNoTile : atomicAdd(&a.hdr->ticket, 1u))) ++stops;
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------------- closer warp
+  if (warp == NW + kLookWarps) {
+    for (unsigned j = 0;; ++j) {
+      const int slot = j % NS;
+      if (!wait_all(&s_full[slot], (j / NS) & 1u)) return;
+      const unsigned tile = s_tile[slot];
+      if (tile == kNoTile) return;
+      if (tile % kBlockTiles == kBlockTiles - 1)  // this CTA holds the block's last tile
+        close_block<A>(a.tiles, a.blocks, tile / kBlockTiles, kBlockTiles, status);
     }
   }
 
   // ---------------------------------------------------------------------- look-back warp
-  if (warp == NW) {
-    for (unsigned j = 0;; ++j) {
+  if (warp >= NW) {
+    for (unsigned j = warp - NW;; j += kLookWarps) {
       const int slot = j % NS;
       const unsigned par = (j / NS) & 1u;
       if (!wait_all(&s_full[slot], par)) return;
       const unsigned tile = s_tile[slot];
       if (tile == kNoTile) return;
       if (!wait_all(&s_scanned[slot], par)) return;
-      SegPair<A> tot{0u, A(0)};
+      SegPair<A> total{s_tot_cnt[slot], A(0)};
+      if constexpr (kSum) total.val = s_tot_val[slot];
+      SegPair<A> exc{0u, A(0)};  // warps in front of warp `lane` inside the tile
       if (lane < NW) {
-        tot.cnt = s_wtot_cnt[slot][lane];
-        if constexpr (kSum) tot.val = s_wtot_val[slot][lane];
+        exc.cnt = s_wtot_cnt[slot][lane];
+        if constexpr (kSum) exc.val = s_wtot_val[slot][lane];
       }
-      SegPair<A> inc = tot;
-#pragma unroll
-      for (int off = 1; off < NW; off <<= 1) {
-        SegPair<A> o;
-        o.cnt = __shfl_up_sync(0xffffffffu, inc.cnt, off);
-        o.val = kSum ? __shfl_up_sync(0xffffffffu, inc.val, off) : A(0);
-        if (lane >= off) inc = combine(o, inc);
-      }
-      SegPair<A> exc;  // warps in front of warp `lane`
-      exc.cnt = __shfl_up_sync(0xffffffffu, inc.cnt, 1);
-      exc.val = kSum ? __shfl_up_sync(0xffffffffu, inc.val, 1) : A(0);
-      if (lane == 0) { exc.cnt = 0; exc.val = A(0); }
-      SegPair<A> total;
-      total.cnt = __shfl_sync(0xffffffffu, inc.cnt, NW - 1);
-      total.val = kSum ? __shfl_sync(0xffffffffu, inc.val, NW - 1) : A(0);
-
       unsigned long long pc = 0;
       A pv = A(0);
-      if (tile != 0) {
-        if (lane == 0) {
-          unsigned payload[4];
-          DescWords<A>::pack(total.cnt, total.val, payload);
-          publish<4>(&a.tiles[tile], kStateAggregate, payload);
-        }
-        lookback<A>(a.tiles, tile, status, pc, pv);
-      }
+      resolve<A>(a.tiles, a.blocks, tile, total.cnt, total.val, status, pc, pv);
       if (lane == 0) {
         const unsigned long long ic = pc + total.cnt;
         const A iv = total.cnt ? total.val : pv + total.val;
-        unsigned payload[4];
-        DescWords<A>::pack(ic, iv, payload);
-        publish<4>(&a.tiles[tile], kStatePrefix, payload);
         if (tile == num_tiles - 1) {
           if constexpr (MODE == kReduceByKey) {  // close the last run
             if (ic > 0) a.vals_out[ic - 1] = iv;
@@ -335,16 +564,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   // ---------------------------------------------------------------------- compute warps
   const unsigned my_off = threadIdx.x * ITEMS;  // first element of this thread inside a tile
   struct Parked {
-    unsigned heads;  // head / selection flags of the thread's items
-    unsigned cnt;    // flags set in earlier lanes of the warp
-    A val;           // sum of the run that is open in front of the thread, counted from the warp's first element
-    unsigned fh;     // scan_by_key: first head of the warp's slice (kWarpItems: none)
+    unsigned heads, cnt;
+    A val;
+    unsigned fh;
   };
 
-  // Phase C of the tile parked in `slot` at iteration jj.
-  auto phase_c = [&](unsigned jj, const Parked& st) -> bool {
+  // Phase C of the tile parked in the slot of iteration jj (its prefix has been resolved).
+  auto phase_c = [&](unsigned jj) -> bool {
     const int slot = jj % NS;
-    if (!wait_all(&s_resolved[slot], (jj / NS) & 1u)) return false;
+    if (!wait_all(&s_resolved[slot], (jj / NS) & 1u)) return false;  // returns at once: the caller saw it complete
+    Parked st;
+    st.heads = s_park_heads[slot][threadIdx.x];
+    st.cnt = s_park_cnt[slot][threadIdx.x];
+    st.val = A(0);
+    if constexpr (kSum) st.val = s_park_val[slot][threadIdx.x];
+    st.fh = s_park_fh[slot][warp];
     const unsigned tile = s_tile[slot];
     const uint64_t tile_base = (uint64_t)tile * TILE;
     const K* sk = slot_keys(slot);
@@ -407,16 +641,34 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     return true;
   };
 
-  Parked parked[kPark];
-#pragma unroll
-  for (int p = 0; p < kPark; ++p) parked[p] = Parked{0u, 0u, A(0), 0u};
-  unsigned j = 0;
-  bool alive = true;
-  for (;; ++j) {
+  // Every warp schedules itself: it scans the next tile as soon as the tile has landed (so the
+  // tile's aggregate reaches the other CTAs as early as possible, whatever this CTA is still
+  // waiting for) and emits the oldest parked tile as soon as its prefix is resolved; it idles
+  // only when neither is possible.
+  unsigned j = 0;       // next tile of the CTA to scan
+  unsigned j_emit = 0;  // oldest scanned tile not yet emitted
+  bool more = true;     // the producer has not run out of tiles
+  unsigned idle = 0;
+  while (more || j_emit < j) {
+    if (j_emit < j && ready(&s_resolved[j_emit % NS], (j_emit / NS) & 1u)) {
+      if (!phase_c(j_emit)) return;
+      ++j_emit;
+      idle = 0;
+      continue;
+    }
+    if (!(more && ready(&s_full[j % NS], (j / NS) & 1u))) {
+      if (++idle > (1u << 24) || ((idle & 4095u) == 0 && ld_relaxed_s32(status) != 0)) {  // bounded
+        if (lane == 0 && idle > (1u << 24)) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+        return;
+      }
+      if (idle > 64) __nanosleep(40);
+      continue;
+    }
+    idle = 0;
     const int slot = j % NS;
-    if (!wait_all(&s_full[slot], (j / NS) & 1u)) { alive = false; break; }
+    if (!wait_all(&s_full[slot], (j / NS) & 1u)) return;  // returns at once
     const unsigned tile = s_tile[slot];
-    if (tile == kNoTile) break;
+    if (tile == kNoTile) { more = false; continue; }
     const uint64_t tile_base = (uint64_t)tile * TILE;
     const uint64_t my_base = tile_base + my_off;
     const bool staged = a.bulk && (uint64_t)(tile + 1) * TILE <= n;  // the tile came by bulk copy
@@ -471,6 +723,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       K prev = __shfl_up_sync(0xffffffffu, k[ITEMS - 1], 1);
       if (lane == 0) {
         if (staged && warp > 0) prev = sk[my_off - 1];
+        else if (staged && tile != 0) prev = *reinterpret_cast<const K*>(&s_halo[slot][16 - sizeof(K)]);
         else prev = (my_base > 0 && my_base <= n) ? a.keys[my_base - 1] : K{};
       }
 #pragma unroll
@@ -549,21 +802,54 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       now.fh = fh;
     }
+    s_park_heads[slot][threadIdx.x] = now.heads;
+    s_park_cnt[slot][threadIdx.x] = now.cnt;
+    if constexpr (kSum) s_park_val[slot][threadIdx.x] = now.val;
+    if (lane == 0) s_park_fh[slot][warp] = now.fh;
     __syncwarp();
-    if (lane == 0) mbar_arrive(&s_scanned[slot]);
-
-    // ---- phase C of the tile this warp scanned kPark iterations ago
-    if (j >= (unsigned)kPark) {
-      if (!phase_c(j - kPark, parked[kPark - 1])) { alive = false; break; }
+    // The last warp to finish phase A of this tile combines the warp totals (in warp order) and
+    // publishes the tile's aggregate.
+    unsigned last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&s_arrivals[slot], 1u) == (unsigned)(NW - 1);
+      __threadfence_block();
     }
+    if (__shfl_sync(0xffffffffu, last, 0)) {
+      SegPair<A> tot{0u, A(0)};
+      if (lane < NW) {
+        tot.cnt = s_wtot_cnt[slot][lane];
+        if constexpr (kSum) tot.val = s_wtot_val[slot][lane];
+      }
+      SegPair<A> inc = tot;
 #pragma unroll
-    for (int p = kPark - 1; p > 0; --p) parked[p] = parked[p - 1];
-    parked[0] = now;
-  }
-  if (alive) {
-#pragma unroll
-    for (int p = kPark; p >= 1; --p)
-      if (j >= (unsigned)p && alive) alive = phase_c(j - p, parked[p - 1]);
+      for (int off = 1; off < NW; off <<= 1) {
+        SegPair<A> o;
+        o.cnt = __shfl_up_sync(0xffffffffu, inc.cnt, off);
+        o.val = kSum ? __shfl_up_sync(0xffffffffu, inc.val, off) : A(0);
+        if (lane >= off) inc = combine(o, inc);
+      }
+      SegPair<A> exc;
+      exc.cnt = __shfl_up_sync(0xffffffffu, inc.cnt, 1);
+      exc.val = kSum ? __shfl_up_sync(0xffffffffu, inc.val, 1) : A(0);
+      if (lane == 0) { exc.cnt = 0; exc.val = A(0); }
+      if (lane < NW) {  // the totals have been read by this warp: the cells now hold the exclusive prefixes
+        s_wtot_cnt[slot][lane] = exc.cnt;
+        if constexpr (kSum) s_wtot_val[slot][lane] = exc.val;
+      }
+      if (lane == NW - 1) {
+        s_tot_cnt[slot] = inc.cnt;
+        if constexpr (kSum) s_tot_val[slot] = inc.val;
+        unsigned payload[4];
+        DescWords<A>::pack(inc.cnt, inc.val, payload);
+        publish<4>(&a.tiles[tile], kStateAggregate, payload);  // plain stores: nothing is waited for
+        s_arrivals[slot] = 0;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_scanned[slot]);  // hands the tile to its look-back warp
+    }
+
+    ++j;
   }
 }
 
@@ -580,11 +866,12 @@ inline int sm_count(int* sms) {
 template <typename K, typename V>
 constexpr uint64_t tile_elems() { return (uint64_t)Shape<K, V>::kTile; }
 
-// Scratch: header + one 32-byte descriptor per tile.
+// Scratch: header + one 32-byte descriptor per tile + one per block of tiles.
 template <typename K, typename V>
 size_t scratch_bytes(uint64_t n) {
   const uint64_t tiles = (n + tile_elems<K, V>() - 1) / tile_elems<K, V>();
-  return kHeaderBytes + (size_t)tiles * sizeof(TileWords<4>);
+  const uint64_t blocks = (tiles + kBlockTiles - 1) / kBlockTiles;
+  return kHeaderBytes + (size_t)(tiles + blocks) * sizeof(TileWords<4>);
 }
 
 // Launches the streaming kernel (n > 0, scratch cleared by the caller). `bulk`: keys, values and,
@@ -607,6 +894,7 @@ int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long
   a.init = init;
   a.hdr = static_cast<TempHeader*>(d_temp);
   a.tiles = reinterpret_cast<TileWords<4>*>(static_cast<char*>(d_temp) + kHeaderBytes);
+  a.blocks = a.tiles + tiles;
   auto kernel = stream_kernel<MODE, K, V>;
   // opt in to the kernel's dynamic shared memory once per device (this function is one
   // instantiation per kernel, so the flag below belongs to this kernel alone)
