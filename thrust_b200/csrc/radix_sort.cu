@@ -28,10 +28,6 @@
 
 #include <type_traits>
 
-#ifndef TB200_MATCH_MODE
-#define TB200_MATCH_MODE 2  // 0: match.any instruction (slow on sm_100), 1: eight ballots in C++, 2: in PTX
-#endif
-
 namespace tb200 {
 namespace {
 
@@ -369,11 +365,7 @@ __device__ __forceinline__ void st_desc(DescT* p, DescT v) {
 
 template <int B>
 __device__ __forceinline__ void match_bit(unsigned& peers, unsigned d) {
-#ifdef TB200_MATCH_ASM_PLAIN
-  asm(
-#else
   asm volatile(
-#endif
       "{\n"
       ".reg .pred p;\n"
       ".reg .b32 t, m, nm;\n"
@@ -391,24 +383,11 @@ __device__ __forceinline__ void match_bit(unsigned& peers, unsigned d) {
 // Lanes of the warp that hold the same 8-bit digit. One ballot per bit; a lane keeps
 // the voters that agree with its own bit: peers &= ~(ballot ^ sign_extend(bit)).
 __device__ __forceinline__ unsigned match_digit(unsigned d) {
-#if TB200_MATCH_MODE == 0
-  return __match_any_sync(0xffffffffu, d);
-#elif TB200_MATCH_MODE == 2
   // four instructions per bit: test, vote, and one predicated AND for either polarity
   unsigned peers = 0xffffffffu;
   match_bit<0>(peers, d); match_bit<1>(peers, d); match_bit<2>(peers, d); match_bit<3>(peers, d);
   match_bit<4>(peers, d); match_bit<5>(peers, d); match_bit<6>(peers, d); match_bit<7>(peers, d);
   return peers;
-#else
-  unsigned peers = 0xffffffffu;
-#pragma unroll
-  for (int b = 0; b < 8; ++b) {
-    const unsigned m = __ballot_sync(0xffffffffu, (d >> b) & 1u);
-    const unsigned t = 0u - ((d >> b) & 1u);  // all ones when the lane's bit is set
-    peers &= ~(m ^ t);
-  }
-  return peers;
-#endif
 }
 // Same, for digits known to fit in `bits` bits (bucket ids of a partition): fewer ballots.
 __device__ __forceinline__ unsigned match_digit_bits(unsigned d, int bits) {
@@ -437,6 +416,8 @@ struct PassShape {
   static constexpr size_t kValsBytes = VB ? align_up((size_t)kTile * VB, 16) : 0;
   static constexpr size_t kWhistBytes = (size_t)kWarps * kRadix * sizeof(unsigned);
   static constexpr size_t kSmem = align_up(kKeysBytes, 16) + kValsBytes + kWhistBytes;
+  // the partition form also keeps one byte per sorted slot: the bucket of the key parked there
+  static constexpr size_t kSmemSplit = kSmem + align_up((size_t)kTile, 16);
 };
 
 // Persistent CTAs: the grid holds as many CTAs as fit on the GPU at once and every
@@ -464,6 +445,7 @@ onesweep_kernel(const PassParams prm) {
   UK* s_keys = reinterpret_cast<UK*>(smem);
   V* s_vals = reinterpret_cast<V*>(smem + align_up(Shape::kKeysBytes, 16));
   unsigned* s_whist = reinterpret_cast<unsigned*>(smem + align_up(Shape::kKeysBytes, 16) + Shape::kValsBytes);
+  unsigned char* s_bkt = smem + Shape::kSmem;  // partition form only: bucket of every parked key
   __shared__ IdxT s_gbase[kRadix];
   __shared__ unsigned s_part[GROUPS][kRadix];  // per-group digit totals
   __shared__ unsigned s_scan[kRadix / kWarp];
@@ -499,13 +481,27 @@ onesweep_kernel(const PassParams prm) {
   unsigned* whist = s_whist + warp * kRadix;
   const unsigned num_split = SPLIT ? prm.num_splitters : 0u;
   const int split_bits = 32 - __clz(num_split | 1u);  // bucket ids are 0..num_split
+  // Partition form: the bucket of a key is the number of splitters strictly below it. It is
+  // computed ONCE per key (while ranking) and kept: in a byte per item in registers until the
+  // reorder, in a byte per sorted slot in shared memory until the scatter. Up to seven splitters
+  // (eight GPUs) live in registers, padded with the largest key: three compare-and-select levels.
+  UK sp[SPLIT ? 7 : 1];
+  const bool few = SPLIT && num_split <= 7;
   if constexpr (SPLIT) {
+#pragma unroll
+    for (int j = 0; j < 7; ++j)
+      sp[j] = (few && (unsigned)j < num_split) ? static_cast<const UK*>(prm.splitters)[j] : (UK)~(UK)0;
     for (unsigned i = threadIdx.x; i < num_split; i += THREADS) s_split[i] = static_cast<const UK*>(prm.splitters)[i];
   }
   auto digit = [&](UK k) -> unsigned {
     if constexpr (SPLIT) {
-      // number of splitters strictly below k: binary search over the ascending splitters
-      unsigned lo = 0, hi = num_split;
+      if (few) {
+        const bool c1 = sp[3] < k;
+        const bool c2 = (c1 ? sp[5] : sp[1]) < k;
+        const bool c3 = (c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0])) < k;
+        return 4u * c1 + 2u * c2 + (unsigned)c3;
+      }
+      unsigned lo = 0, hi = num_split;  // binary search over the ascending splitters
       while (lo < hi) {
         const unsigned mid = (lo + hi) >> 1;
         if (s_split[mid] < k) lo = mid + 1; else hi = mid;
@@ -582,15 +578,8 @@ onesweep_kernel(const PassParams prm) {
       if (grp == 0) {
         const unsigned d = d_own;
         unsigned long long excl = 0;
-  #ifdef TB200_EXPERIMENT_NO_LOOKBACK  // timing experiments only: results are wrong
-        if (false) {
-  #else
         if (p_tile != 0) {
-  #endif
-  #ifndef TB200_SORT_WINDOW
-  #define TB200_SORT_WINDOW 4
-  #endif
-          constexpr int kWindow = TB200_SORT_WINDOW;
+          constexpr int kWindow = 4;
           const DescT* chain = static_cast<const DescT*>(prm.desc) + d;
           const DescT below_first = (DescT)st_prefix << DSH;  // virtual prefix 0 before tile 0
           long long t = (long long)p_tile - 1;
@@ -629,7 +618,7 @@ onesweep_kernel(const PassParams prm) {
       auto emit = [&](unsigned pos) {
         const UK k = s_keys[pos];
         if constexpr (SPLIT) {
-          const unsigned b = digit(k);
+          const unsigned b = s_bkt[pos];
           const IdxT g = s_gbase[b] + pos;  // index inside bucket b (the sum never wraps)
           s_bucket_keys[b][g] = k;
           if constexpr (VB != 0) s_bucket_vals[b][g] = s_vals[pos];
@@ -665,10 +654,12 @@ onesweep_kernel(const PassParams prm) {
     // what round j wrote; the only register dependency inside a round is
     // load -> add -> store.
     unsigned short rank[ITEMS];
+    unsigned char bkt[SPLIT ? ITEMS : 1];
     const unsigned lt_mask = lanemask_lt();
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
       const unsigned d = digit(key[j]);
+      if constexpr (SPLIT) bkt[j] = (unsigned char)d;
       const unsigned peers = SPLIT ? match_digit_bits(d, split_bits) : match_digit(d);
       const unsigned ahead = __popc(peers & lt_mask);
       const unsigned old = whist[d];
@@ -738,18 +729,18 @@ onesweep_kernel(const PassParams prm) {
       for (int w = 0; w < WARPS_PER_GROUP; ++w) s_whist[(grp * WARPS_PER_GROUP + w) * kRadix + d_own] += add;
     }
 
-#ifndef TB200_SORT_FLUSH_IMMEDIATELY
     if (parked) flush_parked();  // tile i-1 leaves while tile i's counts are already published
-#endif
     __syncthreads();  // counters hold slot offsets; the shared tile buffers are free
 
     // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned d = digit(key[j]);
+      unsigned d;
+      if constexpr (SPLIT) d = bkt[j]; else d = digit(key[j]);
       const unsigned q = whist[d] + rank[j];
       rank[j] = (unsigned short)q;
       s_keys[q] = key[j];
+      if constexpr (SPLIT) s_bkt[q] = (unsigned char)d;
     }
     // the key registers are free: fetch the next tile's keys now
     if (next < num_tiles) load_keys(next);
@@ -763,11 +754,6 @@ onesweep_kernel(const PassParams prm) {
     p_valid = tile_valid;
     p_count = count;
     p_digit_start = digit_start;
-#ifdef TB200_SORT_FLUSH_IMMEDIATELY
-    __syncthreads();
-    flush_parked();
-    parked = false;
-#endif
     if (next >= num_tiles) break;
     tile = next;
     __syncthreads();  // counters are cleared and the tile buffers read by the next iteration
@@ -817,20 +803,41 @@ enum { kPhaseAll = 0, kPhaseBegin = 1, kPhaseFinish = 2 };
 template <typename UK, int VB>
 struct Tuning {
   // threads x items per thread of one onesweep tile, and CTAs that must fit the register file of one SM
-#ifdef TB200_TUNE_THREADS
-  static constexpr int kThreads = TB200_TUNE_THREADS;
-  static constexpr int kItems = TB200_TUNE_ITEMS;
-  static constexpr int kMinCtas = TB200_TUNE_MINB;
-#else
   // Measured on B200: few threads with many items each (more independent work per thread,
   // no register spills at 128 registers, fewer per-warp counters to combine) beat 512-thread
-  // CTAs by about 10 %; two CTAs per SM.
+  // CTAs by about 10 %; two CTAs per SM (three CTAs of 16 items or four of 12 measured 2 % and
+  // 8 % slower on 64-bit pairs, 13-25 % slower on 32-bit keys).
   static constexpr int kThreads = 256;
   static constexpr int kItems = sizeof(UK) == 8 ? (VB == 16 ? 12 : (VB == 8 ? 16 : 24))
                                                 : (VB == 16 ? 12 : (VB == 8 ? 24 : (VB == 0 ? 40 : 32)));
   static constexpr int kMinCtas = 2;
-#endif
 };
+
+// Shared-memory opt-in and residency (CTAs per SM) of one kernel, asked of the runtime once per
+// device. Tag names the kernel's instantiation: all instantiations share one function-pointer type.
+template <typename Tag, typename Kernel>
+int resident_ctas(Kernel kernel, int threads, size_t smem, int* per_sm) {
+  static int cached[64] = {};  // 0: not asked yet (benign race: the answer is always the same)
+  int dev = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && cached[dev] > 0) { *per_sm = cached[dev]; return TB200_OK; }
+  TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(per_sm, kernel, threads, smem));
+  if (*per_sm < 1) return TB200_ERR_UNSUPPORTED;
+  if (dev < 64) cached[dev] = *per_sm;
+  return TB200_OK;
+}
+inline int sm_count_of_device(int* sms) {
+  static int cached[64] = {};
+  int dev = 0;
+  TB200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && cached[dev]) { *sms = cached[dev]; return TB200_OK; }
+  TB200_CUDA_TRY(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+  if (dev < 64) cached[dev] = *sms;
+  return TB200_OK;
+}
+template <typename UK, int VB, typename DescT, bool SPLIT> struct PassTag {};
+template <typename UK> struct ByteHistTag {};
 
 struct Layout {
   size_t ctl_off, desc_off, keys_off, vals_off, total, clear_bytes;
@@ -880,9 +887,11 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   enc.dmask = descending ? ~0ull : 0ull;
   const int num_passes = (end_bit - begin_bit + 7) / 8;
 
-  int dev = 0, sms = 0;
-  TB200_CUDA_TRY(cudaGetDevice(&dev));
-  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  {
+    const int rc = sm_count_of_device(&sms);
+    if (rc) return rc;
+  }
 
   if (phase == kPhaseFinish) {
     histogram_finalize_kernel<<<1, kHistThreads, 0, stream>>>(ctl, num_passes, n);
@@ -895,10 +904,9 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
       const uint64_t chunk = (uint64_t)kByteHistThreads * (16 / sizeof(UK)) * kHistUnroll;
       const uint64_t want = (n + chunk - 1) / chunk;
       auto kernel = histogram_bytes_kernel<UK>;
-      TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
       int per_sm = 0;
-      TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kByteHistThreads, kSmem));
-      if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+      const int prc = resident_ctas<ByteHistTag<UK>>(kernel, kByteHistThreads, (size_t)kSmem, &per_sm);
+      if (prc) return prc;
       const uint64_t resident = (uint64_t)per_sm * sms;
       const unsigned grid = (unsigned)(want < resident ? (want ? want : 1) : resident);
       kernel<<<grid, kByteHistThreads, kSmem, stream>>>(static_cast<const UK*>(d_keys), n, enc, ctl, aligned);
@@ -927,11 +935,10 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.num_splitters = 0;
   prm.bucket_keys = nullptr;
   prm.bucket_vals = nullptr;
-  auto launch = [&](auto kernel) -> int {
-    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
+  auto launch = [&](auto kernel, auto tag) -> int {
     int per_sm = 0;
-    TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, T::kThreads, Shape::kSmem));
-    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const int prc = resident_ctas<decltype(tag)>(kernel, T::kThreads, Shape::kSmem, &per_sm);
+    if (prc) return prc;
     const uint64_t resident = (uint64_t)per_sm * sms;
     const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
     for (int p = 0; p < num_passes; ++p) {
@@ -945,8 +952,10 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
     }
     return TB200_OK;
   };
-  int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long>)
-                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned>);
+  int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long>,
+                         PassTag<UK, VB, unsigned long long, false>{})
+                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned>,
+                         PassTag<UK, VB, unsigned, false>{});
   if (rc) return rc;
 
   copy_back_kernel<<<sms * 4, 256, 0, stream>>>(
@@ -1119,9 +1128,11 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   if (!d_keys) return TB200_ERR_INVALID_ARGUMENT;
   if (phase != kPhaseBegin && VB && !d_vals) return TB200_ERR_INVALID_ARGUMENT;
   if (phase == kPhaseAll && (!d_keys_out || (VB && !d_vals_out))) return TB200_ERR_INVALID_ARGUMENT;
-  int dev = 0, sms = 0;
-  TB200_CUDA_TRY(cudaGetDevice(&dev));
-  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  {
+    const int rc = sm_count_of_device(&sms);
+    if (rc) return rc;
+  }
   if (phase != kPhaseFinish) {
     const uint64_t want = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
     const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
@@ -1165,19 +1176,20 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   prm.num_splitters = num_splitters;
   prm.bucket_keys = d_bucket_keys;
   prm.bucket_vals = d_bucket_vals;
-  auto launch = [&](auto kernel) -> int {
-    TB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape::kSmem));
+  auto launch = [&](auto kernel, auto tag) -> int {
     int per_sm = 0;
-    TB200_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, T::kThreads, Shape::kSmem));
-    if (per_sm < 1) return TB200_ERR_UNSUPPORTED;
+    const int prc = resident_ctas<decltype(tag)>(kernel, T::kThreads, Shape::kSmemSplit, &per_sm);
+    if (prc) return prc;
     const uint64_t resident = (uint64_t)per_sm * sms;
     const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
-    kernel<<<grid, T::kThreads, Shape::kSmem, stream>>>(prm);
+    kernel<<<grid, T::kThreads, Shape::kSmemSplit, stream>>>(prm);
     trace_mark(stream, kTracePartitionPass);
     return (int)cudaGetLastError();
   };
-  const int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true>)
-                      : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true>);
+  const int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true>,
+                               PassTag<UK, VB, unsigned long long, true>{})
+                      : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true>,
+                               PassTag<UK, VB, unsigned, true>{});
   return rc;
 }
 
@@ -1400,9 +1412,11 @@ extern "C" int tb200_gather_segments(void* d_dst, const void* const* h_src, cons
     off += h_count[s];
   }
   if (off == 0) return TB200_OK;
-  int dev = 0, sms = 0;
-  TB200_CUDA_TRY(cudaGetDevice(&dev));
-  TB200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  int sms = 0;
+  {
+    const int rc = tb200::sm_count_of_device(&sms);
+    if (rc) return rc;
+  }
   const unsigned grid = (unsigned)sms * 4;
   auto* ctl = static_cast<SortCtl*>(d_sort_temp);
   switch (elem_bytes) {

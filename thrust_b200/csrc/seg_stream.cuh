@@ -227,10 +227,7 @@ __device__ void close_block(const TileWords<4>* tiles, TileWords<4>* blocks, uns
 //    inclusive prefix). Those blocks closed long ago.
 // The block's last tile also publishes the block's inclusive prefix. `total` is the tile's own
 // aggregate.
-#ifndef TB200_SEG_DIRECT
-#define TB200_SEG_DIRECT 0
-#endif
-constexpr int kDirectBlocks = TB200_SEG_DIRECT;
+constexpr int kDirectBlocks = 0;  // measured on B200: every further block read tile by tile costs more descriptor traffic than its closer's delay
 constexpr int kDirectPerLane = (kDirectBlocks * kBlockTiles + kBlockTiles - 1 + kWarp - 1) / kWarp;  
 
 template <typename A>
@@ -344,17 +341,10 @@ __device__ void resolve(const TileWords<4>* tiles, TileWords<4>* blocks, unsigne
 
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * kWarp;
-#ifndef TB200_SEG_PACKS
-#define TB200_SEG_PACKS 5
-#define TB200_SEG_PARK 2
-#define TB200_SEG_STAGES 5
-#define TB200_SEG_LOOK 4
-#endif
-constexpr int kLookWarps = TB200_SEG_LOOK;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
-constexpr int kCtaThreads = kComputeThreads + (kLookWarps + 2) * kWarp;  // + look-back warps + publisher + producer
-constexpr int kPacks = TB200_SEG_PACKS;  // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
-constexpr int kPark = TB200_SEG_PARK;   // tiles a scanned tile waits for its prefix while the warp goes on
-constexpr int kStages = TB200_SEG_STAGES; // ring slots: kPark parked, one in phase A, two loading
+constexpr int kLookWarps = 3;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
+constexpr int kCtaThreads = kComputeThreads + (kLookWarps + 2) * kWarp;  // + look-back warps + closer + producer
+constexpr int kPacks = 5;   // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
+constexpr int kStages = 5;  // ring slots: one or two loading, one being scanned, the rest parked
 constexpr unsigned kNoTile = 0xffffffffu;
 
 template <typename K, typename V>
