@@ -643,7 +643,6 @@ onesweep_kernel(const PassParams prm) {
     const uint64_t remaining = prm.n - tile_base;
     const unsigned tile_valid = remaining < (uint64_t)TILE ? (unsigned)remaining : (unsigned)TILE;
 
-    if (threadIdx.x == 0) s_next = atomicAdd(&ctl->tickets[pass], 1u);  // consumed after the ranking barrier
     for (int i = threadIdx.x; i < WARPS * kRadix / 4; i += THREADS)
       reinterpret_cast<uint4*>(s_whist)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
@@ -682,7 +681,6 @@ onesweep_kernel(const PassParams prm) {
       }
     }
     __syncthreads();
-    const unsigned next = s_next;
 
     // ---- per-digit tile totals and warp offsets: thread (g, d) walks the warps of its
     // group; group totals are combined through shared memory. The tile's counts are
@@ -729,8 +727,14 @@ onesweep_kernel(const PassParams prm) {
       for (int w = 0; w < WARPS_PER_GROUP; ++w) s_whist[(grp * WARPS_PER_GROUP + w) * kRadix + d_own] += add;
     }
 
+    // The next tile's ticket is drawn as late as its latency can still hide behind the scatter:
+    // a drawn tile that waits long before it is ranked holds back every later tile's look-back.
+    unsigned drawn = 0;  // thread 0: in flight during the look-back and the scatter
+    if (threadIdx.x == 0) drawn = atomicAdd(&ctl->tickets[pass], 1u);
     if (parked) flush_parked();  // tile i-1 leaves while tile i's counts are already published
+    if (threadIdx.x == 0) s_next = drawn;
     __syncthreads();  // counters hold slot offsets; the shared tile buffers are free
+    const unsigned next = s_next;
 
     // ---- reorder keys and values through shared memory (tile-local, needs no prefix)
 #pragma unroll
