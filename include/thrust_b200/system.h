@@ -2,7 +2,8 @@
 // examples/minimal_custom_backend.cu:17-37) that routes sort / stable_sort /
 // sort_by_key / stable_sort_by_key / inclusive_scan / exclusive_scan / inclusive_scan_by_key /
 // exclusive_scan_by_key / reduce / reduce_by_key / unique / unique_copy / unique_by_key /
-// unique_by_key_copy / copy_if (stencil form)
+// unique_by_key_copy / copy_if (stencil form), and the asynchronous forms thrust::async::sort /
+// stable_sort / inclusive_scan / exclusive_scan,
 // on contiguous arithmetic data to the sm_100a kernels behind the C ABI of
 // thrust_b200.h, and everything else to the CUDA system it derives from.
 //
@@ -37,6 +38,8 @@
 #include <thrust/sort.h>
 #include <thrust/copy.h>
 #include <thrust/unique.h>
+#include <thrust/async/scan.h>
+#include <thrust/async/sort.h>
 #include <thrust/system/cuda/error.h>
 #include <thrust/system/cuda/execution_policy.h>
 #include <thrust/system/system_error.h>
@@ -44,6 +47,8 @@
 
 #include <atomic>
 #include <cstddef>
+#include <memory>
+#include <tuple>
 #include <cstdint>
 #include <new>
 #include <string>
@@ -623,6 +628,102 @@ template <typename InIt, typename OutIt, typename Pred>
 OutIt copy_if(system& s, InIt first, InIt last, OutIt result, Pred pred) {
   ++detail::forwarded_calls();  // the predicate reads the elements themselves: the caller's device code
   return thrust::copy_if(detail::inherited(s), first, last, result, pred);
+}
+
+// ---- asynchronous forms (thrust/async/sort.h, thrust/async/scan.h) ---------------------------
+// thrust::async::sort / stable_sort / inclusive_scan / exclusive_scan reach these customization
+// points by ADL on the policy (thrust/async/sort.h:60-120, thrust/async/scan.h) and get back the
+// CUDA system's event type, as they do from the reference's own implementations
+// (thrust/system/cuda/detail/async/sort.h:496-512, async/inclusive_scan.h, async/exclusive_scan.h:77-90).
+// The work is enqueued on the event's stream — the policy's stream, or a new one if the policy
+// has the default stream — and the call returns at once; the scratch stays leased until the
+// event is destroyed. The device status word is not read back (no synchronisation): wait on the
+// event and call the blocking form if a status is wanted.
+namespace detail {
+struct lease_release {
+  void operator()(void* p) const { tb200_workspace_release(p); }
+};
+using lease_ptr = std::unique_ptr<void, lease_release>;
+inline lease_ptr lease(size_t bytes, cudaStream_t stream, char** aligned) {
+  void* raw = nullptr;
+  const int rc = tb200_workspace_acquire(bytes + 256, stream, &raw);
+  if (rc == (int)cudaErrorMemoryAllocation) throw std::bad_alloc();
+  throw_on_error(rc, "tb200_workspace_acquire");
+  *aligned = reinterpret_cast<char*>((reinterpret_cast<std::uintptr_t>(raw) + 255) / 256 * 256);
+  return lease_ptr(raw);
+}
+// The event of an asynchronous call: keeps `keep` alive and names the stream the work goes to.
+inline thrust::system::cuda::unique_eager_event async_event(const system& s, lease_ptr keep) {
+  namespace cd = thrust::system::cuda::detail;
+  if (s.stream != nullptr)
+    return cd::make_dependent_event(std::make_tuple(std::move(keep), cd::unique_stream(cd::nonowning, s.stream)));
+  return cd::make_dependent_event(std::make_tuple(std::move(keep)));
+}
+}  // namespace detail
+
+template <typename It, typename Sentinel, typename Compare>
+auto async_stable_sort(system& s, It first, Sentinel last, Compare comp) {
+  if constexpr (detail::sort_fast_v<It, Compare> && std::is_same<It, Sentinel>::value) {
+    using K = detail::value_t<It>;
+    const uint64_t n = (uint64_t)(last - first);
+    size_t bytes = 0;
+    detail::throw_on_error(tb200_radix_sort(nullptr, &bytes, nullptr, nullptr, n, detail::dtype_of<K>(), 0,
+                                            detail::order_of<Compare, K>::value, 0, 8 * (int)sizeof(K), nullptr),
+                           "tb200_radix_sort");
+    // the lease is taken for the legacy stream's pool when the event brings its own stream: its
+    // first use is ordered by the event, and it is released only when the event dies
+    char* temp = nullptr;
+    auto keep = detail::lease(bytes, s.stream, &temp);
+    auto e = detail::async_event(s, std::move(keep));
+    detail::throw_on_error(tb200_radix_sort(temp, &bytes, n ? (void*)detail::raw(first) : nullptr, nullptr, n,
+                                            detail::dtype_of<K>(), 0, detail::order_of<Compare, K>::value, 0,
+                                            8 * (int)sizeof(K), e.stream().native_handle()), "tb200_radix_sort");
+    ++detail::fast_calls();
+    (void)comp;
+    return e;
+  } else {
+    ++detail::forwarded_calls();
+    auto inherited = detail::inherited(s);
+    return thrust::cuda_cub::async_stable_sort(inherited, first, last, comp);
+  }
+}
+
+namespace detail {
+template <typename InIt, typename OutIt, typename T>
+auto async_scan_fast(system& s, InIt first, InIt last, OutIt out, bool exclusive, const T* init) {
+  const uint64_t n = (uint64_t)(last - first);
+  size_t bytes = 0;
+  throw_on_error(tb200_scan(nullptr, &bytes, nullptr, nullptr, n, dtype_of<T>(), exclusive, init, nullptr), "tb200_scan");
+  char* temp = nullptr;
+  auto keep = lease(bytes, s.stream, &temp);
+  auto e = async_event(s, std::move(keep));
+  throw_on_error(tb200_scan(temp, &bytes, n ? (const void*)raw(first) : nullptr, n ? (void*)raw(out) : nullptr, n,
+                            dtype_of<T>(), exclusive, init, e.stream().native_handle()), "tb200_scan");
+  ++fast_calls();
+  return e;
+}
+}  // namespace detail
+
+template <typename InIt, typename Sentinel, typename OutIt, typename Op>
+auto async_inclusive_scan(system& s, InIt first, Sentinel last, OutIt out, Op op) {
+  using T = detail::value_t<InIt>;
+  if constexpr (detail::scan_fast_v<InIt, OutIt, T, Op> && std::is_same<InIt, Sentinel>::value) {
+    return detail::async_scan_fast<InIt, OutIt, T>(s, first, last, out, false, nullptr);
+  } else {
+    ++detail::forwarded_calls();
+    auto inherited = detail::inherited(s);
+    return thrust::cuda_cub::async_inclusive_scan(inherited, first, last, out, op);
+  }
+}
+template <typename InIt, typename Sentinel, typename OutIt, typename Init, typename Op>
+auto async_exclusive_scan(system& s, InIt first, Sentinel last, OutIt out, Init init, Op op) {
+  if constexpr (detail::scan_fast_v<InIt, OutIt, Init, Op> && std::is_same<InIt, Sentinel>::value) {
+    return detail::async_scan_fast<InIt, OutIt, Init>(s, first, last, out, true, &init);
+  } else {
+    ++detail::forwarded_calls();
+    auto inherited = detail::inherited(s);
+    return thrust::cuda_cub::async_exclusive_scan(inherited, first, last, out, init, op);
+  }
 }
 
 }  // namespace thrust_b200

@@ -5,6 +5,8 @@
 // reference's unit tests make (testing/sort.cu:80-90, scan.cu:379-415,
 // reduce_by_key.cu:115-156). Known-answer vectors are the reference's own
 // (testing/sort.cu:42-62, sort_by_key.cu:44-70, scan.cu:44-104, reduce_by_key.cu:15-112).
+#include <thrust/async/scan.h>
+#include <thrust/async/sort.h>
 #include <thrust/device_vector.h>
 #include <thrust/host_vector.h>
 #include <thrust/iterator/counting_iterator.h>
@@ -519,6 +521,50 @@ int main() {
     CHECK(allocs1 == allocs0);  // the pool was not touched by the allocator-aware calls
     cudaStreamDestroy(s);
     CHECK(thrust::is_sorted(k.begin(), k.end()));
+  }
+
+  // ---- asynchronous forms: thrust::async::sort / inclusive_scan / exclusive_scan return events ---------
+  {
+    std::snprintf(g_ctx, sizeof g_ctx, "async");
+    thrust::host_vector<int> h = random_vec<int>(300007, 77, -1000000, 1000000);
+    thrust::device_vector<int> d = h, out(h.size());
+    cudaStream_t s;
+    cudaStreamCreate(&s);
+    const auto f0 = fast();
+    {
+      auto e = thrust::async::sort(tb::par.on(s), d.begin(), d.end());
+      CHECK(fast() == f0 + 1);
+      e.wait();
+    }
+    std::sort(h.begin(), h.end());
+    CHECK(thrust::host_vector<int>(d) == h);
+    {
+      auto e = thrust::async::inclusive_scan(tb::par.on(s), d.begin(), d.end(), out.begin());
+      e.wait();
+    }
+    thrust::host_vector<int> hs(h.size());
+    std::partial_sum(h.begin(), h.end(), hs.begin());
+    CHECK(thrust::host_vector<int>(out) == hs);
+    {
+      auto e = thrust::async::exclusive_scan(tb::par, d.begin(), d.end(), out.begin(), 5);  // default stream: the event brings its own
+      e.wait();
+    }
+    CHECK(out[0] == 5 && out[1] == 5 + h[0] && out[h.size() - 1] == 5 + hs[h.size() - 2]);
+    {
+      auto e = thrust::async::stable_sort(tb::par.on(s), d.begin(), d.end(), thrust::greater<int>());
+      e.wait();
+    }
+    CHECK(thrust::is_sorted(d.begin(), d.end(), thrust::greater<int>()));
+    CHECK(fast() == f0 + 4);
+    // a comparator of the caller's is forwarded to the inherited asynchronous sort
+    const auto w0 = fwd();
+    {
+      auto e = thrust::async::sort(tb::par.on(s), d.begin(), d.end(), less_div_10<int>());
+      e.wait();
+    }
+    CHECK(fwd() == w0 + 1);
+    CHECK(thrust::is_sorted(d.begin(), d.end(), less_div_10<int>()));
+    cudaStreamDestroy(s);
   }
 
   // ---- two host threads on the default stream: every call holds its own scratch -----------------

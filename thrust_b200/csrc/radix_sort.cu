@@ -406,6 +406,32 @@ __device__ __forceinline__ unsigned match_digit_bits(unsigned d, int bits) {
   return peers;
 }
 
+// Copies `len` elements from shared memory to global memory with all THREADS threads of the CTA:
+// element by element up to the first 16-byte boundary of the destination, 16 bytes per thread
+// from there, element by element for what is left.
+template <typename T, int THREADS>
+__device__ __forceinline__ void copy_run(T* __restrict__ dst, const T* __restrict__ src, unsigned len) {
+  constexpr unsigned VEC = 16 / sizeof(T);
+  if constexpr (VEC <= 1) {
+    for (unsigned i = threadIdx.x; i < len; i += THREADS) dst[i] = src[i];
+  } else {
+    unsigned head = (unsigned)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(dst) & 15u)) & 15u) / sizeof(T));
+    if (head > len) head = len;
+    if (threadIdx.x < head) dst[threadIdx.x] = src[threadIdx.x];
+    const unsigned nvec = (len - head) / VEC;
+    struct alignas(16) Vec { T v[VEC]; };
+    Vec* vdst = reinterpret_cast<Vec*>(dst + head);
+    for (unsigned i = threadIdx.x; i < nvec; i += THREADS) {
+      Vec x;
+#pragma unroll
+      for (unsigned e = 0; e < VEC; ++e) x.v[e] = src[head + i * VEC + e];
+      vdst[i] = x;
+    }
+    const unsigned done = head + nvec * VEC;
+    if (threadIdx.x < len - done) dst[done + threadIdx.x] = src[done + threadIdx.x];
+  }
+}
+
 template <typename UK, int VB, int THREADS, int ITEMS>
 struct PassShape {
   using V = typename ValueOf<VB>::type;
@@ -451,6 +477,7 @@ onesweep_kernel(const PassParams prm) {
   __shared__ unsigned s_scan[kRadix / kWarp];
   __shared__ unsigned s_next;
   __shared__ UK s_split[SPLIT ? kRadix : 1];
+  __shared__ unsigned s_run_start[SPLIT ? kRadix : 1], s_run_len[SPLIT ? kRadix : 1];  // partition: runs of the parked tile
   __shared__ UK* s_bucket_keys[SPLIT ? kRadix : 1];
   __shared__ V* s_bucket_vals[SPLIT ? kRadix : 1];
 
@@ -612,9 +639,28 @@ onesweep_kernel(const PassParams prm) {
           st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | (DescT)((excl + p_count) & DescBits<DescT>::kValueMask));
         }
         s_gbase[d] = (IdxT)(pass_offset + excl - p_digit_start);
+        if constexpr (SPLIT) {
+          s_run_start[d] = p_digit_start;
+          s_run_len[d] = p_count;
+        }
       }
       __syncthreads();
       // ---- scatter: every digit leaves as one contiguous run
+      if constexpr (SPLIT) {
+        if (num_split < 16u) {
+          // Few buckets (one per GPU): every bucket's run is long, so the CTA copies run after run
+          // with 16-byte stores once the destination is 16-byte aligned (a few elements in front
+          // and behind go one by one). Wide stores matter when the destination is another GPU:
+          // NVLink moves them in larger packets.
+          for (unsigned b = 0; b <= num_split; ++b) {
+            const unsigned start = s_run_start[b], len = s_run_len[b];
+            const IdxT g0 = s_gbase[b] + start;
+            copy_run<UK, THREADS>(s_bucket_keys[b] + g0, s_keys + start, len);
+            if constexpr (VB != 0) copy_run<V, THREADS>(s_bucket_vals[b] + g0, s_vals + start, len);
+          }
+          return;
+        }
+      }
       auto emit = [&](unsigned pos) {
         const UK k = s_keys[pos];
         if constexpr (SPLIT) {
