@@ -91,6 +91,20 @@ __device__ __forceinline__ int ld_relaxed_s32(const int* p) {
   return v;
 }
 
+// Raises the status word after a bounded wait ran out and records where: the FIRST wait to give
+// up writes aux[0] = site, aux[1..2] = what it waited for, aux[3] = CTA | thread << 32 of the
+// scratch header (every later time-out is a consequence of the first).
+enum : unsigned { kSiteLookback = 1, kSiteBlockChain = 2, kSiteCloser = 3, kSiteIdle = 4, kSiteMbarrier = 5 };
+__device__ __forceinline__ void note_timeout(int* status, unsigned site, unsigned long long x, unsigned long long y) {
+  unsigned long long* aux = reinterpret_cast<unsigned long long*>(status) + 1;  // TempHeader::aux
+  if (atomicCAS(&aux[0], 0ull, (unsigned long long)site) == 0ull) {
+    aux[1] = x;
+    aux[2] = y;
+    aux[3] = (unsigned long long)blockIdx.x | ((unsigned long long)threadIdx.x << 32);
+  }
+  atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+}
+
 __device__ __forceinline__ void backoff(unsigned polls) {
 #if defined(TB200_EXPERIMENT_SLEEP_NS)
   __nanosleep(TB200_EXPERIMENT_SLEEP_NS);
@@ -194,7 +208,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, unsig
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 1023u) == 1023u && ld_relaxed_s32(status) != 0) return false;  // someone else gave up
   }
-  atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+  note_timeout(status, kSiteMbarrier, smem_u32(bar), parity);
   return false;
 }
 

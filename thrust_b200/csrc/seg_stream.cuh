@@ -159,6 +159,60 @@ __device__ void lookback_chain(const TileWords<4>* tiles, unsigned tile, int* st
   out_val = acc_val;
 }
 
+// Look-back of the segmented scans (scan_by_key). Only the run that is open at the end of the
+// predecessors matters, so a tile that contains a head is final the moment it is scanned: such a
+// tile publishes its trailing run sum as PREFIX at once, a tile without a head publishes its
+// total as AGGREGATE and, once its own look-back is done, the open run's sum as PREFIX. The walk
+// goes back to the NEAREST prefix and waits for nothing older: with a head in most tiles that is
+// the tile directly in front, not the slowest of all tiles in flight.
+template <typename A>
+__device__ void lookback_short(const TileWords<4>* tiles, unsigned tile, int* status, A& out_val) {
+  const unsigned lane = lane_id();
+  A acc = A(0);
+  long long base = (long long)tile - 1;
+  bool timed_out = false;
+  unsigned long long missing = 0;
+  while (base >= 0 && !timed_out) {
+    const long long idx = base - lane;
+    unsigned st = kStatePrefix;  // in front of the first tile: an empty prefix
+    unsigned payload[4] = {0u, 0u, 0u, 0u};
+    unsigned polls = 0, first = 0;
+    bool unread = idx >= 0;  // this lane's descriptor has not been seen published yet
+    while (true) {
+      if (unread) {
+        st = peek<4>(&tiles[idx], payload);
+        unread = st == kStateEmpty;
+      }
+      const unsigned pm = __ballot_sync(0xffffffffu, st == kStatePrefix);
+      const unsigned em = __ballot_sync(0xffffffffu, st == kStateEmpty);
+      first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
+      const unsigned needed = first == 31u ? 0xffffffffu : ((2u << first) - 1u);  // lanes up to the nearest prefix
+      if ((em & needed) == 0u) break;
+      backoff(++polls);
+      if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+        timed_out = true;
+        missing = (unsigned long long)(base - (__ffs(em & needed) - 1));
+        break;
+      }
+    }
+    unsigned long long cnt = 0;
+    A val = A(0);
+    if (idx >= 0 && lane <= first && st != kStateEmpty) DescWords<A>::unpack(payload, cnt, val);
+    const bool done = __any_sync(0xffffffffu, st == kStatePrefix);
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {  // ordered sum: farther tiles (higher lanes) on the left
+      const A ov = __shfl_down_sync(0xffffffffu, val, off);
+      if (lane + off < 32) val = ov + val;
+    }
+    val = __shfl_sync(0xffffffffu, val, 0);
+    acc = val + acc;
+    if (done) break;
+    base -= 32;
+  }
+  if (timed_out && lane == 0) note_timeout(status, kSiteLookback, tile, missing);
+  out_val = acc;
+}
+
 constexpr int kBlockTiles = 32;  // tiles per block of the two-level chain (one lane per tile)
 enum : unsigned { kStateInclusive = 2 };  // block descriptors: EMPTY -> AGGREGATE -> INCLUSIVE prefix
 
@@ -206,7 +260,7 @@ __device__ void close_block(const TileWords<4>* tiles, TileWords<4>* blocks, uns
     }
   }
   if (!__all_sync(0xffffffffu, ok)) {
-    if (lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+    if (lane == 0) note_timeout(status, kSiteCloser, b, 0);
     return;
   }
   if (lane == 0) {
@@ -336,13 +390,16 @@ __device__ void resolve(const TileWords<4>* tiles, TileWords<4>* blocks, unsigne
       timed_out = true;
     }
   }
-  if (__any_sync(0xffffffffu, timed_out) && lane == 0) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+  if (__any_sync(0xffffffffu, timed_out) && lane == 0) note_timeout(status, kSiteBlockChain, tile, 0);
 }
 
-constexpr int kComputeWarps = 8;
+constexpr int kComputeWarps = 8;  // warps of one team: a tile is split over them
 constexpr int kComputeThreads = kComputeWarps * kWarp;
+constexpr int kTeams = 2;      // teams of compute warps; tile j of a CTA belongs to team j % kTeams
 constexpr int kLookWarps = 3;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
-constexpr int kCtaThreads = kComputeThreads + (kLookWarps + 2) * kWarp;  // + look-back warps + closer + producer
+constexpr int kStops = kLookWarps > kTeams ? kLookWarps : kTeams;  // "no tile" slots that end the roles
+constexpr int kRoleWarp0 = kTeams * kComputeWarps;  // first warp that is not a compute warp
+constexpr int kCtaThreads = (kRoleWarp0 + kLookWarps + 2) * kWarp;  // + look-back warps + closer + producer
 constexpr int kPacks = 5;   // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
 constexpr int kStages = 5;  // ring slots: one or two loading, one being scanned, the rest parked
 constexpr unsigned kNoTile = 0xffffffffu;
@@ -419,6 +476,9 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
 
   const unsigned warp = threadIdx.x / kWarp;
   const unsigned lane = lane_id();
+  const unsigned team = warp / NW;                         // compute warps: the team ...
+  const unsigned w = warp % NW;                            // ... the warp's place in it ...
+  const unsigned tid = threadIdx.x % kComputeThreads;      // ... and the thread's
   int* status = &a.hdr->status;
   const uint64_t n = a.n;
   const unsigned num_tiles = a.num_tiles;
@@ -442,6 +502,25 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
   };
 
+  // A parity wait tells "phase r completed" apart from "not yet" only for an observer that is at
+  // most one phase away from the barrier. A slot's successive tiles go to DIFFERENT teams and
+  // look-back warps, and tiles land out of order when several loads are in flight, so a warp that
+  // has finished tile j-2 or j-3 may ask for tile j while the slot's previous tenant, tile j-NS, has
+  // not even landed: the parity test would then answer for the phase before. Whoever did not
+  // handle the previous tenant itself therefore first checks that the tenant has been FREED
+  // (that barrier it cannot be two phases away from: tile j-NS is issued before every tile the
+  // warp has seen, and only after tile j-2NS was freed).
+  auto landed = [&](unsigned jj) -> bool {  // non-blocking: tile jj of the CTA is in its slot
+    const int s = jj % NS;
+    const unsigned r = jj / NS;
+    return (r == 0 || ready(&s_freed[s], (r - 1u) & 1u)) && ready(&s_full[s], r & 1u);
+  };
+  auto wait_landed = [&](unsigned jj) -> bool {  // blocking (bounded)
+    const int s = jj % NS;
+    const unsigned r = jj / NS;
+    return (r == 0 || wait_all(&s_freed[s], (r - 1u) & 1u)) && wait_all(&s_full[s], r & 1u);
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&s_full[s], 1);
@@ -450,12 +529,18 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       mbar_init(&s_freed[s], NW);
       s_arrivals[s] = 0;
     }
+    if (blockIdx.x == 0) {  // decodes a recorded mbarrier time-out
+      a.hdr->aux[4] = smem_u32(&s_full[0]);
+      a.hdr->aux[5] = smem_u32(&s_scanned[0]);
+      a.hdr->aux[6] = smem_u32(&s_resolved[0]);
+      a.hdr->aux[7] = smem_u32(&s_freed[0]);
+    }
     mbar_init_fence();
   }
   __syncthreads();  // the only CTA-wide barrier of the kernel
 
   // ---------------------------------------------------------------------- producer
-  if (warp == NW + kLookWarps + 1) {
+  if (warp == kRoleWarp0 + kLookWarps + 1) {
     if (lane != 0) return;
     // tile t goes into `slot`; false when the tickets have run past the last tile
     auto issue = [&](int slot, unsigned t) -> bool {
@@ -479,21 +564,21 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       return true;
     };
-    // After the last tile, kLookWarps further slots are marked "no tile": every look-back warp
-    // meets one and stops.
+    // After the last tile, kStops further slots are marked "no tile": every look-back warp and
+    // every team of compute warps meets one and stops.
     // The first ring-full is drawn one ticket at a time, each after the previous tile has landed:
     // all CTAs start together, so their draws interleave and a CTA's k-th tile comes k rounds
     // after its first in ticket order too. (Drawn in one burst, a CTA's first tiles would be
     // consecutive tickets; every other CTA's first look-back would then wait for tiles this CTA
     // scans several iterations later, and the whole grid would start up one CTA after the other.)
     int stops = 0;
-    for (int s = 0; s < NS && stops < kLookWarps; ++s) {
+    for (int s = 0; s < NS && stops < kStops; ++s) {
       if (!issue(s, stops ? kNoTile : atomicAdd(&a.hdr->ticket, 1u))) ++stops;
       if (!mbar_wait_bounded(&s_full[s], 0u, status)) return;
     }
     // A ticket is drawn only when its slot is free: a drawn tile starts loading at once, so no
     // tile that successors will wait for sits idle.
-    for (unsigned j = NS; stops < kLookWarps; ++j) {
+    for (unsigned j = NS; stops < kStops; ++j) {
       const int slot = j % NS;
       if (!mbar_wait_bounded(&s_freed[slot], ((j / NS) - 1u) & 1u, status)) return;
       if (!issue(slot, stops ? kNoTile : atomicAdd(&a.hdr->ticket, 1u))) ++stops;
@@ -502,7 +587,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   }
 
   // ---------------------------------------------------------------------- closer warp
-  if (warp == NW + kLookWarps) {
+  if (warp == kRoleWarp0 + kLookWarps) {
+    if constexpr (kScanOut) return;  // the segmented scans' chain has one level
     for (unsigned j = 0;; ++j) {
       const int slot = j % NS;
       if (!wait_all(&s_full[slot], (j / NS) & 1u)) return;
@@ -514,11 +600,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   }
 
   // ---------------------------------------------------------------------- look-back warp
-  if (warp >= NW) {
-    for (unsigned j = warp - NW;; j += kLookWarps) {
+  if (warp >= kRoleWarp0) {
+    for (unsigned j = warp - kRoleWarp0;; j += kLookWarps) {
       const int slot = j % NS;
       const unsigned par = (j / NS) & 1u;
-      if (!wait_all(&s_full[slot], par)) return;
+      if (!wait_landed(j)) return;
       const unsigned tile = s_tile[slot];
       if (tile == kNoTile) return;
       if (!wait_all(&s_scanned[slot], par)) return;
@@ -531,7 +617,16 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       unsigned long long pc = 0;
       A pv = A(0);
-      resolve<A>(a.tiles, a.blocks, tile, total.cnt, total.val, status, pc, pv);
+      if constexpr (kScanOut) {
+        lookback_short<A>(a.tiles, tile, status, pv);
+        if (total.cnt == 0 && lane == 0) {  // no head in the tile: the run open in front of it goes on
+          unsigned payload[4];
+          DescWords<A>::pack(0ull, pv + total.val, payload);
+          publish<4>(&a.tiles[tile], kStatePrefix, payload);  // second writer of the descriptor, ordered after the first by the `scanned` barrier
+        }
+      } else {
+        resolve<A>(a.tiles, a.blocks, tile, total.cnt, total.val, status, pc, pv);
+      }
       if (lane == 0) {
         const unsigned long long ic = pc + total.cnt;
         const A iv = total.cnt ? total.val : pv + total.val;
@@ -552,7 +647,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   }
 
   // ---------------------------------------------------------------------- compute warps
-  const unsigned my_off = threadIdx.x * ITEMS;  // first element of this thread inside a tile
+  const unsigned my_off = tid * ITEMS;  // first element of this thread inside a tile
   struct Parked {
     unsigned heads, cnt;
     A val;
@@ -564,23 +659,23 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     const int slot = jj % NS;
     if (!wait_all(&s_resolved[slot], (jj / NS) & 1u)) return false;  // returns at once: the caller saw it complete
     Parked st;
-    st.heads = s_park_heads[slot][threadIdx.x];
-    st.cnt = s_park_cnt[slot][threadIdx.x];
+    st.heads = s_park_heads[slot][tid];
+    st.cnt = s_park_cnt[slot][tid];
     st.val = A(0);
-    if constexpr (kSum) st.val = s_park_val[slot][threadIdx.x];
-    st.fh = s_park_fh[slot][warp];
+    if constexpr (kSum) st.val = s_park_val[slot][tid];
+    st.fh = s_park_fh[slot][w];
     const unsigned tile = s_tile[slot];
     const uint64_t tile_base = (uint64_t)tile * TILE;
     const K* sk = slot_keys(slot);
     const V* sv = slot_vals(slot);
-    const unsigned long long wcnt = s_wpre_cnt[slot][warp];
+    const unsigned long long wcnt = s_wpre_cnt[slot][w];
     A wval = A(0);
-    if constexpr (kSum) wval = s_wpre_val[slot][warp];
+    if constexpr (kSum) wval = s_wpre_val[slot][w];
     if constexpr (kScanOut) {
       // the parked values are complete up to the warp's first head; in front of it the run
       // that was open at the start of the slice continues
-      const Pack<V, E>* src = reinterpret_cast<const Pack<V, E>*>(sv + warp * S::kWarpItems);
-      const uint64_t warp_base = tile_base + (uint64_t)warp * S::kWarpItems;
+      const Pack<V, E>* src = reinterpret_cast<const Pack<V, E>*>(sv + w * S::kWarpItems);
+      const uint64_t warp_base = tile_base + (uint64_t)w * S::kWarpItems;
       const bool whole = (uint64_t)(tile + 1) * TILE <= n && a.bulk;  // a.bulk: the output is 16-byte aligned too
 #pragma unroll
       for (int p = 0; p < kPacks; ++p) {
@@ -635,20 +730,20 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   // tile's aggregate reaches the other CTAs as early as possible, whatever this CTA is still
   // waiting for) and emits the oldest parked tile as soon as its prefix is resolved; it idles
   // only when neither is possible.
-  unsigned j = 0;       // next tile of the CTA to scan
-  unsigned j_emit = 0;  // oldest scanned tile not yet emitted
+  unsigned j = team;       // next tile of the CTA for this team to scan
+  unsigned j_emit = team;  // the team's oldest scanned tile not yet emitted
   bool more = true;     // the producer has not run out of tiles
   unsigned idle = 0;
   while (more || j_emit < j) {
     if (j_emit < j && ready(&s_resolved[j_emit % NS], (j_emit / NS) & 1u)) {
       if (!phase_c(j_emit)) return;
-      ++j_emit;
+      j_emit += kTeams;
       idle = 0;
       continue;
     }
-    if (!(more && ready(&s_full[j % NS], (j / NS) & 1u))) {
+    if (!(more && landed(j))) {
       if (++idle > (1u << 24) || ((idle & 4095u) == 0 && ld_relaxed_s32(status) != 0)) {  // bounded
-        if (lane == 0 && idle > (1u << 24)) atomicExch(status, (int)TB200_ERR_WAIT_TIMEOUT);
+        if (lane == 0 && idle > (1u << 24)) note_timeout(status, kSiteIdle, ((unsigned long long)j << 32) | j_emit, team);
         return;
       }
       if (idle > 64) __nanosleep(40);
@@ -712,7 +807,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       // key in front of this thread's items
       K prev = __shfl_up_sync(0xffffffffu, k[ITEMS - 1], 1);
       if (lane == 0) {
-        if (staged && warp > 0) prev = sk[my_off - 1];
+        if (staged && w > 0) prev = sk[my_off - 1];
         else if (staged && tile != 0) prev = *reinterpret_cast<const K*>(&s_halo[slot][16 - sizeof(K)]);
         else prev = (my_base > 0 && my_base <= n) ? a.keys[my_base - 1] : K{};
       }
@@ -748,8 +843,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     now.val = kSum ? __shfl_up_sync(0xffffffffu, s.val, 1) : A(0);
     if (lane == 0) { now.cnt = 0; now.val = A(0); }
     if (lane == 31) {
-      s_wtot_cnt[slot][warp] = s.cnt;
-      if constexpr (kSum) s_wtot_val[slot][warp] = s.val;
+      s_wtot_cnt[slot][w] = s.cnt;
+      if constexpr (kSum) s_wtot_val[slot][w] = s.val;
     }
     // ---- park what phase C needs in the tile's own slot
     if constexpr (MODE == kReduceByKey) {
@@ -792,10 +887,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       now.fh = fh;
     }
-    s_park_heads[slot][threadIdx.x] = now.heads;
-    s_park_cnt[slot][threadIdx.x] = now.cnt;
-    if constexpr (kSum) s_park_val[slot][threadIdx.x] = now.val;
-    if (lane == 0) s_park_fh[slot][warp] = now.fh;
+    s_park_heads[slot][tid] = now.heads;
+    s_park_cnt[slot][tid] = now.cnt;
+    if constexpr (kSum) s_park_val[slot][tid] = now.val;
+    if (lane == 0) s_park_fh[slot][w] = now.fh;
     __syncwarp();
     // The last warp to finish phase A of this tile combines the warp totals (in warp order) and
     // publishes the tile's aggregate.
@@ -832,14 +927,15 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
         if constexpr (kSum) s_tot_val[slot] = inc.val;
         unsigned payload[4];
         DescWords<A>::pack(inc.cnt, inc.val, payload);
-        publish<4>(&a.tiles[tile], kStateAggregate, payload);  // plain stores: nothing is waited for
+        // plain stores: nothing is waited for. A segmented scan's tile that holds a head is final.
+        publish<4>(&a.tiles[tile], (kScanOut && inc.cnt) ? kStatePrefix : kStateAggregate, payload);
         s_arrivals[slot] = 0;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_scanned[slot]);  // hands the tile to its look-back warp
     }
 
-    ++j;
+    j += kTeams;
   }
 }
 
