@@ -213,193 +213,195 @@ __device__ void lookback_short(const TileWords<4>* tiles, unsigned tile, int* st
   out_val = acc;
 }
 
-constexpr int kBlockTiles = 32;  // tiles per block of the two-level chain (one lane per tile)
-enum : unsigned { kStateInclusive = 2 };  // block descriptors: EMPTY -> AGGREGATE -> INCLUSIVE prefix
+constexpr int kBlockTiles = 32;  // tiles per block of the count chain (one lane per tile)
 
-// Polls one descriptor until it is published (bounded); false on time-out.
-__device__ __forceinline__ bool poll_desc(const TileWords<4>* d, unsigned& st, unsigned (&payload)[4], int* status) {
+// ---- the count chain of the compacting algorithms (reduce_by_key, unique, copy of flagged) ----
+// Where a tile's output goes depends on the number of heads in ALL tiles in front of it, and a
+// GPU at full HBM speed has hundreds of tiles in flight, some of them always a few microseconds
+// late: a tile that waited for that count with its data parked in shared memory would hold its
+// slot for most of its life. The counts are therefore produced AHEAD of the data by scout warps:
+// a scout draws a tile from its own ticket counter, reads only the tile's keys (plain loads, no
+// shared memory), counts the heads and publishes the count; the scout of a block's last tile
+// adds up the block and resolves the block's prefix by look-back over the block descriptors.
+// The scouts run a bounded number of tiles in front of the data tickets, so the keys they read
+// are still in L2 when the data path loads them again, and a data tile finds its prefix already
+// resolved: two descriptor reads, no waiting.
+//   ctiles[t]  one word {state | heads in tile t}                         EMPTY -> AGGREGATE
+//   cblocks[b] {0, heads in block b} then {0, heads in blocks 0..b}       EMPTY -> AGGREGATE -> PREFIX
+__device__ __forceinline__ bool poll_count(const TileWords<1>* d, unsigned& cnt, int* status) {
   unsigned polls = 0;
-  while ((st = peek<4>(d, payload)) == kStateEmpty) {
+  while (true) {
+    const unsigned long long v = ld_relaxed_u64(&d->w[0]);
+    if ((unsigned)(v >> 32) != kStateEmpty) {
+      cnt = (unsigned)v;
+      return true;
+    }
     backoff(++polls);
     if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) return false;
   }
-  return true;
-}
-// Same, continuing from a first peek whose outcome is (st, payload).
-__device__ __forceinline__ bool poll_more(const TileWords<4>* d, unsigned& st, unsigned (&payload)[4], int* status) {
-  unsigned polls = 0;
-  while (st == kStateEmpty) {
-    backoff(++polls);
-    if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) return false;
-    st = peek<4>(d, payload);
-  }
-  return true;
 }
 
-// Waits for the aggregates of all tiles of block b, combines them in tile order and publishes the
-// block's aggregate (one warp, all lanes).
-template <typename A>
-__device__ void close_block(const TileWords<4>* tiles, TileWords<4>* blocks, unsigned b, unsigned tiles_in_block,
-                            int* status) {
+// Heads in tiles [first, first + count) of one block, count <= 32 (one warp, all lanes).
+__device__ __forceinline__ unsigned long long block_part(const TileWords<1>* ctiles, unsigned first, unsigned count,
+                                                         int* status) {
   const unsigned lane = lane_id();
-  unsigned long long cnt = 0;
-  A val = A(0);
+  unsigned c = 0;
   bool ok = true;
-  if (lane < tiles_in_block) {
-    unsigned st, payload[4];
-    ok = poll_desc(&tiles[(size_t)b * kBlockTiles + lane], st, payload, status);
-    if (ok) DescWords<A>::unpack(payload, cnt, val);
-  }
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
-    const A ov = __shfl_down_sync(0xffffffffu, val, off);
-    if (lane + off < 32) {  // (oc, ov) lies to the RIGHT of (cnt, val)
-      val = oc ? ov : val + ov;
-      cnt = cnt + oc;
-    }
-  }
+  if (lane < count) ok = poll_count(&ctiles[first + lane], c, status);
   if (!__all_sync(0xffffffffu, ok)) {
-    if (lane == 0) note_timeout(status, kSiteCloser, b, 0);
-    return;
+    if (lane == 0) note_timeout(status, kSiteBlockChain, first, count);
+    return 0;
   }
+  return (unsigned long long)__reduce_add_sync(0xffffffffu, c);
+}
+
+// Number of heads in front of `tile` (one warp, all lanes).
+__device__ __forceinline__ unsigned long long count_prefix(const TileWords<1>* ctiles, const TileWords<4>* cblocks,
+                                                           unsigned tile, int* status) {
+  const unsigned b = tile / kBlockTiles;
+  const unsigned long long inside = block_part(ctiles, b * kBlockTiles, tile % kBlockTiles, status);
+  unsigned long long before = 0;
+  lookback_short<unsigned long long>(cblocks, b, status, before);
+  return before + inside;
+}
+
+// The scout of a block's last tile: the block's aggregate, then its inclusive prefix.
+__device__ __forceinline__ void close_block(const TileWords<1>* ctiles, TileWords<4>* cblocks, unsigned b,
+                                            unsigned tiles_in_block, int* status) {
+  const unsigned lane = lane_id();
+  const unsigned long long agg = block_part(ctiles, b * kBlockTiles, tiles_in_block, status);
+  unsigned payload[4];
   if (lane == 0) {
-    unsigned payload[4];
-    DescWords<A>::pack(cnt, val, payload);
-    publish<4>(&blocks[b], kStateAggregate, payload);
+    DescWords<unsigned long long>::pack(0ull, agg, payload);
+    publish<4>(&cblocks[b], kStateAggregate, payload);
+  }
+  unsigned long long before = 0;
+  lookback_short<unsigned long long>(cblocks, b, status, before);
+  if (lane == 0) {  // same thread as the aggregate: the two sets of words cannot mix
+    DescWords<unsigned long long>::pack(0ull, before + agg, payload);
+    publish<4>(&cblocks[b], kStatePrefix, payload);
   }
 }
 
-// Resolves the state of the scan in front of `tile` (one warp, all lanes), in two levels that are
-// read together:
-//  * the aggregates of the tiles in front of it in its own block AND in the kDirectBlocks blocks
-//    before that, read directly (a contiguous run of descriptors per lane, combined in order):
-//    blocks that young have usually not been closed yet, and waiting for their closers would add
-//    a round trip per level to every tile;
-//  * the prefix of the oldest block read directly, by a decoupled look-back over the BLOCK
-//    descriptors behind it (lane l reads block first-1-l; the walk stops at the nearest
-//    inclusive prefix). Those blocks closed long ago.
-// The block's last tile also publishes the block's inclusive prefix. `total` is the tile's own
-// aggregate.
-constexpr int kDirectBlocks = 0;  // measured on B200: every further block read tile by tile costs more descriptor traffic than its closer's delay
-constexpr int kDirectPerLane = (kDirectBlocks * kBlockTiles + kBlockTiles - 1 + kWarp - 1) / kWarp;  
+// Asks the memory system to bring [p, p + bytes) into L2 (16-byte aligned, a multiple of 16 bytes):
+// the bytes are in flight without a register or a shared-memory destination waiting for them.
+__device__ __forceinline__ void prefetch_l2(const void* p, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {  // read-only, not kept in L1
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
 
-template <typename A>
-__device__ void resolve(const TileWords<4>* tiles, TileWords<4>* blocks, unsigned tile, unsigned total_cnt, A total_val,
-                        int* status, unsigned long long& out_cnt, A& out_val) {
+// Heads (FLAGS: non-zero elements) of one whole tile of NP 16-byte packs that starts at the
+// 16-byte aligned keys + base; one warp. The scouts share their SM's issue slots with sixteen
+// compute warps, so what counts here is the number of instructions per pack: lane-strided
+// 16-byte loads kept U deep in flight (a pack is counted, then its buffer is loaded again), the
+// element in front of a pack from the neighbouring lane by one shuffle, and the first element of
+// every row (lane 0 has no neighbour) compared with its predecessor in a pass of its own: a
+// lane per row, two small loads each, issued before the packs and added at the end.
+template <typename K, bool FLAGS, int NP>
+__device__ unsigned count_heads_tile(const K* keys, uint64_t base) {
+  constexpr int EP = 16 / (int)sizeof(K);
+  constexpr int ROWS = (NP + kWarp - 1) / kWarp;
+  constexpr int U = ROWS < 8 ? ROWS : 8;
+  constexpr bool kRagged = NP % kWarp != 0;  // the last row is not full
   const unsigned lane = lane_id();
-  const unsigned b = tile / kBlockTiles, i = tile % kBlockTiles;
-  bool timed_out = false;
-  const unsigned first_block = b >= (unsigned)kDirectBlocks ? b - kDirectBlocks : 0u;  // oldest block read tile by tile
-  const unsigned lo = first_block * kBlockTiles;
-  const unsigned count = tile - lo;  // tiles read directly: [lo, tile)
-
-  // ---- issue every first read: this lane's run of tile descriptors and its block descriptor
-  unsigned st_t[kDirectPerLane], pay_t[kDirectPerLane][4];
-  const unsigned my_first = lo + lane * kDirectPerLane;
+  const uint4* src = reinterpret_cast<const uint4*>(keys + base);
+  unsigned row_heads = 0;  // heads among the first elements of the rows
+  if constexpr (!FLAGS) {
 #pragma unroll
-  for (int m = 0; m < kDirectPerLane; ++m) {
-    st_t[m] = kStateAggregate;
-    if (lane * kDirectPerLane + m < count) st_t[m] = peek<4>(&tiles[my_first + m], pay_t[m]);
-  }
-  unsigned st_b = kStateInclusive, pay_b[4];
-  const long long first_idx = (long long)first_block - 1 - lane;
-  if (first_idx >= 0) st_b = peek<4>(&blocks[first_idx], pay_b);
-
-  // ---- tiles read directly, in tile order: each lane combines its run, then the lanes in order
-  unsigned long long icnt = 0;
-  A ival = A(0);
-#pragma unroll
-  for (int m = 0; m < kDirectPerLane; ++m) {
-    if (lane * kDirectPerLane + m < count) {
-      unsigned long long c = 0;
-      A v = A(0);
-      if (poll_more(&tiles[my_first + m], st_t[m], pay_t[m], status)) DescWords<A>::unpack(pay_t[m], c, v);
-      else timed_out = true;
-      ival = c ? v : ival + v;  // (c, v) lies to the RIGHT of what this lane has
-      icnt = icnt + c;
+    for (int r = 0; r < ROWS; r += kWarp) {
+      const uint64_t g = base + (uint64_t)(r + lane) * kWarp * EP;
+      if (r + (int)lane < ROWS) row_heads += (unsigned)(g == 0 || !(keys[g] == keys[g - 1]));
     }
   }
+  uint4 q[U];
+  auto load = [&](int r, uint4& qq) {
+    const unsigned pk = (unsigned)r * kWarp + lane;
+    qq = (!kRagged || pk < (unsigned)NP) ? ld_stream_v4(src + pk) : uint4{0u, 0u, 0u, 0u};
+  };
 #pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {  // ordered reduction: lane l holds l (+) l+1 (+) ...
-    const unsigned long long oc = __shfl_down_sync(0xffffffffu, icnt, off);
-    const A ov = __shfl_down_sync(0xffffffffu, ival, off);
-    if (lane + off < 32) {  // (oc, ov) lies to the RIGHT of (icnt, ival)
-      ival = oc ? ov : ival + ov;
-      icnt = icnt + oc;
+  for (int u = 0; u < U; ++u) load(u, q[u]);
+  unsigned cnt = 0;
+#pragma unroll 1
+  for (int r0 = 0; r0 < ROWS; r0 += U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u;
+      if (ROWS % U == 0 || r < ROWS) {  // the same for all lanes
+        const Pack<K, EP> e = *reinterpret_cast<const Pack<K, EP>*>(&q[u]);
+        if (r + U < ROWS) load(r + U, q[u]);
+        const bool in = !kRagged || (unsigned)r * kWarp + lane < (unsigned)NP;
+        if constexpr (FLAGS) {
+          unsigned c = 0;
+#pragma unroll
+          for (int i = 0; i < EP; ++i) c += (unsigned)(e.v[i] != K(0));
+          cnt += in ? c : 0u;
+        } else {
+          const K prev = __shfl_up_sync(0xffffffffu, e.v[EP - 1], 1);
+          unsigned c = lane == 0 ? 0u : (unsigned)!(e.v[0] == prev);  // lane 0's first element: counted in row_heads
+#pragma unroll
+          for (int i = 1; i < EP; ++i) c += (unsigned)!(e.v[i] == e.v[i - 1]);
+          cnt += in ? c : 0u;
+        }
+      }
     }
   }
-  icnt = __shfl_sync(0xffffffffu, icnt, 0);
-  ival = __shfl_sync(0xffffffffu, ival, 0);
+  return __reduce_add_sync(0xffffffffu, cnt + row_heads);
+}
 
-  // ---- prefix of block `first_block`: look-back over the block descriptors behind it
-  unsigned long long pcnt = 0;
-  A pval = A(0);
-  long long base = (long long)first_block - 1;
-  while (base >= 0) {
-    const long long idx = base - lane;
-    unsigned st = kStateInclusive;
-    unsigned long long cnt = 0;
-    A val = A(0);
-    if (idx >= 0) {
-      unsigned payload[4];
-      bool ok;
-      if (base == (long long)first_block - 1) {  // first window: continue from the read issued above
-        ok = poll_more(&blocks[idx], st_b, pay_b, status);
-        st = st_b;
+// The same for any `count` elements of keys[base, base + count): the last tile of an input and
+// inputs that are not 16-byte aligned. Element-wise, coalesced; one warp.
+template <typename K, bool FLAGS>
+__device__ unsigned count_heads_any(const K* keys, uint64_t base, unsigned count, uint64_t n) {
+  const unsigned lane = lane_id();
+  constexpr int U = 8;
+  unsigned cnt = 0;
+  K carry = K{};  // element in front of lane 0's next one
+  if (!FLAGS && base > 0) carry = keys[base - 1];
+  for (unsigned i0 = 0; i0 < count; i0 += kWarp * U) {
+    K e[U];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) payload[w] = pay_b[w];
+    for (int u = 0; u < U; ++u) {
+      const uint64_t g = base + i0 + u * kWarp + lane;
+      e[u] = (i0 + u * kWarp + lane < count && g < n) ? keys[g] : K{};
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t g = base + i0 + u * kWarp + lane;
+      const bool in = i0 + u * kWarp + lane < count && g < n;
+      if constexpr (FLAGS) {
+        cnt += (unsigned)(in && e[u] != K(0));
       } else {
-        ok = poll_desc(&blocks[idx], st, payload, status);
-      }
-      if (ok) DescWords<A>::unpack(payload, cnt, val);
-      else { timed_out = true; st = kStateInclusive; }
-    }
-    const unsigned pm = __ballot_sync(0xffffffffu, st == kStateInclusive);
-    const unsigned first = pm ? (unsigned)(__ffs(pm) - 1) : 31u;
-    if (lane > first) { cnt = 0; val = A(0); }
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const unsigned long long oc = __shfl_down_sync(0xffffffffu, cnt, off);
-      const A ov = __shfl_down_sync(0xffffffffu, val, off);
-      if (lane + off < 32) {  // (oc, ov) lies to the LEFT of (cnt, val): farther blocks sit in higher lanes
-        val = cnt ? val : ov + val;
-        cnt = oc + cnt;
+        K prev = __shfl_up_sync(0xffffffffu, e[u], 1);
+        const K wrap = __shfl_sync(0xffffffffu, e[u], 31);
+        if (lane == 0) prev = carry;
+        carry = wrap;
+        cnt += (unsigned)(in && (g == 0 || !(e[u] == prev)));
       }
     }
-    cnt = __shfl_sync(0xffffffffu, cnt, 0);
-    val = __shfl_sync(0xffffffffu, val, 0);
-    pval = pcnt ? pval : val + pval;  // this window lies to the left of what is accumulated
-    pcnt = cnt + pcnt;
-    if (pm) break;
-    base -= 32;
   }
-  // state in front of the tile = (prefix of first_block) (+) (tiles read directly)
-  out_cnt = pcnt + icnt;
-  out_val = icnt ? ival : pval + ival;
-  if (i == kBlockTiles - 1 && lane == 0) {
-    // The block descriptor has two writers, in this order: the closer warp (aggregate), then this
-    // one (inclusive prefix). Wait for the first, or the two sets of words could mix.
-    unsigned st, payload[4];
-    if (poll_desc(&blocks[b], st, payload, status)) {
-      const unsigned long long inc_cnt = out_cnt + total_cnt;
-      const A inc_val = total_cnt ? total_val : out_val + total_val;
-      DescWords<A>::pack(inc_cnt, inc_val, payload);
-      publish<4>(&blocks[b], kStateInclusive, payload);
-    } else {
-      timed_out = true;
-    }
-  }
-  if (__any_sync(0xffffffffu, timed_out) && lane == 0) note_timeout(status, kSiteBlockChain, tile, 0);
+  return __reduce_add_sync(0xffffffffu, cnt);
 }
 
 constexpr int kComputeWarps = 8;  // warps of one team: a tile is split over them
 constexpr int kComputeThreads = kComputeWarps * kWarp;
 constexpr int kTeams = 2;      // teams of compute warps; tile j of a CTA belongs to team j % kTeams
-constexpr int kLookWarps = 3;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
+constexpr int kLookWarps = 2;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
+constexpr int kScoutWarps = 6; // warps that count heads ahead of the data (compacting algorithms only)
+constexpr unsigned kScoutAhead = 1536;  // tiles a scout may run in front of the data tickets (their keys stay in L2)
+constexpr unsigned kScoutPrefetch = 512;  // a scout that draws tile u asks for the keys of tile u + kScoutPrefetch
 constexpr int kStops = kLookWarps > kTeams ? kLookWarps : kTeams;  // "no tile" slots that end the roles
 constexpr int kRoleWarp0 = kTeams * kComputeWarps;  // first warp that is not a compute warp
-constexpr int kCtaThreads = (kRoleWarp0 + kLookWarps + 2) * kWarp;  // + look-back warps + closer + producer
+// compute warps + look-back warps + producer (+ scouts: the segmented scans compact nothing and run without)
+constexpr int cta_threads(int mode) {
+  return (kRoleWarp0 + kLookWarps + 1 + ((mode == 1 || mode == 2) ? 0 : kScoutWarps)) * kWarp;
+}
+constexpr int kScoutTicket = 8;  // TempHeader::aux word that deals tiles to the scouts
 constexpr int kPacks = 5;   // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
 constexpr int kStages = 5;  // ring slots: one or two loading, one being scanned, the rest parked
 constexpr unsigned kNoTile = 0xffffffffu;
@@ -432,10 +434,12 @@ struct Args {
   uint64_t n;
   unsigned num_tiles;
   int bulk;                     // inputs are 16-byte aligned: tiles arrive by bulk copy
+  int inplace;                  // an output overlaps its input (unique): a tile is overwritten only after it was read
   V init;                       // exclusive scan_by_key
   TempHeader* hdr;
-  TileWords<4>* tiles;   // one descriptor per tile: EMPTY -> AGGREGATE
-  TileWords<4>* blocks;  // one per block of kBlockTiles tiles: EMPTY -> AGGREGATE -> INCLUSIVE
+  TileWords<4>* tiles;    // value chain, one descriptor per tile: EMPTY -> AGGREGATE -> PREFIX
+  TileWords<4>* cblocks;  // count chain, one per block of kBlockTiles tiles
+  TileWords<1>* ctiles;   // count chain, one word per tile
 };
 
 template <int MODE, typename V> struct AccOf { using type = unsigned; };
@@ -444,7 +448,7 @@ template <typename V> struct AccOf<kScanByKeyIncl, V> { using type = V; };
 template <typename V> struct AccOf<kScanByKeyExcl, V> { using type = V; };
 
 template <int MODE, typename K, typename V>
-__global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V> a) {
+__global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args<K, V> a) {
   using S = Shape<K, V>;
   using A = typename AccOf<MODE, V>::type;
   constexpr bool kSum = MODE == kReduceByKey || MODE == kScanByKeyIncl || MODE == kScanByKeyExcl;
@@ -458,7 +462,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   constexpr int NW = kComputeWarps;
 
   extern __shared__ __align__(128) unsigned char ring[];
-  __shared__ __align__(8) unsigned long long s_full[NS], s_scanned[NS], s_resolved[NS], s_freed[NS];
+  __shared__ __align__(8) unsigned long long s_full[NS], s_scanned[NS], s_resolved[NS], s_freed[NS], s_issued[NS];
   __shared__ unsigned s_tile[NS];
   __shared__ __align__(16) unsigned char s_halo[NS][16];  // the 16 bytes of keys in front of the slot's tile
   __shared__ unsigned s_arrivals[NS];        // compute warps that have finished phase A of the slot's tile
@@ -466,8 +470,10 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   __shared__ A s_wtot_val[NS][NW];
   __shared__ unsigned s_tot_cnt[NS];         // tile aggregate
   __shared__ A s_tot_val[NS];
-  __shared__ unsigned long long s_wpre_cnt[NS][NW];  // state of the scan in front of every warp, set by the look-back warp
-  __shared__ A s_wpre_val[NS][NW];
+  __shared__ A s_wlead[NS][NW];              // reduce_by_key: sum of the warp's elements in front of its first head
+  __shared__ A s_lead[NS];                   // reduce_by_key: the same for the whole tile
+  __shared__ unsigned long long s_pc[NS];  // compacting algorithms: heads in front of the tile, set by the look-back warp
+  __shared__ A s_wpre_val[NS][NW];         // scan_by_key: run open in front of every warp, set by the look-back warp
   // what a thread keeps of a scanned tile until its prefix is known (per slot)
   __shared__ unsigned s_park_heads[NS][kComputeThreads];  // head / selection flags of the thread's items
   __shared__ unsigned s_park_cnt[NS][kComputeThreads];    // flags set in earlier lanes of the warp
@@ -515,6 +521,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     const unsigned r = jj / NS;
     return (r == 0 || ready(&s_freed[s], (r - 1u) & 1u)) && ready(&s_full[s], r & 1u);
   };
+  auto wait_issued = [&](unsigned jj) -> bool {  // blocking (bounded): s_tile of tile jj is set
+    const int s = jj % NS;
+    const unsigned r = jj / NS;
+    return (r == 0 || wait_all(&s_freed[s], (r - 1u) & 1u)) && wait_all(&s_issued[s], r & 1u);
+  };
   auto wait_landed = [&](unsigned jj) -> bool {  // blocking (bounded)
     const int s = jj % NS;
     const unsigned r = jj / NS;
@@ -527,6 +538,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       mbar_init(&s_scanned[s], 1);
       mbar_init(&s_resolved[s], 1);
       mbar_init(&s_freed[s], NW);
+      mbar_init(&s_issued[s], 1);
       s_arrivals[s] = 0;
     }
     if (blockIdx.x == 0) {  // decodes a recorded mbarrier time-out
@@ -540,16 +552,18 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
   __syncthreads();  // the only CTA-wide barrier of the kernel
 
   // ---------------------------------------------------------------------- producer
-  if (warp == kRoleWarp0 + kLookWarps + 1) {
+  if (warp == kRoleWarp0 + kLookWarps) {
     if (lane != 0) return;
     // tile t goes into `slot`; false when the tickets have run past the last tile
     auto issue = [&](int slot, unsigned t) -> bool {
       if (t >= num_tiles) {
         s_tile[slot] = kNoTile;
+        mbar_arrive(&s_issued[slot]);
         mbar_arrive(&s_full[slot]);
         return false;
       }
       s_tile[slot] = t;
+      mbar_arrive(&s_issued[slot]);  // the look-back warp may resolve the tile's count while the tile loads
       if (a.bulk && (uint64_t)(t + 1) * TILE <= n) {
         fence_proxy_async_smem();  // the slot was last written by ordinary stores (parked values)
         constexpr bool kNeedsPrev = MODE != kCopyFlagged;  // the key in front of the tile decides its first head
@@ -586,63 +600,142 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     return;
   }
 
-  // ---------------------------------------------------------------------- closer warp
-  if (warp == kRoleWarp0 + kLookWarps) {
-    if constexpr (kScanOut) return;  // the segmented scans' chain has one level
-    for (unsigned j = 0;; ++j) {
-      const int slot = j % NS;
-      if (!wait_all(&s_full[slot], (j / NS) & 1u)) return;
-      const unsigned tile = s_tile[slot];
-      if (tile == kNoTile) return;
-      if (tile % kBlockTiles == kBlockTiles - 1)  // this CTA holds the block's last tile
-        close_block<A>(a.tiles, a.blocks, tile / kBlockTiles, kBlockTiles, status);
+  // ---------------------------------------------------------------------- scout warps
+  if (warp > kRoleWarp0 + kLookWarps) {
+    if constexpr (kScanOut) {
+      return;  // the segmented scans compact nothing
+    } else {
+      unsigned long long* scout_ticket = &a.hdr->aux[kScoutTicket];
+      unsigned seen = 0;  // data tickets known to have been drawn
+      while (true) {
+        // (a ticket drawn ahead of its turn would sit idle for a whole tile while others wait for it)
+        unsigned u = 0;
+        if (lane == 0) u = (unsigned)atomicAdd(scout_ticket, 1ull);
+        u = __shfl_sync(0xffffffffu, u, 0);
+        if (u >= num_tiles) return;
+        // The scouts read half of what the kernel takes from HBM; registers cannot hold that many
+        // bytes in flight, an L2 prefetch issued a few microseconds ahead can. Every tile is asked
+        // for exactly once, by the scout that draws the ticket kScoutPrefetch below it.
+        if (lane == 0 && reinterpret_cast<uintptr_t>(a.keys) % 16 == 0) {
+          const uint64_t pf = (uint64_t)u + kScoutPrefetch;
+          if ((pf + 1) * TILE <= n) prefetch_l2(a.keys + pf * TILE, S::kKeyBytes);
+        }
+        // stay within reach of the data path, so that the keys read here are still in L2 when the
+        // tile is loaded again. (Tile u only waits while a data ticket below u - kScoutAhead is
+        // still to be drawn, and no data tile ever waits for a scout in front of it.)
+        unsigned waits = 0;
+        while (u > seen + kScoutAhead) {
+          seen = ld_relaxed_u32(&a.hdr->ticket);
+          if (u <= seen + kScoutAhead) break;
+          __nanosleep(500);
+          if (++waits >= kSpinLimit || ((waits & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+            if (lane == 0 && waits >= kSpinLimit) note_timeout(status, kSiteIdle, u, 1);
+            return;
+          }
+        }
+        const uint64_t base = (uint64_t)u * TILE;
+        const bool whole = (uint64_t)(u + 1) * TILE <= n;
+        const unsigned heads = (whole && reinterpret_cast<uintptr_t>(a.keys) % 16 == 0)
+            ? count_heads_tile<K, MODE == kCopyFlagged, S::kKeyBytes / 16>(a.keys, base)
+            : count_heads_any<K, MODE == kCopyFlagged>(a.keys, base, whole ? (unsigned)TILE : (unsigned)(n - base), n);
+        if (lane == 0) {
+          const unsigned payload[1] = {heads};
+          publish<1>(&a.ctiles[u], kStateAggregate, payload);
+        }
+        if (u % kBlockTiles == kBlockTiles - 1 || u == num_tiles - 1)  // the block's last tile
+          close_block(a.ctiles, a.cblocks, u / kBlockTiles, u % kBlockTiles + 1, status);
+      }
     }
   }
 
-  // ---------------------------------------------------------------------- look-back warp
+  // ---------------------------------------------------------------------- look-back warps
   if (warp >= kRoleWarp0) {
+    unsigned checked = 0;  // in-place runs: every tile in [first tile the last output touched, checked) has been read
     for (unsigned j = warp - kRoleWarp0;; j += kLookWarps) {
       const int slot = j % NS;
       const unsigned par = (j / NS) & 1u;
-      if (!wait_landed(j)) return;
+      if (!wait_issued(j)) return;
       const unsigned tile = s_tile[slot];
       if (tile == kNoTile) return;
+      unsigned long long pc = 0;  // heads in front of the tile: the scouts' work, read while the tile loads
+      if constexpr (!kScanOut) {
+        pc = count_prefix(a.ctiles, a.cblocks, tile, status);
+        if (a.inplace) {
+          // The output overwrites the input from element pc on: every tile from there up to this
+          // one must have been read (scanned tiles have published a descriptor). Tiles below
+          // `checked` are known to be.
+          unsigned t0 = (unsigned)(pc / TILE);
+          if (t0 < checked) t0 = checked;
+          unsigned polls = 0;
+          while (t0 < tile) {
+            const unsigned idx = t0 + lane;
+            const bool done = idx >= tile || (unsigned)(ld_relaxed_u64(&a.tiles[idx].w[0]) >> 32) != kStateEmpty;
+            const unsigned waiting = __ballot_sync(0xffffffffu, !done);
+            if (waiting == 0) { t0 += kWarp; continue; }
+            t0 += (unsigned)(__ffs(waiting) - 1);
+            backoff(++polls);
+            if (polls >= kSpinLimit || ((polls & 255u) == 0 && ld_relaxed_s32(status) != 0)) {
+              if (lane == 0 && polls >= kSpinLimit) note_timeout(status, kSiteLookback, tile, t0);
+              return;
+            }
+          }
+          checked = tile;
+          // ... and by its scout: the scouts of the tiles in front are done (their counts are in
+          // pc), this tile's own may still be reading the keys this tile is about to overwrite
+          unsigned own = 0;
+          if (!poll_count(&a.ctiles[tile], own, status)) {
+            if (lane == 0) note_timeout(status, kSiteBlockChain, tile, 1);
+            return;
+          }
+        }
+      }
+      if (!wait_landed(j)) return;
       if (!wait_all(&s_scanned[slot], par)) return;
       SegPair<A> total{s_tot_cnt[slot], A(0)};
       if constexpr (kSum) total.val = s_tot_val[slot];
-      SegPair<A> exc{0u, A(0)};  // warps in front of warp `lane` inside the tile
-      if (lane < NW) {
-        exc.cnt = s_wtot_cnt[slot][lane];
-        if constexpr (kSum) exc.val = s_wtot_val[slot][lane];
-      }
-      unsigned long long pc = 0;
       A pv = A(0);
       if constexpr (kScanOut) {
+        A exc = A(0);  // warps in front of warp `lane` inside the tile
+        unsigned exc_cnt = 0;
+        if (lane < NW) {
+          exc_cnt = s_wtot_cnt[slot][lane];
+          exc = s_wtot_val[slot][lane];
+        }
         lookback_short<A>(a.tiles, tile, status, pv);
         if (total.cnt == 0 && lane == 0) {  // no head in the tile: the run open in front of it goes on
           unsigned payload[4];
           DescWords<A>::pack(0ull, pv + total.val, payload);
           publish<4>(&a.tiles[tile], kStatePrefix, payload);  // second writer of the descriptor, ordered after the first by the `scanned` barrier
         }
+        if (lane < NW) s_wpre_val[slot][lane] = exc_cnt ? exc : pv + exc;  // run open in front of compute warp `lane`
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_resolved[slot]);
       } else {
-        resolve<A>(a.tiles, a.blocks, tile, total.cnt, total.val, status, pc, pv);
-      }
-      if (lane == 0) {
-        const unsigned long long ic = pc + total.cnt;
-        const A iv = total.cnt ? total.val : pv + total.val;
-        if (tile == num_tiles - 1) {
-          if constexpr (MODE == kReduceByKey) {  // close the last run
-            if (ic > 0) a.vals_out[ic - 1] = iv;
+        // The compute warps need only the count: hand it over, then settle the one value that
+        // depends on other tiles (the run that the tile's first head closes).
+        A lead = A(0);
+        if constexpr (MODE == kReduceByKey) lead = s_lead[slot];
+        if (lane == 0) s_pc[slot] = pc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_resolved[slot]);
+        if (tile == num_tiles - 1 && lane == 0) *a.num_out = pc + total.cnt;
+        if constexpr (MODE == kReduceByKey) {
+          lookback_short<A>(a.tiles, tile, status, pv);
+          if (lane == 0) {
+            if (total.cnt == 0) {
+              unsigned payload[4];
+              DescWords<A>::pack(0ull, pv + total.val, payload);
+              publish<4>(&a.tiles[tile], kStatePrefix, payload);
+            } else if (pc > 0) {
+              a.vals_out[pc - 1] = pv + lead;
+            }
+            if (tile == num_tiles - 1) {  // close the last run
+              const unsigned long long ic = pc + total.cnt;
+              if (ic > 0) a.vals_out[ic - 1] = total.cnt ? total.val : pv + total.val;
+            }
           }
-          if constexpr (!kScanOut) *a.num_out = ic;
         }
       }
-      if (lane < NW) {  // state of the scan in front of compute warp `lane`
-        s_wpre_cnt[slot][lane] = pc + exc.cnt;
-        if constexpr (kSum) s_wpre_val[slot][lane] = exc.cnt ? exc.val : pv + exc.val;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_resolved[slot]);
     }
   }
 
@@ -668,9 +761,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     const uint64_t tile_base = (uint64_t)tile * TILE;
     const K* sk = slot_keys(slot);
     const V* sv = slot_vals(slot);
-    const unsigned long long wcnt = s_wpre_cnt[slot][w];
-    A wval = A(0);
-    if constexpr (kSum) wval = s_wpre_val[slot][w];
+    const unsigned wexc = s_wtot_cnt[slot][w];  // heads in the warps in front of this one inside the tile
+    unsigned long long wcnt = 0;                // heads in front of the warp
+    if constexpr (!kScanOut) wcnt = s_pc[slot] + wexc;
+    A wval = A(0);  // run open in front of the warp: over all tiles (scan_by_key), inside the tile (reduce_by_key)
+    if constexpr (kScanOut) wval = s_wpre_val[slot][w];
+    else if constexpr (kSum) wval = s_wtot_val[slot][w];
     if constexpr (kScanOut) {
       // the parked values are complete up to the warp's first head; in front of it the run
       // that was open at the start of the slice continues
@@ -701,22 +797,37 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
         if constexpr (MODE == kReduceByKey) {
           // the run that closes at the thread's first head began in front of the thread
           A carried = st.cnt ? st.val : wval + st.val;
+          // The run that the TILE's first head closes began in another tile: its sum is stored by
+          // the look-back warp, the only one to wait for other tiles' values.
+          bool other_tile = wexc == 0 && st.cnt == 0;
           while (heads) {
             const int i = __ffs(heads) - 1;
             heads &= heads - 1;
             const A r = i ? carried + sv[my_off + i - 1] : carried;
-            if (at > 0) a.vals_out[at - 1] = r;
+            if (at > 0 && !other_tile) a.vals_out[at - 1] = r;
+            other_tile = false;
             a.keys_out[at] = sk[my_off + i];
             carried = A(0);
             ++at;
           }
         } else {
-          while (heads) {
-            const int i = __ffs(heads) - 1;
-            heads &= heads - 1;
-            if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
-            if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
-            ++at;
+          if (__popc(heads) * 3 > ITEMS) {  // many selected: no dependent search for the next one
+#pragma unroll
+            for (int i = 0; i < ITEMS; ++i) {
+              if (heads & (1u << i)) {
+                if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
+                if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
+                ++at;
+              }
+            }
+          } else {
+            while (heads) {
+              const int i = __ffs(heads) - 1;
+              heads &= heads - 1;
+              if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
+              if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
+              ++at;
+            }
           }
         }
       }
@@ -820,6 +931,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       if (left < (uint64_t)ITEMS) heads &= (1u << (unsigned)left) - 1u;
     }
 
+    int lead_lane = -1;  // reduce_by_key: the lane that holds the warp's first head
     Parked now;
     now.heads = heads;
     now.fh = 0;
@@ -845,6 +957,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
     if (lane == 31) {
       s_wtot_cnt[slot][w] = s.cnt;
       if constexpr (kSum) s_wtot_val[slot][w] = s.val;
+    }
+    if constexpr (MODE == kReduceByKey) {
+      // sum of the warp's elements in front of its first head (the whole warp if it has none)
+      const unsigned with_head = __ballot_sync(0xffffffffu, heads != 0);
+      if (with_head == 0) {
+        if (lane == 31) s_wlead[slot][w] = s.val;
+      }
+      lead_lane = with_head ? __ffs(with_head) - 1 : -1;
     }
     // ---- park what phase C needs in the tile's own slot
     if constexpr (MODE == kReduceByKey) {
@@ -887,6 +1007,12 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
       }
       now.fh = fh;
     }
+    if constexpr (MODE == kReduceByKey) {
+      if ((int)lane == lead_lane) {  // the lanes in front of this one have no head; its run sums are parked above
+        const int i0 = __ffs(heads) - 1;
+        s_wlead[slot][w] = i0 ? now.val + sv[my_off + i0 - 1] : now.val;
+      }
+    }
     s_park_heads[slot][tid] = now.heads;
     s_park_cnt[slot][tid] = now.cnt;
     if constexpr (kSum) s_park_val[slot][tid] = now.val;
@@ -922,13 +1048,23 @@ __global__ void __launch_bounds__(kCtaThreads, 1) stream_kernel(const Args<K, V>
         s_wtot_cnt[slot][lane] = exc.cnt;
         if constexpr (kSum) s_wtot_val[slot][lane] = exc.val;
       }
+      if constexpr (MODE == kReduceByKey) {
+        const unsigned hm = __ballot_sync(0xffffffffu, lane < NW && tot.cnt != 0);
+        if (hm && lane == (unsigned)(__ffs(hm) - 1)) s_lead[slot] = exc.val + s_wlead[slot][lane];
+      }
       if (lane == NW - 1) {
         s_tot_cnt[slot] = inc.cnt;
-        if constexpr (kSum) s_tot_val[slot] = inc.val;
-        unsigned payload[4];
-        DescWords<A>::pack(inc.cnt, inc.val, payload);
-        // plain stores: nothing is waited for. A segmented scan's tile that holds a head is final.
-        publish<4>(&a.tiles[tile], (kScanOut && inc.cnt) ? kStatePrefix : kStateAggregate, payload);
+        if constexpr (kSum) {
+          s_tot_val[slot] = inc.val;
+          unsigned payload[4];
+          DescWords<A>::pack(inc.cnt, inc.val, payload);
+          // The value chain (plain stores: nothing is waited for). Only the run open at the end
+          // of a tile matters to its successors, so a tile that holds a head is final at once.
+          publish<4>(&a.tiles[tile], inc.cnt ? kStatePrefix : kStateAggregate, payload);
+        }
+        else if (a.inplace) {  // the tile's input is in shared memory now: it may be overwritten
+          st_relaxed_u64(&a.tiles[tile].w[0], (unsigned long long)kStateAggregate << 32);
+        }
         s_arrivals[slot] = 0;
       }
       __syncwarp();
@@ -952,19 +1088,20 @@ inline int sm_count(int* sms) {
 template <typename K, typename V>
 constexpr uint64_t tile_elems() { return (uint64_t)Shape<K, V>::kTile; }
 
-// Scratch: header + one 32-byte descriptor per tile + one per block of tiles.
+// Scratch: header + a 32-byte value descriptor per tile + a 32-byte count descriptor per block
+// of tiles + an 8-byte count word per tile.
 template <typename K, typename V>
 size_t scratch_bytes(uint64_t n) {
   const uint64_t tiles = (n + tile_elems<K, V>() - 1) / tile_elems<K, V>();
   const uint64_t blocks = (tiles + kBlockTiles - 1) / kBlockTiles;
-  return kHeaderBytes + (size_t)(tiles + blocks) * sizeof(TileWords<4>);
+  return kHeaderBytes + (size_t)(tiles + blocks) * sizeof(TileWords<4>) + (size_t)tiles * sizeof(TileWords<1>);
 }
 
 // Launches the streaming kernel (n > 0, scratch cleared by the caller). `bulk`: keys, values and,
 // for scan_by_key, the output are 16-byte aligned.
 template <int MODE, typename K, typename V>
 int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long long* num_out, uint64_t n, V init,
-           bool bulk, void* d_temp, cudaStream_t stream) {
+           bool bulk, void* d_temp, cudaStream_t stream, bool inplace = false) {
   using S = Shape<K, V>;
   const uint64_t tiles = (n + S::kTile - 1) / S::kTile;
   if (tiles > 0x7fffffffull) return TB200_ERR_UNSUPPORTED;
@@ -977,10 +1114,12 @@ int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long
   a.n = n;
   a.num_tiles = (unsigned)tiles;
   a.bulk = bulk ? 1 : 0;
+  a.inplace = inplace ? 1 : 0;
   a.init = init;
   a.hdr = static_cast<TempHeader*>(d_temp);
   a.tiles = reinterpret_cast<TileWords<4>*>(static_cast<char*>(d_temp) + kHeaderBytes);
-  a.blocks = a.tiles + tiles;
+  a.cblocks = a.tiles + tiles;
+  a.ctiles = reinterpret_cast<TileWords<1>*>(a.cblocks + (tiles + kBlockTiles - 1) / kBlockTiles);
   auto kernel = stream_kernel<MODE, K, V>;
   // opt in to the kernel's dynamic shared memory once per device (this function is one
   // instantiation per kernel, so the flag below belongs to this kernel alone)
@@ -995,7 +1134,7 @@ int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long
   const int rc = sm_count(&sms);
   if (rc) return rc;
   const unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
-  kernel<<<grid, kCtaThreads, S::kSmem, stream>>>(a);
+  kernel<<<grid, cta_threads(MODE), S::kSmem, stream>>>(a);
   return (int)cudaGetLastError();
 }
 

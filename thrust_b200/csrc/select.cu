@@ -30,9 +30,16 @@ int launch_select(void* d_temp, size_t* temp_bytes, const void* kin, const void*
   uintptr_t bits = reinterpret_cast<uintptr_t>(kin);
   if (kHasVals) bits |= reinterpret_cast<uintptr_t>(vin);
   const bool bulk = bits % 16 == 0;
+  // unique / unique_by_key may run in place (thrust::unique_by_key is unique_by_key_copy onto its own input)
+  auto overlap = [n](const void* in, const void* out, size_t elem) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(in), b = reinterpret_cast<uintptr_t>(out), len = (uintptr_t)n * elem;
+    return in && out && a < b + len && b < a + len;
+  };
+  const bool inplace = (MODE == seg::kUniqueByKey && overlap(kin, kout, sizeof(K))) ||
+                       (kHasVals && overlap(vin, vout, seg::Shape<K, V>::kValSize));
   const int rc = seg::launch<MODE, K, V>(static_cast<const K*>(kin), static_cast<const V*>(vin), static_cast<K*>(kout),
                                          static_cast<V*>(vout), reinterpret_cast<unsigned long long*>(d_num_out), n,
-                                         V{}, bulk, d_temp, stream);
+                                         V{}, bulk, d_temp, stream, inplace);
   trace_mark(stream, trace_kind);
   return rc;
 }
