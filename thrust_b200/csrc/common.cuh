@@ -94,7 +94,7 @@ __device__ __forceinline__ int ld_relaxed_s32(const int* p) {
 // Raises the status word after a bounded wait ran out and records where: the FIRST wait to give
 // up writes aux[0] = site, aux[1..2] = what it waited for, aux[3] = CTA | thread << 32 of the
 // scratch header (every later time-out is a consequence of the first).
-enum : unsigned { kSiteLookback = 1, kSiteBlockChain = 2, kSiteCloser = 3, kSiteIdle = 4, kSiteMbarrier = 5 };
+enum : unsigned { kSiteLookback = 1, kSiteBlockChain = 2, kSiteIdle = 4, kSiteMbarrier = 5 };
 __device__ __forceinline__ void note_timeout(int* status, unsigned site, unsigned long long x, unsigned long long y) {
   unsigned long long* aux = reinterpret_cast<unsigned long long*>(status) + 1;  // TempHeader::aux
   if (atomicCAS(&aux[0], 0ull, (unsigned long long)site) == 0ull) {
