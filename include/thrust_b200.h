@@ -120,8 +120,10 @@ int tb200_radix_sort_finish(void* d_temp, size_t* temp_bytes, void* d_keys, void
 
 /* ---- scan ---------------------------------------------------------------------------
  * Prefix sum with plus over n elements of dtype in {I32,U32,I64,U64,F32,F64}; accumulator
- * type == element type. exclusive == 0: inclusive_scan. exclusive != 0: exclusive_scan
- * seeded with *h_init (a HOST pointer to one element; NULL = value-initialised zero).
+ * type == element type. exclusive == 0: inclusive_scan. exclusive != 0: exclusive_scan.
+ * Both are seeded with *h_init (a HOST pointer to one element; NULL = value-initialised zero):
+ * out[i] = init + in[0] + ... + in[i] or init + in[0] + ... + in[i-1]. (A seeded inclusive
+ * scan is what a shard of a distributed scan runs: the seed is the sum of the shards in front.)
  * d_out may equal d_in (exactly in place); no other overlap.
  * Replaces: cuda_cub::detail::inclusive_scan_n_impl / exclusive_scan_n_impl and their
  * cub::DispatchScan calls (thrust/system/cuda/detail/scan.h:50-125, 127-204). */

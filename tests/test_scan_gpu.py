@@ -105,3 +105,32 @@ def test_scan_rejects_bad_arguments(cuda_device):
         tb.inclusive_scan(torch.zeros(8, dtype=torch.int16, device="cuda"))
     with pytest.raises(ValueError):
         tb.inclusive_scan(torch.zeros(8, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.uint64])
+@pytest.mark.parametrize("n", [1, 33, 4097, (1 << 20) + 13, (1 << 23) + 5])
+def test_seeded_inclusive_scan_bit_exact(cuda_device, dtype, n):
+    # out[i] = seed + in[0] + ... + in[i]: what a shard of a distributed scan runs
+    rng = np.random.default_rng(70 + n)
+    a = _data(rng, n, dtype)
+    with np.errstate(over="ignore"):
+        want = (oracle.port().scan(a, True, 12345) + a).astype(dtype)
+    got = tb.inclusive_scan(to_device(a), init=12345)
+    assert to_host(got, dtype).tobytes() == want.tobytes()
+
+
+def test_sharded_scan_and_reduce_by_key_on_one_rank_match_the_oracle(cuda_device):
+    from thrust_b200.sharded_scan import ShardedScan
+    rng = np.random.default_rng(5)
+    n = (1 << 20) + 77
+    vals = rng.integers(-1000, 1000, size=n, dtype=np.int64)
+    keys = np.cumsum(rng.random(n) < 1 / 16).astype(np.int32)
+    chk = oracle.port()
+    sh = ShardedScan(1, 0)
+    dv, dk = to_device(vals), to_device(keys)
+    assert to_host(sh.inclusive_scan(dv), np.int64).tobytes() == chk.scan(vals).tobytes()
+    assert to_host(sh.exclusive_scan(dv, init=3), np.int64).tobytes() == chk.scan(vals, True, 3).tobytes()
+    ko, vo, m = sh.reduce_by_key(dk, dv)
+    wk, wv = chk.reduce_by_key(keys, vals)
+    assert m == wk.size and to_host(ko[:m], np.int32).tobytes() == wk.tobytes()
+    assert to_host(vo[:m], np.int64).tobytes() == wv.tobytes()

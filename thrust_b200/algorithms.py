@@ -107,7 +107,7 @@ def _scan(inp: torch.Tensor, out: Optional[torch.Tensor], exclusive: bool, init,
         raise ValueError("output must match the input")
     n = inp.numel()
     init_buf = None
-    if exclusive and init is not None:
+    if init is not None:
         ctype = {capi.I32: C.c_int32, capi.U32: C.c_uint32, capi.I64: C.c_int64, capi.U64: C.c_uint64,
                  capi.F32: C.c_float, capi.F64: C.c_double}[dt]
         init_buf = ctype(init)
@@ -128,9 +128,10 @@ def _scan(inp: torch.Tensor, out: Optional[torch.Tensor], exclusive: bool, init,
 
 
 def inclusive_scan(inp: torch.Tensor, out: Optional[torch.Tensor] = None, dtype: Optional[int] = None,
-                   sync: bool = True, temp: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """thrust::inclusive_scan with plus (thrust/scan.h:99); ``out`` may be ``inp``."""
-    return _scan(inp, out, False, None, dtype, sync, temp)
+                   sync: bool = True, temp: Optional[torch.Tensor] = None, init=None) -> torch.Tensor:
+    """thrust::inclusive_scan with plus (thrust/scan.h:99); ``out`` may be ``inp``. ``init`` seeds the
+    scan (out[i] = init + in[0] + ... + in[i]); None is the plain form."""
+    return _scan(inp, out, False, init, dtype, sync, temp)
 
 
 def exclusive_scan(inp: torch.Tensor, out: Optional[torch.Tensor] = None, init=None,

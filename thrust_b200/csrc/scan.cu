@@ -187,7 +187,7 @@ scan_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr,
     unsigned payload[W];
     T prefix;
     if (tile == 0) {
-      prefix = EXCLUSIVE ? init : T(0);
+      prefix = init;  // the seed: in front of the first element in both forms
       if (lane == 0) {
         Words<T>::pack(prefix + tile_total, payload);
         publish<W>(&tiles[0], kStatePrefix, payload);
@@ -332,7 +332,7 @@ scan_stream_kernel(const T* in, T* out, uint64_t n, T init, TempHeader* hdr, Til
       const T total = s_look_total[slot];
       T prefix;
       if (tile == 0) {
-        prefix = EXCLUSIVE ? init : T(0);
+        prefix = init;  // the seed: in front of the first element in both forms
       } else {
         prefix = lookback_sum<T>(tiles, tile, status);
       }
@@ -508,7 +508,7 @@ int launch_scan(void* d_temp, size_t* temp_bytes, const void* d_in, void* d_out,
   if (d_in == nullptr || d_out == nullptr) return TB200_ERR_INVALID_ARGUMENT;
 
   T init = T(0);
-  if (exclusive && h_init) init = *static_cast<const T*>(h_init);
+  if (h_init) init = *static_cast<const T*>(h_init);
   auto* hdr = static_cast<TempHeader*>(d_temp);
   auto* desc = reinterpret_cast<TileWords<W>*>(static_cast<char*>(d_temp) + kHeaderBytes);
   const T* in = static_cast<const T*>(d_in);
