@@ -20,6 +20,9 @@ LIB = PKG / "libthrust_b200.so"
 # test / benchmark support (seeded inputs, reference-free checker): its own library
 DATAGEN_SRC = PKG / "datagen" / "datagen.cu"
 DATAGEN_LIB = PKG / "datagen" / "libtb200_datagen.so"
+# the sharded sort behind one C entry point: links NCCL, so it is a library of its own
+NCCL_SRC = PKG / "csrc_nccl" / "sample_sort.cu"
+NCCL_LIB = PKG / "libthrust_b200_nccl.so"
 ROOT = PKG.parent
 
 NVCC_FLAGS = [
@@ -79,6 +82,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objs = [OBJ / (s.stem + ".o") for s in srcs]
     if todo or not LIB.exists():
         cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-ccbin", "/usr/bin/g++", "-lcudart", "-lgomp"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    nccl_obj = OBJ / "nccl_sample_sort.o"
+    if force or not NCCL_LIB.exists() or NCCL_LIB.stat().st_mtime < max(NCCL_SRC.stat().st_mtime, hdr_time, LIB.stat().st_mtime):
+        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(NCCL_SRC), "-o", str(nccl_obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {NCCL_SRC.name} (needs nccl.h):\n{r.stdout}\n{r.stderr}")
+        cmd = [_nvcc(), "-shared", "-o", str(NCCL_LIB), str(nccl_obj), "-ccbin", "/usr/bin/g++", "-L", str(PKG),
+               "-lthrust_b200", "-lnccl", "-lcudart", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
