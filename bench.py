@@ -525,6 +525,9 @@ def main():
     ap.add_argument("--log2-per-gpu", type=int, default=PER_GPU_LOG2, help="for quick checks only")
     ap.add_argument("--no-others", action="store_true", help="skip the side configurations at --gpus 1")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--engine", default="python", choices=["python", "c"],
+                    help="who runs the steps of the sharded sort at --gpus > 1: the Python class over torch.distributed, "
+                         "or one call of the C entry point tb200_sample_sort on its own NCCL communicator")
     ap.add_argument("--exchange", default="auto", choices=["auto", "push", "peer", "nccl"],
                     help="exchange step of the sharded sort at --gpus > 1 (default: push over NVLink)")
     ap.add_argument("--no-cpu", action="store_true")
@@ -559,7 +562,8 @@ def main():
     n = 1 << args.log2_per_gpu
     stream = torch.cuda.current_stream(dev)
 
-    sorter = ss.ShardedSorter(n, dev, world_size=world, rank=rank, seed=SEED, exchange=args.exchange)
+    sorter = ss.ShardedSorter(n, dev, world_size=world, rank=rank, seed=SEED, exchange=args.exchange,
+                              engine=args.engine)
     k0, v0 = g.pairs_u64_u32(n, SEED, rank * n, dev)
     k, v = torch.empty_like(k0), torch.empty_like(v0)
 
@@ -648,6 +652,7 @@ def main():
     if world > 1:
         line["phases_ms_rank0_last_step"] = phases
         line["config"]["exchange"] = sorter_exchange
+        line["config"]["engine"] = args.engine
     if rank == 0 and world == 1:
         if not args.no_cpu:
             line["cpu_baseline"], _ = cpu_sort_sample(25, 3, 1)

@@ -98,3 +98,18 @@ def test_argument_validation_precedes_any_device_work():
                                     None) == capi.ERR_UNSUPPORTED
     assert capi.lib.tb200_gather_segments(None, None, None, None, 17, 8, 0, None, None) == capi.ERR_UNSUPPORTED
     assert capi.lib.tb200_scan_static(None, None, 1 << 40, capi.F32, 0, None, None) == capi.ERR_OVERFLOW
+
+
+def test_nccl_library_exports_its_entry_point_and_answers_the_size_query():
+    import torch  # noqa: F401  (its NCCL is the one the library resolves to)
+    from thrust_b200 import _capi as capi, nccl_sort
+    names = _declared(ROOT / "include" / "thrust_b200_nccl.h")
+    assert names == ["tb200_sample_sort"]
+    for n in names:
+        assert hasattr(nccl_sort.lib, n) and not hasattr(capi.lib, n), "the NCCL entry lives in its own library"
+    push = nccl_sort.temp_bytes(8, 1 << 20, (1 << 20) + (1 << 18), True)
+    coll = nccl_sort.temp_bytes(8, 1 << 20, (1 << 20) + (1 << 18), False)
+    assert coll >= push + (1 << 20) * 12  # the collective form keeps a partitioned copy of the shard
+    need = C.c_size_t(0)
+    assert nccl_sort.lib.tb200_sample_sort(None, 3, 2, None, C.byref(need), None, None, 10, None, None, 10, None, None,
+                                           None, None) == capi.ERR_INVALID_ARGUMENT  # rank outside the communicator

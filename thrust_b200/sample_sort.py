@@ -183,8 +183,12 @@ class ShardedSorter:
 
     def __init__(self, n: int, device: torch.device, world_size: int = 1, rank: int = 0, seed: int = 0,
                  ops=None, group=None, slack: Optional[float] = None, pipeline: str = "partition_first",
-                 exchange: str = "auto"):
-        """exchange: "push" — the partition kernel stores every bucket straight into its
+                 exchange: str = "auto", engine: str = "python"):
+        """engine: "python" — this class runs the steps (torch.distributed collectives around the
+        C-ABI kernels); "c" — the whole step is ONE call of tb200_sample_sort
+        (include/thrust_b200_nccl.h) on a raw NCCL communicator made for it, and this class only
+        owns the buffers (partition_first pipeline, "push" or "nccl" exchange).
+        exchange: "push" — the partition kernel stores every bucket straight into its
         destination GPU's receive buffer over NVLink (receive buffers in torch symmetric memory,
         plain peer stores, no multicast), so partition and exchange are one pass over the shard;
         "peer" — partition locally, then every GPU pulls its runs out of the other GPUs' partition
@@ -232,6 +236,19 @@ class ShardedSorter:
                 self.recv_v = torch.empty(self.capacity, dtype=torch.int32, device=device)
         self.last_counts = None
         self._marks = []
+        if engine not in ("python", "c"):
+            raise ValueError(engine)
+        self.engine = engine if world_size > 1 else "python"
+        if self.engine == "c":
+            if pipeline != "partition_first" or self.exchange not in ("push", "nccl") or device.type != "cuda":
+                raise ValueError("engine='c' runs the partition_first pipeline with the push or nccl exchange on CUDA")
+            from . import nccl_sort
+            self._nccl_sort = nccl_sort
+            self._comm = nccl_sort.create_comm(rank, world_size, device, group)
+            push = self.exchange == "push"
+            self.part_k = self.part_v = None  # the C entry keeps its partition buffers in its scratch
+            self._c_temp = torch.empty(nccl_sort.temp_bytes(world_size, n, self.capacity, push), dtype=torch.uint8,
+                                       device=device)
 
     def _alloc_symmetric(self, n: int, mode: str) -> None:
         """Buffers the peers touch, in symmetric memory, and every rank's pointers to them:
@@ -289,6 +306,14 @@ class ShardedSorter:
         sort_first = self.pipeline == "sort_first"
         self._marks = []
         self._mark("start")
+        if self.engine == "c":
+            push = self.exchange == "push"
+            m = self._nccl_sort.sample_sort(self._comm, self.rank, G, keys[:n], vals[:n], self.recv_k, self.recv_v,
+                                            self.peer_k if push else None, self.peer_v if push else None,
+                                            self._c_temp)
+            self.last_counts = None
+            self._mark("sample_sort_c")
+            return self.recv_k, self.recv_v, m
         if sort_first:
             self.ops.sort_pairs(keys, vals, n)
             self._mark("local_sort")
