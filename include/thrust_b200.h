@@ -93,6 +93,26 @@ int tb200_partition_scatter(void* d_temp, size_t* temp_bytes, const void* d_keys
                             int key_dtype, int val_bytes, const void* d_splitters, uint32_t num_splitters,
                             void* const* h_bucket_keys, void* const* h_bucket_vals, tb200_stream_t stream);
 
+/* The same three with (key, index) PAIRS as the thing that is compared: splitter i is the pair
+ * (d_splitters[i], d_splitter_index[i]), element g of the input is the pair (key, index_base + g),
+ * pairs compare by key first, then by index, and bucket b holds the pairs in (splitter[b-1],
+ * splitter[b]]. Equal keys can then be divided between buckets, in input order: the sharded sort
+ * uses this (index = position in the global sequence) when a few keys make up most of the
+ * input and all copies of one key would not fit one rank. d_splitter_index == NULL is the plain
+ * form. No counterpart in the reference. */
+int tb200_partition_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                         void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
+                         const void* d_splitters, const uint64_t* d_splitter_index, uint32_t num_splitters,
+                         uint64_t index_base, uint64_t* d_counts, tb200_stream_t stream);
+int tb200_partition_count_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, uint64_t n, int key_dtype,
+                               int val_bytes, const void* d_splitters, const uint64_t* d_splitter_index,
+                               uint32_t num_splitters, uint64_t index_base, uint64_t* d_counts,
+                               tb200_stream_t stream);
+int tb200_partition_scatter_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                                 uint64_t n, int key_dtype, int val_bytes, const void* d_splitters,
+                                 const uint64_t* d_splitter_index, uint32_t num_splitters, uint64_t index_base,
+                                 void* const* h_bucket_keys, void* const* h_bucket_vals, tb200_stream_t stream);
+
 /* ---- segment gather (exchange step of the sharded sort) ---------------------------------
  * Concatenates num_segments (at most 16) source ranges into d_dst, in order: segment s is
  * h_count[s] elements of elem_bytes (4, 8 or 16) starting h_src_offset[s] elements into

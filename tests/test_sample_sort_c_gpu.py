@@ -54,7 +54,7 @@ def _worker(rank, world, port, out_dir):
     from thrust_b200.sample_sort import ShardedSorter
     n = 300_000 + 17
     rng = np.random.default_rng(99 + rank)
-    for case, bits in (("wide", 64), ("narrow", 10)):
+    for case, bits in (("wide", 64), ("narrow", 10), ("heavy", 1)):  # heavy: two keys, divided between the ranks
         keys = rng.integers(0, 1 << bits, size=n, dtype=np.uint64) << np.uint64(64 - bits)
         vals = (np.arange(n, dtype=np.uint64) + rank * n).astype(np.uint32)
         np.save(f"{out_dir}/{case}_in_k{rank}.npy", keys)
@@ -62,15 +62,19 @@ def _worker(rank, world, port, out_dir):
         k = torch.from_numpy(keys.view(np.int64)).to(dev)
         v = torch.from_numpy(vals.view(np.int32)).to(dev)
         for exchange in ("nccl", "push"):
-            sorter = ShardedSorter(n, dev, world, rank, exchange=exchange, engine="c", slack=0.5)
+            sorter = ShardedSorter(n, dev, world, rank, exchange=exchange, engine="c", slack=0.25)
             ok, ov, m = sorter.sort(k, v)
+            if case == "heavy":  # the Python orchestration takes the same decisions
+                ok2, ov2, m2 = ShardedSorter(n, dev, world, rank, exchange=exchange, slack=0.25).sort(k, v)
+                torch.cuda.synchronize()
+                assert m2 == m and torch.equal(ok2[:m], ok[:m]) and torch.equal(ov2[:m], ov[:m])
             torch.cuda.synchronize()
             np.save(f"{out_dir}/{case}_{exchange}_k{rank}.npy", ok[:m].cpu().numpy().view(np.uint64))
             np.save(f"{out_dir}/{case}_{exchange}_v{rank}.npy", ov[:m].cpu().numpy().view(np.uint32))
             dist.barrier()
-    # everything goes to one rank: no room with 1/64 slack, and every rank says so
+    # receive buffers smaller than a rank's share: no room, and every rank says so
     k = torch.zeros(n, dtype=torch.int64, device=dev)
-    sorter = ShardedSorter(n, dev, world, rank, exchange="nccl", engine="c", slack=1.0 / 64)
+    sorter = ShardedSorter(n, dev, world, rank, exchange="nccl", engine="c", slack=-0.5)
     try:
         sorter.sort(k, torch.zeros(n, dtype=torch.int32, device=dev))
     except OverflowError:
@@ -86,7 +90,7 @@ def test_two_ranks_match_the_single_process_stable_sort(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     chk = oracle.port()
-    for case in ("wide", "narrow"):
+    for case in ("wide", "narrow", "heavy"):
         in_k = np.concatenate([np.load(tmp_path / f"{case}_in_k{r}.npy") for r in range(world)])
         in_v = np.concatenate([np.load(tmp_path / f"{case}_in_v{r}.npy") for r in range(world)])
         want_k, want_v = chk.sort_by_key(in_k, in_v)

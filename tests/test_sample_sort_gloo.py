@@ -40,10 +40,16 @@ class OracleOps:
         ub = np.searchsorted(k, splitters.numpy().view(np.uint64), side="right")
         return torch.from_numpy(np.diff(np.concatenate([[0], ub])).astype(np.int64))
 
-    def partition(self, keys, vals, n, splitters, out_k, out_v):
+    def partition(self, keys, vals, n, splitters, out_k, out_v, split_idx=None, index_base=0):
         k = keys[:n].numpy().view(np.uint64)
         sp = splitters.numpy().view(np.uint64)
-        bucket = np.searchsorted(sp, k, side="left")  # number of splitters strictly below the key
+        if split_idx is None:
+            bucket = np.searchsorted(sp, k, side="left")  # number of splitters strictly below the key
+        else:  # (key, global index) pairs: number of splitter pairs strictly below the element's pair
+            g = np.arange(n, dtype=np.int64) + index_base
+            si = split_idx.numpy()
+            below = (sp[None, :] < k[:, None]) | ((sp[None, :] == k[:, None]) & (si[None, :] < g[:, None]))
+            bucket = below.sum(axis=1)
         order = np.argsort(bucket, kind="stable")
         out_k[:n] = torch.from_numpy(k[order].view(np.int64))
         out_v[:n] = torch.from_numpy(vals[:n].numpy()[order])
@@ -109,9 +115,28 @@ def test_sharded_sort_matches_single_process_stable_sort(tmp_path, world, n, key
 
 
 def test_receive_overflow_is_an_error_not_a_crash(tmp_path):
-    # all keys equal: everything goes to one rank, which cannot hold it with 1/64 slack
-    _run(2, 4000, 1, 1.0 / 64, tmp_path)
+    # all keys equal and compared by key alone (sort_first): everything goes to one rank, which cannot hold it
+    _run(2, 4000, 1, 1.0 / 64, tmp_path, "sort_first")
     assert any((tmp_path / f"overflow{r}").exists() for r in range(2))
+
+
+@pytest.mark.parametrize("world,key_bits", [(2, 1), (3, 1), (3, 2)])
+def test_a_few_heavy_keys_are_divided_between_the_ranks_in_input_order(tmp_path, world, key_bits):
+    # one or a few distinct keys: all copies of a key cannot go to one rank; the partition compares
+    # (key, global index) pairs, the result is still the single-process stable sort
+    import oracle
+    oracle.build(ref=False)
+    n = 4000
+    _run(world, n, key_bits, 1.0 / 8, tmp_path)
+    assert not any((tmp_path / f"overflow{r}").exists() for r in range(world))
+    in_k = np.concatenate([np.load(tmp_path / f"in_k{r}.npy") for r in range(world)])
+    in_v = np.concatenate([np.load(tmp_path / f"in_v{r}.npy") for r in range(world)])
+    outs = [np.load(tmp_path / f"out_k{r}.npy") for r in range(world)]
+    assert max(o.size for o in outs) <= n + n // 8 + 1024
+    out_k = np.concatenate(outs)
+    out_v = np.concatenate([np.load(tmp_path / f"out_v{r}.npy") for r in range(world)])
+    want_k, want_v = oracle.port().sort_by_key(in_k, in_v)
+    assert out_k.tobytes() == want_k.tobytes() and out_v.tobytes() == want_v.tobytes()
 
 
 def test_sample_positions_and_splitters():

@@ -283,6 +283,56 @@ def test_partition_count_then_scatter_into_separate_buffers(cuda_device, kdtype,
                 assert hv[pad:pad + got[b]].tobytes() == v[sel].tobytes(), (n, ns, b)
 
 
+@pytest.mark.parametrize("ns", [1, 3, 7, 20])
+def test_partition_with_key_index_pairs_divides_equal_keys_in_input_order(cuda_device, ns):
+    """The _ties forms: splitters and elements are (key, index) pairs. A handful of distinct keys,
+    so most splitter keys repeat; checked against numpy for the one-call form and for count +
+    scatter into separate buffers (the push form of the exchange)."""
+    import ctypes as C
+    rng = np.random.default_rng(31 + ns)
+    n, base = 200_003, 5_000_000_000  # indices beyond 32 bits
+    k = (rng.integers(0, 3, size=n, dtype=np.uint64) << np.uint64(62)) | np.uint64(0x3fffffffffffffff) * (rng.random(n) < 0.3)
+    k = k.astype(np.uint64)  # includes the largest key, which is also the value of the tile padding
+    v = rng.integers(0, 1 << 31, size=n).astype(np.uint32)
+    cand = np.sort(rng.choice(n, size=ns, replace=False))
+    order = np.lexsort((cand, k[cand]))
+    sp, si = k[cand][order], (cand[order] + base).astype(np.int64)
+    g = np.arange(n, dtype=np.int64) + base
+    bucket = ((sp[None, :] < k[:, None]) | ((sp[None, :] == k[:, None]) & (si[None, :] < g[:, None]))).sum(axis=1)
+    want_counts = np.bincount(bucket, minlength=ns + 1).tolist()
+    perm = np.argsort(bucket, kind="stable")
+    dk, dv, dsp, dsi = to_device(k), to_device(v), to_device(sp), to_device(si)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    need = C.c_size_t(0)
+    capi.check(capi.lib.tb200_partition_ties(None, C.byref(need), None, None, None, None, n, capi.U64, 4, None, None, ns,
+                                             base, None, stream), "size")
+    temp = torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda:0")
+    ok, ov = torch.empty_like(dk), torch.empty_like(dv)
+    counts = torch.zeros(ns + 1, dtype=torch.int64, device="cuda:0")
+    P = lambda t: C.c_void_p(t.data_ptr())
+    capi.check(capi.lib.tb200_partition_ties(P(temp), C.byref(need), P(dk), P(dv), P(ok), P(ov), n, capi.U64, 4, P(dsp),
+                                             P(dsi), ns, base, P(counts), stream), "tb200_partition_ties")
+    capi.check(capi.lib.tb200_temp_status(P(temp), stream), "status")
+    assert counts.cpu().numpy().tolist() == want_counts
+    assert to_host(ok, np.uint64).tobytes() == k[perm].tobytes() and to_host(ov, np.uint32).tobytes() == v[perm].tobytes()
+    counts.zero_()
+    capi.check(capi.lib.tb200_partition_count_ties(P(temp), C.byref(need), P(dk), n, capi.U64, 4, P(dsp), P(dsi), ns, base,
+                                                   P(counts), stream), "count")
+    got = counts.cpu().numpy().tolist()
+    assert got == want_counts
+    out_k = [torch.full((c + 1,), -1, dtype=torch.int64, device="cuda:0") for c in got]
+    out_v = [torch.full((c + 1,), -1, dtype=torch.int32, device="cuda:0") for c in got]
+    pk = (C.c_void_p * (ns + 1))(*[t.data_ptr() for t in out_k])
+    pv = (C.c_void_p * (ns + 1))(*[t.data_ptr() for t in out_v])
+    capi.check(capi.lib.tb200_partition_scatter_ties(P(temp), C.byref(need), P(dk), P(dv), n, capi.U64, 4, P(dsp), P(dsi),
+                                                     ns, base, pk, pv, stream), "scatter")
+    capi.check(capi.lib.tb200_temp_status(P(temp), stream), "status")
+    for b in range(ns + 1):
+        sel = bucket == b
+        assert to_host(out_k[b], np.uint64)[:got[b]].tobytes() == k[sel].tobytes(), b
+        assert to_host(out_v[b], np.uint32)[:got[b]].tobytes() == v[sel].tobytes(), b
+
+
 @pytest.mark.parametrize("dtype", [np.uint64, np.uint32])
 def test_gather_segments_concatenates_ranges(cuda_device, dtype):
     """tb200_gather_segments on local pointers: odd offsets and lengths, empty segments."""

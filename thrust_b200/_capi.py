@@ -38,6 +38,9 @@ def _load() -> C.CDLL:
         "tb200_partition": ([vp, psz, vp, vp, vp, vp, u64, i32, i32, vp, u32, vp, vp], i32),
         "tb200_partition_count": ([vp, psz, vp, u64, i32, i32, vp, u32, vp, vp], i32),
         "tb200_partition_scatter": ([vp, psz, vp, vp, u64, i32, i32, vp, u32, vp, vp, vp], i32),
+        "tb200_partition_ties": ([vp, psz, vp, vp, vp, vp, u64, i32, i32, vp, vp, u32, u64, vp, vp], i32),
+        "tb200_partition_count_ties": ([vp, psz, vp, u64, i32, i32, vp, vp, u32, u64, vp, vp], i32),
+        "tb200_partition_scatter_ties": ([vp, psz, vp, vp, u64, i32, i32, vp, vp, u32, u64, vp, vp, vp], i32),
         "tb200_gather_segments": ([vp, vp, vp, vp, u32, i32, u32, vp, vp], i32),
         "tb200_radix_sort_begin": ([vp, psz, u64, i32, i32, vp], i32),
         "tb200_radix_sort_finish": ([vp, psz, vp, vp, u64, i32, i32, vp], i32),
@@ -72,7 +75,7 @@ def _load() -> C.CDLL:
 lib = _load()
 
 EXPORTS = [
-    "tb200_version", "tb200_error_string", "tb200_radix_sort", "tb200_partition", "tb200_partition_count", "tb200_partition_scatter", "tb200_gather_segments", "tb200_radix_sort_begin", "tb200_radix_sort_finish", "tb200_scan", "tb200_scan_static", "tb200_scan_static_status", "tb200_reduce_by_key", "tb200_reduce", "tb200_scan_by_key", "tb200_unique_by_key", "tb200_copy_flagged",
+    "tb200_version", "tb200_error_string", "tb200_radix_sort", "tb200_partition", "tb200_partition_count", "tb200_partition_scatter", "tb200_partition_ties", "tb200_partition_count_ties", "tb200_partition_scatter_ties", "tb200_gather_segments", "tb200_radix_sort_begin", "tb200_radix_sort_finish", "tb200_scan", "tb200_scan_static", "tb200_scan_static_status", "tb200_reduce_by_key", "tb200_reduce", "tb200_scan_by_key", "tb200_unique_by_key", "tb200_copy_flagged",
     "tb200_histogram_sorted", "tb200_temp_status", "tb200_selftest_wait_timeout", "tb200_trace_begin", "tb200_trace_end",
     "tb200_workspace_acquire",
     "tb200_workspace_release", "tb200_workspace_stats", "tb200_workspace_release_all", "tb200_radix_sort_host", "tb200_scan_host",

@@ -335,6 +335,11 @@ struct PassParams {
   void* desc;
   const void* splitters;   // partition mode: ascending splitters (device), else unused
   unsigned num_splitters;
+  // partition mode, optional: splitter i is the PAIR (splitters[i], splitter_index[i]) and element g
+  // of the input is the pair (key, index_base + g); pairs compare by key, then by index. Equal
+  // keys can then be split between buckets (in input order). Null: keys alone decide.
+  const unsigned long long* splitter_index;
+  unsigned long long index_base;
   // partition mode: device tables of num_splitters + 1 pointers, the first element of every
   // bucket's output (keys, values); the buckets may live in different allocations, another
   // GPU's memory included. Null: bucket b starts at element offs[0][b] of the alternate arrays.
@@ -453,7 +458,8 @@ struct PassShape {
 // latency hides behind the look-back and the scatter of the current tile.
 // SPLIT = true turns the pass into a stable multi-way partition: the "digit" of a key is the
 // number of splitters strictly below it (bucket b holds keys in (s[b-1], s[b]]).
-template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT, bool SPLIT = false>
+template <typename UK, int VB, int THREADS, int ITEMS, int MIN_CTAS, typename DescT, bool SPLIT = false,
+          bool TIES = false>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
 onesweep_kernel(const PassParams prm) {
   using Shape = PassShape<UK, VB, THREADS, ITEMS>;
@@ -477,6 +483,7 @@ onesweep_kernel(const PassParams prm) {
   __shared__ unsigned s_scan[kRadix / kWarp];
   __shared__ unsigned s_next;
   __shared__ UK s_split[SPLIT ? kRadix : 1];
+  __shared__ unsigned long long s_split_idx[TIES ? kRadix : 1];
   __shared__ unsigned s_run_start[SPLIT ? kRadix : 1], s_run_len[SPLIT ? kRadix : 1];  // partition: runs of the parked tile
   __shared__ UK* s_bucket_keys[SPLIT ? kRadix : 1];
   __shared__ V* s_bucket_vals[SPLIT ? kRadix : 1];
@@ -513,25 +520,46 @@ onesweep_kernel(const PassParams prm) {
   // reorder, in a byte per sorted slot in shared memory until the scatter. Up to seven splitters
   // (eight GPUs) live in registers, padded with the largest key: three compare-and-select levels.
   UK sp[SPLIT ? 7 : 1];
+  unsigned long long spi[TIES ? 7 : 1];  // TIES: the splitters' indices (padding: the largest index)
   const bool few = SPLIT && num_split <= 7;
+  static_assert(SPLIT || !TIES, "ties belong to the partition form");
   if constexpr (SPLIT) {
 #pragma unroll
-    for (int j = 0; j < 7; ++j)
-      sp[j] = (few && (unsigned)j < num_split) ? static_cast<const UK*>(prm.splitters)[j] : (UK)~(UK)0;
-    for (unsigned i = threadIdx.x; i < num_split; i += THREADS) s_split[i] = static_cast<const UK*>(prm.splitters)[i];
+    for (int j = 0; j < 7; ++j) {
+      const bool real = few && (unsigned)j < num_split;
+      sp[j] = real ? static_cast<const UK*>(prm.splitters)[j] : (UK)~(UK)0;
+      if constexpr (TIES) spi[j] = real ? prm.splitter_index[j] : ~0ull;
+    }
+    for (unsigned i = threadIdx.x; i < num_split; i += THREADS) {
+      s_split[i] = static_cast<const UK*>(prm.splitters)[i];
+      if constexpr (TIES) s_split_idx[i] = prm.splitter_index[i];
+    }
   }
-  auto digit = [&](UK k) -> unsigned {
+  // is splitter number i (registers: REG) strictly below the element (k, g)? Without TIES keys alone decide.
+  auto below = [&](UK s_, unsigned long long si, UK k, unsigned long long g) -> bool {
+    if constexpr (TIES) return s_ < k || (s_ == k && si < g);
+    else return s_ < k;
+  };
+  auto idx_of = [&](int a, int b, bool pick_a) -> unsigned long long {  // spi[pick_a ? a : b] without touching spi when unused
+    if constexpr (TIES) return pick_a ? spi[a] : spi[b];
+    else return 0ull;
+  };
+  // g: the element's global index (only read with ties)
+  auto digit = [&](UK k, unsigned long long g = ~0ull) -> unsigned {
     if constexpr (SPLIT) {
       if (few) {
-        const bool c1 = sp[3] < k;
-        const bool c2 = (c1 ? sp[5] : sp[1]) < k;
-        const bool c3 = (c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0])) < k;
+        const bool c1 = below(sp[3], idx_of(3, 3, true), k, g);
+        const bool c2 = below(c1 ? sp[5] : sp[1], idx_of(5, 1, c1), k, g);
+        const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]),
+                              c1 ? idx_of(6, 4, c2) : idx_of(2, 0, c2), k, g);
         return 4u * c1 + 2u * c2 + (unsigned)c3;
       }
       unsigned lo = 0, hi = num_split;  // binary search over the ascending splitters
       while (lo < hi) {
         const unsigned mid = (lo + hi) >> 1;
-        if (s_split[mid] < k) lo = mid + 1; else hi = mid;
+        unsigned long long si = 0;
+        if constexpr (TIES) si = s_split_idx[mid];
+        if (below(s_split[mid], si, k, g)) lo = mid + 1; else hi = mid;
       }
       return lo;
     } else {
@@ -703,7 +731,10 @@ onesweep_kernel(const PassParams prm) {
     const unsigned lt_mask = lanemask_lt();
 #pragma unroll
     for (int j = 0; j < ITEMS; ++j) {
-      const unsigned d = digit(key[j]);
+      // (warp-striped: round j of lane l is element warp_off + j * 32 + l of the tile)
+      // padding (all-ones keys behind the input's end) lies above every splitter pair
+      const unsigned at_ = warp_off + j * kWarp + lane;
+      const unsigned d = digit(key[j], at_ < tile_valid ? prm.index_base + tile_base + at_ : ~0ull);
       if constexpr (SPLIT) bkt[j] = (unsigned char)d;
       const unsigned peers = SPLIT ? match_digit_bits(d, split_bits) : match_digit(d);
       const unsigned ahead = __popc(peers & lt_mask);
@@ -750,7 +781,7 @@ onesweep_kernel(const PassParams prm) {
       count += c;
     }
     // padding (all-ones keys at the end of the tile) carries the largest digit in use
-    if (d_own == (SPLIT ? digit((UK)~(UK)0) : mask)) count -= (unsigned)TILE - tile_valid;
+    if (d_own == (SPLIT ? digit((UK)~(UK)0, ~0ull) : mask)) count -= (unsigned)TILE - tile_valid;
     if (grp == 0) {
       DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d_own;
       if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
@@ -886,7 +917,7 @@ inline int sm_count_of_device(int* sms) {
   if (dev < 64) cached[dev] = *sms;
   return TB200_OK;
 }
-template <typename UK, int VB, typename DescT, bool SPLIT> struct PassTag {};
+template <typename UK, int VB, typename DescT, bool SPLIT, bool TIES = false> struct PassTag {};
 template <typename UK> struct ByteHistTag {};
 
 struct Layout {
@@ -983,6 +1014,8 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.desc = base + lay.desc_off;
   prm.splitters = nullptr;
   prm.num_splitters = 0;
+  prm.splitter_index = nullptr;
+  prm.index_base = 0;
   prm.bucket_keys = nullptr;
   prm.bucket_vals = nullptr;
   auto launch = [&](auto kernel, auto tag) -> int {
@@ -1021,13 +1054,19 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
 template <typename UK>
 __global__ void __launch_bounds__(kHistThreads)
 bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __restrict__ splitters, unsigned num_split,
-                        SortCtl* ctl) {
+                        SortCtl* ctl, const unsigned long long* __restrict__ splitter_index,
+                        unsigned long long index_base) {
   __shared__ unsigned s_hist[kRadix];
   __shared__ UK s_split[kRadix];
+  __shared__ unsigned long long s_split_idx[kRadix];
+  const bool ties = splitter_index != nullptr;  // splitters and elements are (key, index) pairs
   __shared__ unsigned s_last;
   __shared__ unsigned long long s_warp_tot[8];
   for (int i = threadIdx.x; i < kRadix; i += kHistThreads) s_hist[i] = 0;
-  for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) s_split[i] = splitters[i];
+  for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) {
+    s_split[i] = splitters[i];
+    s_split_idx[i] = ties ? splitter_index[i] : ~0ull;
+  }
   __syncthreads();
   // Two forms. Up to seven splitters (eight GPUs): the splitters live in registers, padded with
   // the largest key, the search is at most three compare-and-select levels, and every thread
@@ -1037,8 +1076,16 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
   // atomics do not serialise.
   const bool few = num_split <= 7;
   UK sp[7];
+  unsigned long long spi[7];
 #pragma unroll
-  for (int j = 0; j < 7; ++j) sp[j] = (few && (unsigned)j < num_split) ? s_split[j] : (UK)~(UK)0;
+  for (int j = 0; j < 7; ++j) {
+    const bool real = few && (unsigned)j < num_split;
+    sp[j] = real ? s_split[j] : (UK)~(UK)0;
+    spi[j] = real ? s_split_idx[j] : ~0ull;
+  }
+  auto below = [&](UK s_, unsigned long long si, UK k, unsigned long long g) -> bool {
+    return s_ < k || (ties && s_ == k && si < g);
+  };
   unsigned long long packed = 0;
   unsigned since = 0;
   auto flush = [&]() {
@@ -1050,24 +1097,25 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
     packed = 0;
     since = 0;
   };
-  auto bucket_few = [&](UK k) -> unsigned {  // number of splitters strictly below k
-    if (num_split <= 1) return sp[0] < k;
+  auto bucket_few = [&](UK k, unsigned long long g) -> unsigned {  // number of splitters strictly below (k, g)
+    if (num_split <= 1) return below(sp[0], spi[0], k, g);
     if (num_split <= 3) {
-      const bool c1 = sp[1] < k;
-      return 2u * c1 + (unsigned)((c1 ? sp[2] : sp[0]) < k);
+      const bool c1 = below(sp[1], spi[1], k, g);
+      return 2u * c1 + (unsigned)below(c1 ? sp[2] : sp[0], c1 ? spi[2] : spi[0], k, g);
     }
-    const bool c1 = sp[3] < k;
-    const bool c2 = (c1 ? sp[5] : sp[1]) < k;
-    const bool c3 = (c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0])) < k;
+    const bool c1 = below(sp[3], spi[3], k, g);
+    const bool c2 = below(c1 ? sp[5] : sp[1], c1 ? spi[5] : spi[1], k, g);
+    const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]),
+                          c1 ? (c2 ? spi[6] : spi[4]) : (c2 ? spi[2] : spi[0]), k, g);
     return 4u * c1 + 2u * c2 + (unsigned)c3;
   };
   const int split_bits = 32 - __clz(num_split | 1u);
   const unsigned lt_mask = lanemask_lt();
-  auto count_many = [&](UK k, bool valid) {
+  auto count_many = [&](UK k, unsigned long long g, bool valid) {
     unsigned lo = 0, hi = num_split;
     while (lo < hi) {
       const unsigned mid = (lo + hi) >> 1;
-      if (s_split[mid] < k) lo = mid + 1; else hi = mid;
+      if (below(s_split[mid], s_split_idx[mid], k, g)) lo = mid + 1; else hi = mid;
     }
     unsigned peers = match_digit_bits(lo, split_bits) & __ballot_sync(0xffffffffu, valid);
     if (valid && (peers & lt_mask) == 0) atomicAdd(&s_hist[lo], (unsigned)__popc(peers));
@@ -1084,14 +1132,16 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
 #pragma unroll
       for (int u = 0; u < kHistUnroll; ++u)
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) packed += 1ull << (8 * bucket_few(v[u].v[j]));
+        for (int j = 0; j < VEC; ++j)
+          packed += 1ull << (8 * bucket_few(v[u].v[j], index_base + c * CHUNK + (uint64_t)(u * kHistThreads + threadIdx.x) * VEC + j));
       since += VEC * kHistUnroll;
       if (since + VEC * kHistUnroll > 255u) flush();
     } else {
 #pragma unroll
       for (int u = 0; u < kHistUnroll; ++u)
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) count_many(v[u].v[j], true);
+        for (int j = 0; j < VEC; ++j)
+          count_many(v[u].v[j], index_base + c * CHUNK + (uint64_t)(u * kHistThreads + threadIdx.x) * VEC + j, true);
     }
   }
   for (uint64_t base = full_chunks * CHUNK + (uint64_t)blockIdx.x * kHistThreads; base < n;
@@ -1100,11 +1150,11 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
     const bool valid = i < n;
     if (few) {
       if (valid) {
-        packed += 1ull << (8 * bucket_few(keys[i]));
+        packed += 1ull << (8 * bucket_few(keys[i], index_base + i));
         if (++since >= 255u) flush();
       }
     } else {
-      count_many(valid ? keys[i] : UK(0), valid);
+      count_many(valid ? keys[i] : UK(0), index_base + i, valid);
     }
   }
   if (few) flush();
@@ -1149,7 +1199,8 @@ template <typename UK, int VB>
 int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, void* d_keys_out,
                    void* d_vals_out, uint64_t n, const void* d_splitters, unsigned num_splitters,
                    uint64_t* d_counts, cudaStream_t stream, int phase = kPhaseAll,
-                   void* const* h_bucket_keys = nullptr, void* const* h_bucket_vals = nullptr) {
+                   void* const* h_bucket_keys = nullptr, void* const* h_bucket_vals = nullptr,
+                   const uint64_t* d_splitter_index = nullptr, uint64_t index_base = 0) {
   using T = Tuning<UK, VB>;
   using Shape = PassShape<UK, VB, T::kThreads, T::kItems>;
   constexpr uint64_t TILE = Shape::kTile;
@@ -1187,7 +1238,9 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
     const uint64_t want = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
     const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
     bucket_histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n,
-                                                                   static_cast<const UK*>(d_splitters), num_splitters, ctl);
+                                                                   static_cast<const UK*>(d_splitters), num_splitters, ctl,
+                                                                   reinterpret_cast<const unsigned long long*>(d_splitter_index),
+                                                                   index_base);
     trace_mark(stream, kTracePartitionHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
     TB200_CUDA_TRY(cudaMemcpyAsync(d_counts, &ctl->hist[0][0], (num_splitters + 1) * sizeof(uint64_t),
@@ -1224,6 +1277,8 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   prm.mask = num_splitters;
   prm.splitters = d_splitters;
   prm.num_splitters = num_splitters;
+  prm.splitter_index = reinterpret_cast<const unsigned long long*>(d_splitter_index);
+  prm.index_base = index_base;
   prm.bucket_keys = d_bucket_keys;
   prm.bucket_vals = d_bucket_vals;
   auto launch = [&](auto kernel, auto tag) -> int {
@@ -1236,6 +1291,12 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
     trace_mark(stream, kTracePartitionPass);
     return (int)cudaGetLastError();
   };
+  // pairs (key, index) are a kernel of their own: the indices cost registers that the plain form keeps
+  if (d_splitter_index != nullptr)
+    return wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true, true>,
+                         PassTag<UK, VB, unsigned long long, true, true>{})
+                : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true, true>,
+                         PassTag<UK, VB, unsigned, true, true>{});
   const int rc = wide ? launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned long long, true>,
                                PassTag<UK, VB, unsigned long long, true>{})
                       : launch(onesweep_kernel<UK, VB, T::kThreads, T::kItems, T::kMinCtas, unsigned, true>,
@@ -1282,16 +1343,16 @@ extern "C" int tb200_radix_sort(void* d_temp, size_t* temp_bytes, void* d_keys, 
   }
 }
 
-extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
-                               void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
-                               const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
-                               tb200_stream_t stream) {
+extern "C" int tb200_partition_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                                    void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
+                                    const void* d_splitters, const uint64_t* d_splitter_index, uint32_t num_splitters,
+                                    uint64_t index_base, uint64_t* d_counts, tb200_stream_t stream) {
   using namespace tb200;
   if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
   if (num_splitters > 255) return TB200_ERR_INVALID_ARGUMENT;
 #define TB200_PART(UK, VB) \
   return partition_impl<UK, VB>(d_temp, temp_bytes, d_keys, d_vals, d_keys_out, d_vals_out, n, d_splitters, \
-                                num_splitters, d_counts, stream)
+                                num_splitters, d_counts, stream, kPhaseAll, nullptr, nullptr, d_splitter_index, index_base)
   if (key_dtype == TB200_U64) {
     if (val_bytes == 0) TB200_PART(unsigned long long, 0);
     if (val_bytes == 4) TB200_PART(unsigned long long, 4);
@@ -1305,16 +1366,25 @@ extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_k
   return TB200_ERR_UNSUPPORTED;
 }
 
+extern "C" int tb200_partition(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                               void* d_keys_out, void* d_vals_out, uint64_t n, int key_dtype, int val_bytes,
+                               const void* d_splitters, uint32_t num_splitters, uint64_t* d_counts,
+                               tb200_stream_t stream) {
+  return tb200_partition_ties(d_temp, temp_bytes, d_keys, d_vals, d_keys_out, d_vals_out, n, key_dtype, val_bytes,
+                              d_splitters, nullptr, num_splitters, 0, d_counts, stream);
+}
+
 namespace tb200 {
 namespace {
 int partition_phase(int phase, void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals, uint64_t n,
                     int key_dtype, int val_bytes, const void* d_splitters, uint32_t num_splitters,
-                    uint64_t* d_counts, void* const* h_bucket_keys, void* const* h_bucket_vals, cudaStream_t stream) {
+                    uint64_t* d_counts, void* const* h_bucket_keys, void* const* h_bucket_vals, cudaStream_t stream,
+                    const uint64_t* d_splitter_index = nullptr, uint64_t index_base = 0) {
   if (temp_bytes == nullptr) return TB200_ERR_INVALID_ARGUMENT;
   if (num_splitters > 255) return TB200_ERR_INVALID_ARGUMENT;
 #define TB200_PART(UK, VB) \
   return partition_impl<UK, VB>(d_temp, temp_bytes, d_keys, d_vals, nullptr, nullptr, n, d_splitters, num_splitters, \
-                                d_counts, stream, phase, h_bucket_keys, h_bucket_vals)
+                                d_counts, stream, phase, h_bucket_keys, h_bucket_vals, d_splitter_index, index_base)
   if (key_dtype == TB200_U64) {
     if (val_bytes == 0) TB200_PART(unsigned long long, 0);
     if (val_bytes == 4) TB200_PART(unsigned long long, 4);
@@ -1343,6 +1413,25 @@ extern "C" int tb200_partition_scatter(void* d_temp, size_t* temp_bytes, const v
                                        void* const* h_bucket_vals, tb200_stream_t stream) {
   return tb200::partition_phase(tb200::kPhaseFinish, d_temp, temp_bytes, d_keys, d_vals, n, key_dtype, val_bytes,
                                 d_splitters, num_splitters, nullptr, h_bucket_keys, h_bucket_vals, stream);
+}
+
+extern "C" int tb200_partition_count_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, uint64_t n,
+                                          int key_dtype, int val_bytes, const void* d_splitters,
+                                          const uint64_t* d_splitter_index, uint32_t num_splitters, uint64_t index_base,
+                                          uint64_t* d_counts, tb200_stream_t stream) {
+  return tb200::partition_phase(tb200::kPhaseBegin, d_temp, temp_bytes, d_keys, nullptr, n, key_dtype, val_bytes,
+                                d_splitters, num_splitters, d_counts, nullptr, nullptr, stream, d_splitter_index,
+                                index_base);
+}
+
+extern "C" int tb200_partition_scatter_ties(void* d_temp, size_t* temp_bytes, const void* d_keys, const void* d_vals,
+                                            uint64_t n, int key_dtype, int val_bytes, const void* d_splitters,
+                                            const uint64_t* d_splitter_index, uint32_t num_splitters,
+                                            uint64_t index_base, void* const* h_bucket_keys,
+                                            void* const* h_bucket_vals, tb200_stream_t stream) {
+  return tb200::partition_phase(tb200::kPhaseFinish, d_temp, temp_bytes, d_keys, d_vals, n, key_dtype, val_bytes,
+                                d_splitters, num_splitters, nullptr, h_bucket_keys, h_bucket_vals, stream,
+                                d_splitter_index, index_base);
 }
 
 // ---------------------------------------------------------------------------------------

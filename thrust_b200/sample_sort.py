@@ -80,33 +80,38 @@ class DeviceOps:
                    "tb200_histogram_sorted")
         return counts.to(torch.int64) & 0xFFFFFFFF
 
+    # In the three partition calls ``split_idx`` (int64 tensor or None) turns splitters and elements into
+    # (key, index) pairs, element g of the shard having index ``index_base + g``: equal keys can then
+    # be divided between buckets, in input order.
     def partition(self, keys: torch.Tensor, vals: torch.Tensor, n: int, splitters: torch.Tensor,
-                  out_k: torch.Tensor, out_v: torch.Tensor) -> torch.Tensor:
+                  out_k: torch.Tensor, out_v: torch.Tensor, split_idx: Optional[torch.Tensor] = None,
+                  index_base: int = 0) -> torch.Tensor:
         """Stable partition into len(splitters)+1 buckets; returns the bucket sizes (int64 tensor)."""
         capi = self.capi
         counts = torch.empty(splitters.numel() + 1, dtype=torch.int64, device=self.device)
         have = C.c_size_t(self.temp.numel())
-        capi.check(capi.lib.tb200_partition(C.c_void_p(self.temp.data_ptr()), C.byref(have),
-                                            C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
-                                            C.c_void_p(out_k.data_ptr()), C.c_void_p(out_v.data_ptr()), n, capi.U64, 4,
-                                            C.c_void_p(splitters.data_ptr()), splitters.numel(),
-                                            C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
+        capi.check(capi.lib.tb200_partition_ties(
+            C.c_void_p(self.temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()),
+            C.c_void_p(out_k.data_ptr()), C.c_void_p(out_v.data_ptr()), n, capi.U64, 4,
+            C.c_void_p(splitters.data_ptr()), C.c_void_p(split_idx.data_ptr()) if split_idx is not None else None,
+            splitters.numel(), index_base, C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition")
         return counts
 
-    def partition_count(self, keys: torch.Tensor, n: int, splitters: torch.Tensor) -> torch.Tensor:
+    def partition_count(self, keys: torch.Tensor, n: int, splitters: torch.Tensor,
+                        split_idx: Optional[torch.Tensor] = None, index_base: int = 0) -> torch.Tensor:
         """Bucket sizes of the stable partition by ``splitters`` (int64 tensor); first half of a push."""
         capi = self.capi
         counts = torch.empty(splitters.numel() + 1, dtype=torch.int64, device=self.device)
         have = C.c_size_t(self.temp.numel())
-        capi.check(capi.lib.tb200_partition_count(C.c_void_p(self.temp.data_ptr()), C.byref(have),
-                                                  C.c_void_p(keys.data_ptr()), n, capi.U64, 4,
-                                                  C.c_void_p(splitters.data_ptr()), splitters.numel(),
-                                                  C.c_void_p(counts.data_ptr()), self._stream()),
-                   "tb200_partition_count")
+        capi.check(capi.lib.tb200_partition_count_ties(
+            C.c_void_p(self.temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), n, capi.U64, 4,
+            C.c_void_p(splitters.data_ptr()), C.c_void_p(split_idx.data_ptr()) if split_idx is not None else None,
+            splitters.numel(), index_base, C.c_void_p(counts.data_ptr()), self._stream()), "tb200_partition_count")
         return counts
 
     def partition_scatter(self, keys: torch.Tensor, vals: torch.Tensor, n: int, splitters: torch.Tensor,
-                          bucket_keys, bucket_vals) -> None:
+                          bucket_keys, bucket_vals, split_idx: Optional[torch.Tensor] = None,
+                          index_base: int = 0) -> None:
         """Second half: bucket b goes to the device addresses bucket_keys[b] / bucket_vals[b]
         (integers; peer mappings allowed)."""
         capi = self.capi
@@ -114,10 +119,11 @@ class DeviceOps:
         pk = (C.c_void_p * g)(*bucket_keys)
         pv = (C.c_void_p * g)(*bucket_vals)
         have = C.c_size_t(self.temp.numel())
-        capi.check(capi.lib.tb200_partition_scatter(C.c_void_p(self.temp.data_ptr()), C.byref(have),
-                                                    C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), n,
-                                                    capi.U64, 4, C.c_void_p(splitters.data_ptr()), splitters.numel(),
-                                                    pk, pv, self._stream()), "tb200_partition_scatter")
+        capi.check(capi.lib.tb200_partition_scatter_ties(
+            C.c_void_p(self.temp.data_ptr()), C.byref(have), C.c_void_p(keys.data_ptr()), C.c_void_p(vals.data_ptr()), n,
+            capi.U64, 4, C.c_void_p(splitters.data_ptr()),
+            C.c_void_p(split_idx.data_ptr()) if split_idx is not None else None, splitters.numel(), index_base,
+            pk, pv, self._stream()), "tb200_partition_scatter")
 
     def sort_begin(self, n: int) -> None:
         """First half of sort_pairs: clears the scratch; the key gather then counts the digits."""
@@ -322,8 +328,23 @@ class ShardedSorter:
         mine = keys[pos].contiguous()
         gathered = torch.empty(G * mine.numel(), dtype=torch.int64, device=self.device)
         dist.all_gather_into_tensor(gathered, mine, group=self.group)
-        self.ops.sort_keys(gathered)
+        split_idx, index_base = None, self.rank * n
+        if sort_first:
+            self.ops.sort_keys(gathered)
+        else:
+            # The sample also tells whether a few keys make up so much of the input that all copies of one
+            # key cannot go to one rank. Then elements are compared as (key, global index) pairs, and so
+            # are the splitters: the sample is sorted with each key's ordinal as its value (a stable sort
+            # of a rank-major, position-ascending sample leaves equal keys in index order).
+            ordinal = torch.arange(gathered.numel(), dtype=torch.int32, device=self.device)
+            self.ops.sort_pairs(gathered, ordinal, gathered.numel())
+            heaviest = int(torch.unique_consecutive(gathered, return_counts=True)[1].max())
+            if heaviest * 16 >= mine.numel():  # one key holds a sixteenth of a rank's share or more
+                where = ordinal.long()
+                sample_index = (where // mine.numel()) * n + pos[where % mine.numel()]
+                split_idx = pick_splitters(sample_index, G).contiguous()
         splitters = pick_splitters(gathered, G).contiguous()
+        self.split_ties = split_idx is not None
         self._mark("sample_and_splitters")
         if sort_first:
             # contiguous send segments of the sorted shard
@@ -331,10 +352,10 @@ class ShardedSorter:
             send = torch.cat([head, (n - head.sum()).reshape(1)])
             src_k, src_v = keys, vals
         elif self.exchange == "push":
-            send = self.ops.partition_count(keys, n, splitters)
+            send = self.ops.partition_count(keys, n, splitters, split_idx, index_base)
             src_k = src_v = None
         else:
-            send = self.ops.partition(keys, vals, n, splitters, self.part_k, self.part_v)
+            send = self.ops.partition(keys, vals, n, splitters, self.part_k, self.part_v, split_idx, index_base)
             src_k, src_v = self.part_k, self.part_v
         self._mark("segments" if sort_first else ("bucket_counts" if self.exchange == "push" else "partition"))
         # 5. the whole G x G count matrix goes to every rank (row r = what rank r sends), so all
@@ -357,7 +378,7 @@ class ShardedSorter:
             off = push_offsets(mat.tolist(), self.rank)
             self.ops.partition_scatter(keys, vals, n, splitters,
                                        [self.peer_k[b] + 8 * off[b] for b in range(G)],
-                                       [self.peer_v[b] + 4 * off[b] for b in range(G)])
+                                       [self.peer_v[b] + 4 * off[b] for b in range(G)], split_idx, index_base)
             # every rank's stores have landed once every rank's partition kernel has finished
             dist.barrier(group=self.group)
             self._mark("partition_and_exchange")
