@@ -1051,21 +1051,20 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
 // ---------------------------------------------------------------------------------
 // stable multi-way partition by splitters (one onesweep pass with bucket ids as digits)
 // ---------------------------------------------------------------------------------
-template <typename UK>
+template <typename UK, bool TIES>
 __global__ void __launch_bounds__(kHistThreads)
 bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __restrict__ splitters, unsigned num_split,
                         SortCtl* ctl, const unsigned long long* __restrict__ splitter_index,
                         unsigned long long index_base) {
   __shared__ unsigned s_hist[kRadix];
   __shared__ UK s_split[kRadix];
-  __shared__ unsigned long long s_split_idx[kRadix];
-  const bool ties = splitter_index != nullptr;  // splitters and elements are (key, index) pairs
+  __shared__ unsigned long long s_split_idx[TIES ? kRadix : 1];  // TIES: splitters and elements are (key, index) pairs
   __shared__ unsigned s_last;
   __shared__ unsigned long long s_warp_tot[8];
   for (int i = threadIdx.x; i < kRadix; i += kHistThreads) s_hist[i] = 0;
   for (unsigned i = threadIdx.x; i < num_split; i += kHistThreads) {
     s_split[i] = splitters[i];
-    s_split_idx[i] = ties ? splitter_index[i] : ~0ull;
+    if constexpr (TIES) s_split_idx[i] = splitter_index[i];
   }
   __syncthreads();
   // Two forms. Up to seven splitters (eight GPUs): the splitters live in registers, padded with
@@ -1076,15 +1075,20 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
   // atomics do not serialise.
   const bool few = num_split <= 7;
   UK sp[7];
-  unsigned long long spi[7];
+  unsigned long long spi[TIES ? 7 : 1];
 #pragma unroll
   for (int j = 0; j < 7; ++j) {
     const bool real = few && (unsigned)j < num_split;
     sp[j] = real ? s_split[j] : (UK)~(UK)0;
-    spi[j] = real ? s_split_idx[j] : ~0ull;
+    if constexpr (TIES) spi[j] = real ? s_split_idx[j] : ~0ull;
   }
   auto below = [&](UK s_, unsigned long long si, UK k, unsigned long long g) -> bool {
-    return s_ < k || (ties && s_ == k && si < g);
+    if constexpr (TIES) return s_ < k || (s_ == k && si < g);
+    else return s_ < k;
+  };
+  auto idx_of = [&](int a, int b, bool pick_a) -> unsigned long long {
+    if constexpr (TIES) return pick_a ? spi[a] : spi[b];
+    else return 0ull;
   };
   unsigned long long packed = 0;
   unsigned since = 0;
@@ -1098,15 +1102,14 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
     since = 0;
   };
   auto bucket_few = [&](UK k, unsigned long long g) -> unsigned {  // number of splitters strictly below (k, g)
-    if (num_split <= 1) return below(sp[0], spi[0], k, g);
+    if (num_split <= 1) return below(sp[0], idx_of(0, 0, true), k, g);
     if (num_split <= 3) {
-      const bool c1 = below(sp[1], spi[1], k, g);
-      return 2u * c1 + (unsigned)below(c1 ? sp[2] : sp[0], c1 ? spi[2] : spi[0], k, g);
+      const bool c1 = below(sp[1], idx_of(1, 1, true), k, g);
+      return 2u * c1 + (unsigned)below(c1 ? sp[2] : sp[0], idx_of(2, 0, c1), k, g);
     }
-    const bool c1 = below(sp[3], spi[3], k, g);
-    const bool c2 = below(c1 ? sp[5] : sp[1], c1 ? spi[5] : spi[1], k, g);
-    const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]),
-                          c1 ? (c2 ? spi[6] : spi[4]) : (c2 ? spi[2] : spi[0]), k, g);
+    const bool c1 = below(sp[3], idx_of(3, 3, true), k, g);
+    const bool c2 = below(c1 ? sp[5] : sp[1], idx_of(5, 1, c1), k, g);
+    const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]), c1 ? idx_of(6, 4, c2) : idx_of(2, 0, c2), k, g);
     return 4u * c1 + 2u * c2 + (unsigned)c3;
   };
   const int split_bits = 32 - __clz(num_split | 1u);
@@ -1115,7 +1118,9 @@ bucket_histogram_kernel(const UK* __restrict__ keys, uint64_t n, const UK* __res
     unsigned lo = 0, hi = num_split;
     while (lo < hi) {
       const unsigned mid = (lo + hi) >> 1;
-      if (below(s_split[mid], s_split_idx[mid], k, g)) lo = mid + 1; else hi = mid;
+      unsigned long long si = 0;
+      if constexpr (TIES) si = s_split_idx[mid];
+      if (below(s_split[mid], si, k, g)) lo = mid + 1; else hi = mid;
     }
     unsigned peers = match_digit_bits(lo, split_bits) & __ballot_sync(0xffffffffu, valid);
     if (valid && (peers & lt_mask) == 0) atomicAdd(&s_hist[lo], (unsigned)__popc(peers));
@@ -1237,10 +1242,13 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   if (phase != kPhaseFinish) {
     const uint64_t want = (n + kHistThreads * 16 - 1) / (kHistThreads * 16);
     const unsigned grid = (unsigned)(want < (uint64_t)sms * 4 ? want : (uint64_t)sms * 4);
-    bucket_histogram_kernel<UK><<<grid, kHistThreads, 0, stream>>>(static_cast<const UK*>(d_keys), n,
-                                                                   static_cast<const UK*>(d_splitters), num_splitters, ctl,
-                                                                   reinterpret_cast<const unsigned long long*>(d_splitter_index),
-                                                                   index_base);
+    if (d_splitter_index != nullptr)
+      bucket_histogram_kernel<UK, true><<<grid, kHistThreads, 0, stream>>>(
+          static_cast<const UK*>(d_keys), n, static_cast<const UK*>(d_splitters), num_splitters, ctl,
+          reinterpret_cast<const unsigned long long*>(d_splitter_index), index_base);
+    else
+      bucket_histogram_kernel<UK, false><<<grid, kHistThreads, 0, stream>>>(
+          static_cast<const UK*>(d_keys), n, static_cast<const UK*>(d_splitters), num_splitters, ctl, nullptr, 0);
     trace_mark(stream, kTracePartitionHistogram);
     TB200_CUDA_TRY(cudaGetLastError());
     TB200_CUDA_TRY(cudaMemcpyAsync(d_counts, &ctl->hist[0][0], (num_splitters + 1) * sizeof(uint64_t),
