@@ -24,6 +24,8 @@ constexpr unsigned kSpinLimit = 1u << 22;
 struct TempHeader {
   int status;            // 0 or a tb200_error, written by kernels
   unsigned ticket;       // dynamic tile counter of single-kernel algorithms
+  // aux[0..3]: where the first bounded wait gave up (note_timeout); aux[4..7]: shared-memory addresses of the
+  // by-key kernel's mbarrier arrays (decode a recorded mbarrier time-out); aux[8]: the scouts' ticket counter
   unsigned long long aux[30];
 };
 static_assert(sizeof(TempHeader) <= 256, "header must fit the first 256 bytes");
