@@ -288,9 +288,11 @@ __device__ __forceinline__ void close_block(const TileWords<1>* ctiles, TileWord
 __device__ __forceinline__ void prefetch_l2(const void* p, unsigned bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {  // read-only, not kept in L1
+// read-only 16-byte load that the compiler may schedule freely (measured: keeping the lines in L1 and
+// dropping `volatile` took unique_by_key from 0.48 to 0.45 ms)
+__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
   uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+  asm("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p));
   return r;
@@ -299,10 +301,10 @@ __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {  // read-only, n
 // Heads (FLAGS: non-zero elements) of one whole tile of NP 16-byte packs that starts at the
 // 16-byte aligned keys + base; one warp. The scouts share their SM's issue slots with sixteen
 // compute warps, so what counts here is the number of instructions per pack: lane-strided
-// 16-byte loads kept U deep in flight (a pack is counted, then its buffer is loaded again), the
-// element in front of a pack from the neighbouring lane by one shuffle, and the first element of
-// every row (lane 0 has no neighbour) compared with its predecessor in a pass of its own: a
-// lane per row, two small loads each, issued before the packs and added at the end.
+// 16-byte loads kept U deep in flight (a pack is counted, then its buffer is loaded again), and
+// the element in front of a pack by a small load of its own that travels with the pack (it hits
+// L1: the line belongs to the neighbouring lane's pack). No shuffle: nothing orders the rows, so
+// their latencies overlap.
 template <typename K, bool FLAGS, int NP>
 __device__ unsigned count_heads_tile(const K* keys, uint64_t base) {
   constexpr int EP = 16 / (int)sizeof(K);
@@ -311,21 +313,17 @@ __device__ unsigned count_heads_tile(const K* keys, uint64_t base) {
   constexpr bool kRagged = NP % kWarp != 0;  // the last row is not full
   const unsigned lane = lane_id();
   const uint4* src = reinterpret_cast<const uint4*>(keys + base);
-  unsigned row_heads = 0;  // heads among the first elements of the rows
-  if constexpr (!FLAGS) {
-#pragma unroll
-    for (int r = 0; r < ROWS; r += kWarp) {
-      const uint64_t g = base + (uint64_t)(r + lane) * kWarp * EP;
-      if (r + (int)lane < ROWS) row_heads += (unsigned)(g == 0 || !(keys[g] == keys[g - 1]));
-    }
-  }
+  const K* first = keys + base;
   uint4 q[U];
-  auto load = [&](int r, uint4& qq) {
+  K front[U];  // the element in front of the pack: the line is in L1 (the neighbouring lane's pack)
+  auto load = [&](int r, uint4& qq, K& ff) {
     const unsigned pk = (unsigned)r * kWarp + lane;
-    qq = (!kRagged || pk < (unsigned)NP) ? ld_stream_v4(src + pk) : uint4{0u, 0u, 0u, 0u};
+    const bool in = !kRagged || pk < (unsigned)NP;
+    qq = in ? ld_stream_v4(src + pk) : uint4{0u, 0u, 0u, 0u};
+    if constexpr (!FLAGS) ff = (in && (base != 0 || pk != 0)) ? first[(long long)pk * EP - 1] : K{};
   };
 #pragma unroll
-  for (int u = 0; u < U; ++u) load(u, q[u]);
+  for (int u = 0; u < U; ++u) load(u, q[u], front[u]);
   unsigned cnt = 0;
 #pragma unroll 1
   for (int r0 = 0; r0 < ROWS; r0 += U) {
@@ -334,24 +332,24 @@ __device__ unsigned count_heads_tile(const K* keys, uint64_t base) {
       const int r = r0 + u;
       if (ROWS % U == 0 || r < ROWS) {  // the same for all lanes
         const Pack<K, EP> e = *reinterpret_cast<const Pack<K, EP>*>(&q[u]);
-        if (r + U < ROWS) load(r + U, q[u]);
-        const bool in = !kRagged || (unsigned)r * kWarp + lane < (unsigned)NP;
+        const K prev = front[u];
+        if (r + U < ROWS) load(r + U, q[u], front[u]);
+        const unsigned pk = (unsigned)r * kWarp + lane;
+        const bool in = !kRagged || pk < (unsigned)NP;
+        unsigned c = 0;
         if constexpr (FLAGS) {
-          unsigned c = 0;
 #pragma unroll
           for (int i = 0; i < EP; ++i) c += (unsigned)(e.v[i] != K(0));
-          cnt += in ? c : 0u;
         } else {
-          const K prev = __shfl_up_sync(0xffffffffu, e.v[EP - 1], 1);
-          unsigned c = lane == 0 ? 0u : (unsigned)!(e.v[0] == prev);  // lane 0's first element: counted in row_heads
+          c = (unsigned)((base == 0 && pk == 0) || !(e.v[0] == prev));  // the input's first element is a head
 #pragma unroll
           for (int i = 1; i < EP; ++i) c += (unsigned)!(e.v[i] == e.v[i - 1]);
-          cnt += in ? c : 0u;
         }
+        cnt += in ? c : 0u;
       }
     }
   }
-  return __reduce_add_sync(0xffffffffu, cnt + row_heads);
+  return __reduce_add_sync(0xffffffffu, cnt);
 }
 
 // The same for any `count` elements of keys[base, base + count): the last tile of an input and
