@@ -335,11 +335,10 @@ struct PassParams {
   void* desc;
   const void* splitters;   // partition mode: ascending splitters (device), else unused
   unsigned num_splitters;
-  // partition mode, optional: splitter i is the PAIR (splitters[i], splitter_index[i]) and element g
-  // of the input is the pair (key, index_base + g); pairs compare by key, then by index. Equal
-  // keys can then be split between buckets (in input order). Null: keys alone decide.
-  const unsigned long long* splitter_index;
-  unsigned long long index_base;
+  // (The pair form of the partition, TIES, finds its two extra arguments in the control block,
+  // ctl->offs[3][0..1]: the splitters' indices and the index of the input's first element. They are
+  // kept out of this struct on purpose: a larger parameter block changed the register allocation of
+  // the plain radix pass and cost it 3 %.)
   // partition mode: device tables of num_splitters + 1 pointers, the first element of every
   // bucket's output (keys, values); the buckets may live in different allocations, another
   // GPU's memory included. Null: bucket b starts at element offs[0][b] of the alternate arrays.
@@ -523,47 +522,63 @@ onesweep_kernel(const PassParams prm) {
   unsigned long long spi[TIES ? 7 : 1];  // TIES: the splitters' indices (padding: the largest index)
   const bool few = SPLIT && num_split <= 7;
   static_assert(SPLIT || !TIES, "ties belong to the partition form");
+  // TIES: splitter i is the PAIR (splitters[i], splitter_index[i]) and element g of the input is the pair
+  // (key, index_base + g); pairs compare by key, then by index
+  const unsigned long long* splitter_index = nullptr;
+  unsigned long long index_base = 0;
+  if constexpr (TIES) {
+    splitter_index = reinterpret_cast<const unsigned long long*>(ctl->offs[3][0]);
+    index_base = ctl->offs[3][1];
+  }
   if constexpr (SPLIT) {
 #pragma unroll
     for (int j = 0; j < 7; ++j) {
       const bool real = few && (unsigned)j < num_split;
       sp[j] = real ? static_cast<const UK*>(prm.splitters)[j] : (UK)~(UK)0;
-      if constexpr (TIES) spi[j] = real ? prm.splitter_index[j] : ~0ull;
+      if constexpr (TIES) spi[j] = real ? splitter_index[j] : ~0ull;
     }
     for (unsigned i = threadIdx.x; i < num_split; i += THREADS) {
       s_split[i] = static_cast<const UK*>(prm.splitters)[i];
-      if constexpr (TIES) s_split_idx[i] = prm.splitter_index[i];
+      if constexpr (TIES) s_split_idx[i] = splitter_index[i];
     }
   }
-  // is splitter number i (registers: REG) strictly below the element (k, g)? Without TIES keys alone decide.
-  auto below = [&](UK s_, unsigned long long si, UK k, unsigned long long g) -> bool {
-    if constexpr (TIES) return s_ < k || (s_ == k && si < g);
-    else return s_ < k;
-  };
-  auto idx_of = [&](int a, int b, bool pick_a) -> unsigned long long {  // spi[pick_a ? a : b] without touching spi when unused
-    if constexpr (TIES) return pick_a ? spi[a] : spi[b];
-    else return 0ull;
-  };
-  // g: the element's global index (only read with ties)
-  auto digit = [&](UK k, unsigned long long g = ~0ull) -> unsigned {
+  auto digit = [&](UK k) -> unsigned {
     if constexpr (SPLIT) {
       if (few) {
-        const bool c1 = below(sp[3], idx_of(3, 3, true), k, g);
-        const bool c2 = below(c1 ? sp[5] : sp[1], idx_of(5, 1, c1), k, g);
-        const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]),
-                              c1 ? idx_of(6, 4, c2) : idx_of(2, 0, c2), k, g);
+        const bool c1 = sp[3] < k;
+        const bool c2 = (c1 ? sp[5] : sp[1]) < k;
+        const bool c3 = (c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0])) < k;
         return 4u * c1 + 2u * c2 + (unsigned)c3;
       }
       unsigned lo = 0, hi = num_split;  // binary search over the ascending splitters
       while (lo < hi) {
         const unsigned mid = (lo + hi) >> 1;
-        unsigned long long si = 0;
-        if constexpr (TIES) si = s_split_idx[mid];
-        if (below(s_split[mid], si, k, g)) lo = mid + 1; else hi = mid;
+        if (s_split[mid] < k) lo = mid + 1; else hi = mid;
       }
       return lo;
     } else {
       return digit_of(k, shift, mask);
+    }
+  };
+  // TIES: the bucket of the PAIR (k, g): the number of splitter pairs strictly below it
+  auto digit_pair = [&](UK k, unsigned long long g) -> unsigned {
+    if constexpr (TIES) {
+      auto below = [&](UK s_, unsigned long long si) -> bool { return s_ < k || (s_ == k && si < g); };
+      if (few) {
+        const bool c1 = below(sp[3], spi[3]);
+        const bool c2 = below(c1 ? sp[5] : sp[1], c1 ? spi[5] : spi[1]);
+        const bool c3 = below(c1 ? (c2 ? sp[6] : sp[4]) : (c2 ? sp[2] : sp[0]),
+                              c1 ? (c2 ? spi[6] : spi[4]) : (c2 ? spi[2] : spi[0]));
+        return 4u * c1 + 2u * c2 + (unsigned)c3;
+      }
+      unsigned lo = 0, hi = num_split;
+      while (lo < hi) {
+        const unsigned mid = (lo + hi) >> 1;
+        if (below(s_split[mid], s_split_idx[mid])) lo = mid + 1; else hi = mid;
+      }
+      return lo;
+    } else {
+      return 0u;
     }
   };
 
@@ -733,8 +748,13 @@ onesweep_kernel(const PassParams prm) {
     for (int j = 0; j < ITEMS; ++j) {
       // (warp-striped: round j of lane l is element warp_off + j * 32 + l of the tile)
       // padding (all-ones keys behind the input's end) lies above every splitter pair
-      const unsigned at_ = warp_off + j * kWarp + lane;
-      const unsigned d = digit(key[j], at_ < tile_valid ? prm.index_base + tile_base + at_ : ~0ull);
+      unsigned d;
+      if constexpr (TIES) {
+        const unsigned at_ = warp_off + j * kWarp + lane;
+        d = digit_pair(key[j], at_ < tile_valid ? index_base + tile_base + at_ : ~0ull);
+      } else {
+        d = digit(key[j]);
+      }
       if constexpr (SPLIT) bkt[j] = (unsigned char)d;
       const unsigned peers = SPLIT ? match_digit_bits(d, split_bits) : match_digit(d);
       const unsigned ahead = __popc(peers & lt_mask);
@@ -781,7 +801,7 @@ onesweep_kernel(const PassParams prm) {
       count += c;
     }
     // padding (all-ones keys at the end of the tile) carries the largest digit in use
-    if (d_own == (SPLIT ? digit((UK)~(UK)0, ~0ull) : mask)) count -= (unsigned)TILE - tile_valid;
+    if (d_own == (SPLIT ? (TIES ? num_split : digit((UK)~(UK)0)) : mask)) count -= (unsigned)TILE - tile_valid;
     if (grp == 0) {
       DescT* mine = static_cast<DescT*>(prm.desc) + (size_t)tile * kRadix + d_own;
       if (tile == 0) st_desc<DescT>(mine, ((DescT)st_prefix << DSH) | count);
@@ -1014,8 +1034,6 @@ int sort_impl(void* d_temp, size_t* temp_bytes, void* d_keys, void* d_vals, uint
   prm.desc = base + lay.desc_off;
   prm.splitters = nullptr;
   prm.num_splitters = 0;
-  prm.splitter_index = nullptr;
-  prm.index_base = 0;
   prm.bucket_keys = nullptr;
   prm.bucket_vals = nullptr;
   auto launch = [&](auto kernel, auto tag) -> int {
@@ -1285,8 +1303,10 @@ int partition_impl(void* d_temp, size_t* temp_bytes, const void* d_keys, const v
   prm.mask = num_splitters;
   prm.splitters = d_splitters;
   prm.num_splitters = num_splitters;
-  prm.splitter_index = reinterpret_cast<const unsigned long long*>(d_splitter_index);
-  prm.index_base = index_base;
+  if (d_splitter_index != nullptr) {
+    const unsigned long long pair_args[2] = {reinterpret_cast<unsigned long long>(d_splitter_index), index_base};
+    TB200_CUDA_TRY(cudaMemcpyAsync(&ctl->offs[3][0], pair_args, sizeof(pair_args), cudaMemcpyHostToDevice, stream));
+  }
   prm.bucket_keys = d_bucket_keys;
   prm.bucket_vals = d_bucket_vals;
   auto launch = [&](auto kernel, auto tag) -> int {
