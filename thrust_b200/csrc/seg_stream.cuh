@@ -288,6 +288,28 @@ __device__ __forceinline__ void close_block(const TileWords<1>* ctiles, TileWord
 __device__ __forceinline__ void prefetch_l2(const void* p, unsigned bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
+// L2 eviction priorities. The keys are read twice, a few microseconds apart (scouts, then the data
+// path): they are brought in to stay (evict_last) and read the second time, like everything that is
+// read once, as the first to go (evict_first).
+__device__ __forceinline__ unsigned long long policy_evict_last() {
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+  unsigned long long pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void prefetch_l2_hint(const void* p, unsigned bytes, unsigned long long pol) {
+  asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(p), "r"(bytes), "l"(pol) : "memory");
+}
+__device__ __forceinline__ void bulk_load_hint(void* smem_dst, const void* gmem_src, unsigned bytes,
+                                               unsigned long long* bar, unsigned long long pol) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
+               : "memory");
+}
 // read-only 16-byte load that the compiler may schedule freely (measured: keeping the lines in L1 and
 // dropping `volatile` took unique_by_key from 0.48 to 0.45 ms)
 __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
@@ -552,6 +574,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
   // ---------------------------------------------------------------------- producer
   if (warp == kRoleWarp0 + kLookWarps) {
     if (lane != 0) return;
+    const unsigned long long pol_first = policy_evict_first();
     // tile t goes into `slot`; false when the tickets have run past the last tile
     auto issue = [&](int slot, unsigned t) -> bool {
       if (t >= num_tiles) {
@@ -568,9 +591,14 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
         mbar_expect_tx(&s_full[slot], S::kKeyBytes + S::kValBytes + ((kNeedsPrev && t != 0) ? 16 : 0));
         if (kNeedsPrev && t != 0)
           bulk_load(s_halo[slot], reinterpret_cast<const unsigned char*>(a.keys + (uint64_t)t * TILE) - 16, 16, &s_full[slot]);
-        bulk_load(slot_keys(slot), a.keys + (uint64_t)t * TILE, S::kKeyBytes, &s_full[slot]);
-        if constexpr (kHasVals)
+        if constexpr (kScanOut) {
+          bulk_load(slot_keys(slot), a.keys + (uint64_t)t * TILE, S::kKeyBytes, &s_full[slot]);
           bulk_load(slot_vals(slot), a.vals + (uint64_t)t * TILE, S::kValBytes, &s_full[slot]);
+        } else {  // second and last read of the keys, only read of the values: first to leave L2
+          bulk_load_hint(slot_keys(slot), a.keys + (uint64_t)t * TILE, S::kKeyBytes, &s_full[slot], pol_first);
+          if constexpr (kHasVals)
+            bulk_load_hint(slot_vals(slot), a.vals + (uint64_t)t * TILE, S::kValBytes, &s_full[slot], pol_first);
+        }
       } else {
         mbar_arrive(&s_full[slot]);  // ragged last tile or unaligned input: the compute warps load it themselves
       }
@@ -604,6 +632,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
       return;  // the segmented scans compact nothing
     } else {
       unsigned long long* scout_ticket = &a.hdr->aux[kScoutTicket];
+      const unsigned long long pol_last = policy_evict_last();
       unsigned seen = 0;  // data tickets known to have been drawn
       while (true) {
         // (a ticket drawn ahead of its turn would sit idle for a whole tile while others wait for it)
@@ -616,7 +645,7 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
         // for exactly once, by the scout that draws the ticket kScoutPrefetch below it.
         if (lane == 0 && reinterpret_cast<uintptr_t>(a.keys) % 16 == 0) {
           const uint64_t pf = (uint64_t)u + kScoutPrefetch;
-          if ((pf + 1) * TILE <= n) prefetch_l2(a.keys + pf * TILE, S::kKeyBytes);
+          if ((pf + 1) * TILE <= n) prefetch_l2_hint(a.keys + pf * TILE, S::kKeyBytes, pol_last);
         }
         // stay within reach of the data path, so that the keys read here are still in L2 when the
         // tile is loaded again. (Tile u only waits while a data ticket below u - kScoutAhead is
