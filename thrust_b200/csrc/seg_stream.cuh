@@ -819,7 +819,43 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
       }
     } else {
       unsigned heads = st.heads;
-      if (heads) {
+      bool emitted = false;
+      if constexpr (MODE != kReduceByKey) {
+        // Many selected in the warp's slice: compact the slice in place in shared memory (read
+        // everything, synchronise, write each selected element to its rank), then copy it out with
+        // consecutive lanes writing consecutive elements. (Per-thread stores of ten elements each
+        // would touch thirty-two lines per instruction.)
+        const unsigned wtotal = __reduce_add_sync(0xffffffffu, (unsigned)__popc(heads));
+        if (wtotal * 3 > (unsigned)S::kWarpItems) {
+          K* wk = const_cast<K*>(sk) + w * S::kWarpItems;
+          V* wv = const_cast<V*>(sv) + w * S::kWarpItems;
+          const unsigned lo = lane * ITEMS;  // this thread's items inside the slice
+          K kk[MODE == kUniqueByKey ? ITEMS : 1];
+          V vv[kHasVals ? ITEMS : 1];
+#pragma unroll
+          for (int i = 0; i < ITEMS; ++i) {
+            if constexpr (MODE == kUniqueByKey) kk[i] = wk[lo + i];
+            if constexpr (kHasVals) vv[i] = wv[lo + i];
+          }
+          __syncwarp();
+          unsigned r = st.cnt;  // selected in the lanes in front
+#pragma unroll
+          for (int i = 0; i < ITEMS; ++i) {
+            if (heads & (1u << i)) {
+              if constexpr (MODE == kUniqueByKey) wk[r] = kk[i];
+              if constexpr (kHasVals) wv[r] = vv[i];
+              ++r;
+            }
+          }
+          __syncwarp();
+          for (unsigned i = lane; i < wtotal; i += kWarp) {
+            if constexpr (MODE == kUniqueByKey) a.keys_out[wcnt + i] = wk[i];
+            if constexpr (kHasVals) a.vals_out[wcnt + i] = wv[i];
+          }
+          emitted = true;
+        }
+      }
+      if (heads && !emitted) {
         unsigned long long at = wcnt + st.cnt;
         if constexpr (MODE == kReduceByKey) {
           // the run that closes at the thread's first head began in front of the thread
@@ -838,23 +874,12 @@ __global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args
             ++at;
           }
         } else {
-          if (__popc(heads) * 3 > ITEMS) {  // many selected: no dependent search for the next one
-#pragma unroll
-            for (int i = 0; i < ITEMS; ++i) {
-              if (heads & (1u << i)) {
-                if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
-                if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
-                ++at;
-              }
-            }
-          } else {
-            while (heads) {
-              const int i = __ffs(heads) - 1;
-              heads &= heads - 1;
-              if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
-              if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
-              ++at;
-            }
+          while (heads) {
+            const int i = __ffs(heads) - 1;
+            heads &= heads - 1;
+            if constexpr (MODE == kUniqueByKey) a.keys_out[at] = sk[my_off + i];
+            if constexpr (kHasVals) a.vals_out[at] = sv[my_off + i];
+            ++at;
           }
         }
       }
