@@ -382,7 +382,21 @@ def bench_others(dev, peak):
         return r == int(first.sum()) and bool((ko[:r] == keys[first]).all()) and bool((vo[:r] == vals[first]).all())
     entry("unique_by_key_i32_f32_2^28", ubk, lambda: None, n, "Gelem/s", 8.0 * (n + nruns),
           f"(n + kept) x (4 B key + 4 B value), kept = {nruns}", verify=ubk_ok)
-    del keys, vals, ko, vo, so, run_of
+    # next row of the path: copy_if with a stencil (half of the 4-byte elements selected)
+    flags = (keys & 1).to(torch.uint8)  # the low bit of the run id: whole runs in or out, about half of the elements
+    nsel = int(flags.sum())
+
+    def cpf():
+        capi.check(capi.lib.tb200_copy_flagged(
+            C.c_void_p(temp.data_ptr()), C.byref(have), C.c_void_p(vals.data_ptr()), C.c_void_p(flags.data_ptr()),
+            C.c_void_p(vo.data_ptr()), C.c_void_p(kept.data_ptr()), n, 4, capi.U8, st), "tb200_copy_flagged")
+
+    def cpf_ok():
+        r = int(kept.item())
+        return r == nsel and bool((vo[:r] == vals[flags.bool()]).all())
+    entry("copy_if_stencil_f32_u8_2^28", cpf, lambda: None, n, "Gelem/s", 5.0 * n + 4.0 * nsel,
+          f"4 B element + 1 B flag read, 4 B written per selected element, selected = {nsel}", verify=cpf_ok)
+    del keys, vals, ko, vo, so, run_of, flags
 
     # C3: stable sort_by_key of 2^28 (uint64, uint32) pairs
     k0, v0 = g.pairs_u64_u32(n, g.SEED_PAIRS_U64, 0, dev)
