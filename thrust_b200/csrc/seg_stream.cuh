@@ -1,43 +1,40 @@
 // Streaming skeleton of the by-key algorithms (reduce_by_key, inclusive / exclusive
-// scan_by_key, unique_by_key, copy of flagged elements): ONE pass over the input, a decoupled
-// look-back chain across tiles, and no barrier that spans the whole CTA on the data path.
+// scan_by_key, unique_by_key, copy of flagged elements): ONE pass over the input and no barrier
+// that spans the whole CTA on the data path.
 //
-// A persistent CTA (one per SM) has three kinds of warps:
+// A persistent CTA (one per SM) has these warps:
 //   * one producer thread draws tiles from an atomic ticket counter and fills a ring of
 //     shared-memory slots with bulk asynchronous copies (the untiled TMA form), keys and values
 //     of a tile per slot, completion signalled on the slot's `full` mbarrier;
-//   * kComputeWarps compute warps, each working on its own 32 x kItems slice of every tile
-//     WITHOUT synchronising with the other compute warps: phase A (head flags, run sums inside
-//     the thread, one segmented warp scan, warp total to shared memory; the LAST warp to get
-//     there combines the warp totals, publishes the tile's aggregate to the other CTAs with
-//     plain stores (nothing to wait for) and arrives on the slot's `scanned` mbarrier) and,
-//     whenever a parked tile's prefix has been resolved, phase C (the slot's `resolved`
-//     mbarrier, read the warp's prefix, emit, arrive on the slot's `freed` mbarrier);
-//   * one closer warp: when the CTA holds the LAST tile of a block of 32 tiles, it waits for the
-//     block's 32 aggregates and publishes the block's aggregate. This waiting sits on no other
-//     path: a compute warp that took global round trips would be the last again on the next
-//     tile and its loop would set the CTA's pace, and a look-back warp that did it would hold
-//     back the tiles queued behind it;
-//   * two look-back warps that take the CTA's tiles in turn: resolve the tile's prefix over the
-//     predecessor tiles and hand every compute warp its own prefix. (A tile's aggregate never
-//     waits behind a look-back: a look-back that is waiting for other CTAs' aggregates must not
-//     hold back the aggregate those CTAs are waiting for.)
-// The chain over tiles has two levels. Tiles are grouped in blocks of 32; a tile's prefix is the
-// prefix of its block plus the aggregates of the tiles in front of it inside the block. The
-// closer warp of the CTA that holds a block's last tile combines the block's 32 aggregates into
-// the block's aggregate as soon as they are all published; the block's last tile
-// publishes the block's inclusive prefix once it knows the block's prefix; block prefixes are
-// resolved by the usual decoupled look-back, but over BLOCK descriptors. No aggregate, of a
-// tile or of a block, ever waits behind a look-back. A tile therefore
-// resolves in two descriptor reads that are in flight together, however many tiles are
-// unresolved in front of it, and the serial chain is 32 times shorter than the tile sequence:
-// the tile rate a GPU at full HBM speed needs (over 100 tiles per microsecond) does not
-// outrun it.
-// Because every warp runs at its own pace, the latency chains of different warps (shared-memory
-// loads, dependent adds, shuffles, scattered stores) overlap instead of adding up behind CTA
-// barriers. Every tile, the first ring-full included, is drawn by ticket, so a tile is only
-// ever owned by a CTA that is already running: no look-back waits for an unscheduled CTA.
-// Every wait (mbarrier or look-back poll) is bounded and reports through the status word.
+//   * two teams of kComputeWarps compute warps; tile j of the CTA belongs to team j % 2, and each
+//     warp works on its own 32 x kItems slice of the tile WITHOUT synchronising with the other
+//     warps: phase A (head flags, run sums inside the thread, one segmented warp scan, warp total
+//     to shared memory; the LAST warp to get there combines the warp totals, publishes what other
+//     tiles need with plain stores and arrives on the slot's `scanned` mbarrier) and, once the
+//     slot's `resolved` mbarrier completes, phase C (emit, arrive on the slot's `freed`
+//     mbarrier). A warp scans the next tile as soon as it has landed and emits as soon as a
+//     parked tile is resolved; two teams keep sixteen such latency chains in flight per SM;
+//   * look-back warps that take the CTA's tiles in turn and supply what a tile needs from the
+//     tiles in front of it;
+//   * scout warps (compacting algorithms only), see below.
+//
+// What a tile needs from its predecessors differs by algorithm, and nothing waits for more:
+//   * scan_by_key needs the sum of the run that is open where the tile starts. A tile that holds
+//     a head is final for its successors the moment it is scanned, so the look-back goes to the
+//     NEAREST such tile (usually the one directly in front) instead of waiting for the slowest
+//     of the hundreds of tiles in flight;
+//   * reduce_by_key, unique and the copy of flagged elements need the NUMBER of heads in front of
+//     the tile: that depends on all predecessors, so it is produced ahead of the data by the
+//     scout warps (keys only, from L2-prefetched global memory) with a block-level chain, and is
+//     read by the look-back warp while the tile is still loading. reduce_by_key's one value that
+//     depends on other tiles (the run that the tile's first head closes) is stored by the
+//     look-back warp from the same nearest-final-tile chain as scan_by_key; the compute warps
+//     never wait for it.
+// A tile therefore stays in its slot for load + scan + emit and no longer for the prefix of
+// the whole grid. Every tile is drawn by ticket, so a tile is only ever owned by a CTA that is
+// already running: no wait depends on an unscheduled CTA. Every wait (mbarrier, descriptor
+// poll, idle loop, the scouts' throttle) is bounded and reports through the status word; the
+// first one to give up records where.
 #pragma once
 
 #include "common.cuh"
