@@ -26,7 +26,7 @@
 
 namespace {
 
-constexpr unsigned kSamples = 1024;  // per rank
+constexpr unsigned kSamples = 16384;  // per rank: the largest share exceeds the mean by ~1.3 % at eight ranks (5 % with 1024)
 
 #define TB200_TRY(expr)          \
   do {                           \
