@@ -7,11 +7,16 @@ Two pipelines share the sampling, splitter and exchange code:
 ``pipeline="partition_first"`` (default; one full local sort per step)
   1. regular sample of the shard: ``samples_per_rank`` keys at evenly spaced positions
   2. all-gather the samples; every rank sorts them identically and takes the keys
-     at ranks samples_per_rank * r (r = 1..G-1) as splitters
+     at ranks samples_per_rank * r (r = 1..G-1) as splitters. When one key makes up
+     a sixteenth of a rank's share of the sample or more, elements and splitters are
+     compared as (key, global index) pairs from here on, so that the copies of one
+     key can be divided between ranks, in input order
   3. stable partition of the shard into G buckets, destination d owning the keys in
-     (splitter[d-1], splitter[d]] (tb200_partition: one onesweep pass)
-  4. all-gather of the G x G count matrix, then all-to-all-v of keys and of values
-     over NCCL; received runs are stored in source-rank order
+     (splitter[d-1], splitter[d]] (tb200_partition*: one onesweep pass)
+  4. all-gather of the G x G count matrix, then the exchange: the partition pass
+     stores every bucket straight into its destination's receive buffer over NVLink
+     ("push", the default on GPUs), or all-to-all-v of keys and of values over NCCL;
+     received runs are stored in source-rank order
   5. local onesweep sort of the received pairs (tb200_radix_sort). Rank r holds
      global indices [r*n, (r+1)*n), so a stable sort of runs concatenated in
      source-rank order reproduces the single-process stable order.
@@ -22,6 +27,9 @@ Two pipelines share the sampling, splitter and exchange code:
   segments are contiguous ranges found by upper-bound search (tb200_histogram_sorted)
   with no data movement, and step 5 sorts runs that are already sorted. It costs a
   second full local sort and exists for comparison.
+
+``engine="c"`` runs the partition_first pipeline as ONE call of the C entry point
+tb200_sample_sort (include/thrust_b200_nccl.h) on a raw NCCL communicator.
 
 The collectives go through ``torch.distributed`` (NCCL on GPUs). The per-shard
 compute goes through an ``ops`` object; the default ``DeviceOps`` calls the CUDA
