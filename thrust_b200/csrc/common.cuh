@@ -108,13 +108,9 @@ __device__ __forceinline__ void note_timeout(int* status, unsigned site, unsigne
 }
 
 __device__ __forceinline__ void backoff(unsigned polls) {
-#if defined(TB200_EXPERIMENT_SLEEP_NS)
-  __nanosleep(TB200_EXPERIMENT_SLEEP_NS);
-#elif !defined(TB200_EXPERIMENT_NO_BACKOFF)
   // a short sleep from the first retry on: tight polling of the few descriptor lines that
   // every look-back reads delays the very stores it is waiting for
   __nanosleep(polls > 256 ? 400 : 100);
-#endif
 }
 
 // Tile descriptors of the decoupled look-back chains. A descriptor is W 64-bit
