@@ -1,8 +1,8 @@
 """Build the C++ boundary test (Thrust custom system over the C ABI) and the small C++ timing
 program of the policy path for sm_100a.
 
-Output: tests/cpp/bin/test_system and tests/cpp/bin/bench_system, linked against
-thrust_b200/libthrust_b200.so by relative rpath. Uses the CUDA toolkit's Thrust headers.
+Output: tests/cpp/bin/test_system, bench_system and test_sample_sort (the C entry point of the
+sharded sort called from C++), linked against thrust_b200/libthrust_b200.so by relative rpath. Uses the CUDA toolkit's Thrust headers.
 """
 import os
 import subprocess
@@ -12,7 +12,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 LIBDIR = ROOT / "thrust_b200"
-PROGRAMS = ("test_system", "bench_system")
+PROGRAMS = ("test_system", "bench_system", "test_sample_sort")
 
 
 def _build_one(name: str, force: bool) -> Path:
@@ -24,6 +24,8 @@ def _build_one(name: str, force: bool) -> Path:
     cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17",
            "--extended-lambda", "-ccbin", "/usr/bin/g++", "-I", str(ROOT / "include"), str(src), "-o", str(out),
            "-L", str(LIBDIR), "-lthrust_b200", "-Xlinker", "-rpath=$ORIGIN/../../../thrust_b200"]
+    if name == "test_sample_sort":  # the sharded sort's C entry point lives in the NCCL library
+        cmd += ["-lthrust_b200_nccl", "-lnccl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n" + r.stdout + r.stderr)
