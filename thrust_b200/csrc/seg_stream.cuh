@@ -409,14 +409,20 @@ constexpr int kComputeWarps = 8;  // warps of one team: a tile is split over the
 constexpr int kComputeThreads = kComputeWarps * kWarp;
 constexpr int kTeams = 2;      // teams of compute warps; tile j of a CTA belongs to team j % kTeams
 constexpr int kLookWarps = 2;  // look-back warps; tile j of a CTA is resolved by warp j % kLookWarps
-constexpr int kScoutWarps = 6; // warps that count heads ahead of the data (compacting algorithms only)
+// Warps that count heads ahead of the data (compacting algorithms only). Measured: the scouts take issue
+// slots from the compute warps, so an algorithm gets as few as keep its counts ahead: reduce_by_key and
+// the copy of flagged elements (whose compute warps do the most per tile) 4, unique_by_key 5, keys-only
+// unique (the cheapest tiles, so the fastest consumer) 6.
+constexpr int scout_warps(int mode, bool has_vals) {
+  return (mode == 1 || mode == 2) ? 0 : (mode == 0 || mode == 4) ? 4 : (has_vals ? 5 : 6);
+}
 constexpr unsigned kScoutAhead = 1536;  // tiles a scout may run in front of the data tickets (their keys stay in L2)
 constexpr unsigned kScoutPrefetch = 512;  // a scout that draws tile u asks for the keys of tile u + kScoutPrefetch
 constexpr int kStops = kLookWarps > kTeams ? kLookWarps : kTeams;  // "no tile" slots that end the roles
 constexpr int kRoleWarp0 = kTeams * kComputeWarps;  // first warp that is not a compute warp
 // compute warps + look-back warps + producer (+ scouts: the segmented scans compact nothing and run without)
-constexpr int cta_threads(int mode) {
-  return (kRoleWarp0 + kLookWarps + 1 + ((mode == 1 || mode == 2) ? 0 : kScoutWarps)) * kWarp;
+constexpr int cta_threads(int mode, bool has_vals) {
+  return (kRoleWarp0 + kLookWarps + 1 + scout_warps(mode, has_vals)) * kWarp;
 }
 constexpr int kScoutTicket = 8;  // TempHeader::aux word that deals tiles to the scouts
 constexpr int kPacks = 5;   // 16-byte packs of the wider type per thread: an 80-byte stride has no bank conflicts
@@ -465,7 +471,7 @@ template <typename V> struct AccOf<kScanByKeyIncl, V> { using type = V; };
 template <typename V> struct AccOf<kScanByKeyExcl, V> { using type = V; };
 
 template <int MODE, typename K, typename V>
-__global__ void __launch_bounds__(cta_threads(MODE), 1) stream_kernel(const Args<K, V> a) {
+__global__ void __launch_bounds__(cta_threads(MODE, !std::is_same<V, NoVal>::value), 1) stream_kernel(const Args<K, V> a) {
   using S = Shape<K, V>;
   using A = typename AccOf<MODE, V>::type;
   constexpr bool kSum = MODE == kReduceByKey || MODE == kScanByKeyIncl || MODE == kScanByKeyExcl;
@@ -1183,7 +1189,7 @@ int launch(const K* keys, const V* vals, K* keys_out, V* vals_out, unsigned long
   const int rc = sm_count(&sms);
   if (rc) return rc;
   const unsigned grid = (unsigned)(tiles < (uint64_t)sms ? tiles : (uint64_t)sms);
-  kernel<<<grid, cta_threads(MODE), S::kSmem, stream>>>(a);
+  kernel<<<grid, cta_threads(MODE, S::kHasVals), S::kSmem, stream>>>(a);
   return (int)cudaGetLastError();
 }
 
